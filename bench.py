@@ -1,0 +1,385 @@
+"""Benchmark of the moe_fused_linear hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload gate_up|down]
+
+One step = one pass of the hot path over one synthetic batch of the Qwen3-30B-A3B gate_up
+shape: grouped-GEMM forward, input gradient (dX) and weight gradient (dW) for 65536
+expanded rows (8192 tokens x top-8), hidden 2048 -> 1536, 128 experts, bf16 with fp32
+accumulation.  `value` is the algorithmic TFLOP/s (2*M*N*K per GEMM, real rows only) of the
+whole job with inputs resident in HBM; `e2e` is the same figure through the public Python
+API with inputs in pinned host memory (router epilogue, sort, gather and the three GEMMs,
+host->device and device->host copies inside the timed region).
+
+With N > 1 the 128 experts are sharded over the ranks (expert parallel); every rank routes
+its own 8192 tokens, rows travel to the rank that owns their expert by NCCL all-to-all and
+gradients travel back (weak scaling: per-GPU rows are fixed).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (str(ROOT), str(ROOT / "transformers-qwen3-moe-fused_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np
+import torch
+
+WORKLOADS = {
+    # name: (tokens, hidden(K), out(N), experts, top_k, routing)
+    "gate_up": dict(tokens=8192, K=2048, N=1536, E=128, k=8, routing="softmax-top8 of N(0,1) logits"),
+    "down": dict(tokens=8192, K=768, N=2048, E=128, k=8, routing="zipf(1.2) expert ids, 3 experts emptied"),
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def make_routing(cfg, seed: int):
+    """Expert id per expanded row (tokens*k,), int64, on the CPU."""
+    g = torch.Generator().manual_seed(seed)
+    T, E, k = cfg["tokens"], cfg["E"], cfg["k"]
+    if cfg["routing"].startswith("softmax"):
+        logits = torch.randn(T, E, generator=g)
+        return logits, None
+    pmf = (torch.arange(E, dtype=torch.float64) + 1) ** -1.2
+    ids = torch.multinomial(pmf / pmf.sum(), T * k, replacement=True, generator=g)
+    for dead in (5, 64, 127):
+        ids[ids == dead] = 0
+    perm = torch.randperm(E, generator=g)
+    return None, perm[ids]
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 3), ("hw_thermal_slowdown", 4), ("sw_thermal_slowdown", 5), ("sw_power_cap", 6)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_reference_arm(cfg, steps: int, warmup: int, sample_rows: int):
+    """The reference's CPU implementation of the path (one torch mat-vec / outer product per
+    row, qwen3_moe_fused/functional.py:7-61 of the reference) on all host threads, on a
+    bounded sample of the workload's rows."""
+    from oracle import cpu_baseline as C
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    K, N, E = cfg["K"], cfg["N"], cfg["E"]
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(E, N, K, generator=g) * 0.02
+    x = torch.randn(sample_rows, K, generator=g)
+    dy = torch.randn(sample_rows, N, generator=g)
+    experts = torch.sort(torch.randint(0, E, (sample_rows,), generator=g)).values
+    flops = 3 * 2.0 * sample_rows * N * K
+
+    def step():
+        C.rowloop_fwd(x, w, experts)
+        C.rowloop_bwd_input(dy, w, experts)
+        C.rowloop_bwd_weight(dy, x, w, experts)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return flops / dt / 1e12, dt, torch.get_num_threads()
+
+
+def run_reference(args, cfg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = args.cpu_rows
+    steps = max(1, min(args.steps, 2))
+    warm = 1 if args.warmup > 0 else 0
+    tf, dt, cores = cpu_reference_arm(cfg, steps, warm, rows)
+    sample = f"{rows} of {cfg['tokens'] * cfg['k']} sorted rows, fp32, fwd+dX+dW row loops, {steps} timed step(s)"
+    line = {
+        "impl": "reference", "metric": "moe_fused_linear fwd+dX+dW algorithmic TFLOP/s", "value": tf, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_dict(args, cfg),
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(args, cfg):
+    return {"workload": f"Qwen3-30B-A3B {args.workload} grouped GEMM fwd+dX+dW: {cfg['tokens']} tokens x top-{cfg['k']} = "
+                        f"{cfg['tokens'] * cfg['k']} rows/GPU, in={cfg['K']}, out={cfg['N']}, experts={cfg['E']}",
+            "routing": cfg["routing"], "l2": "inputs larger than L2 (weights alone exceed 400 MB); no flush needed",
+            "parallelism": "single GPU" if args.gpus == 1 else f"expert parallel ep{args.gpus} (all-to-all dispatch/combine)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="gate_up", choices=sorted(WORKLOADS))
+    ap.add_argument("--cpu-rows", type=int, default=4096, help="rows of the bounded CPU-baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, cfg)
+        return
+
+    import __graft_entry__ as entry
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    if rank == 0:
+        entry.build()
+    if world > 1:
+        dist.barrier()
+
+    from qwen3_moe_fused import _lib
+    from qwen3_moe_fused.grouped_gemm.backward_dw import grouped_gemm_backward_dw
+    from qwen3_moe_fused.grouped_gemm.forward import grouped_gemm_forward
+    from qwen3_moe_fused.grouped_gemm.forward_transposed import grouped_gemm_forward_transposed
+    from qwen3_moe_fused.kernels.indexing import get_expert_counts_and_idx
+    from qwen3_moe_fused.kernels.routing import _gather_rows, softmax_topk
+
+    _lib.load()
+    T, K, N, E, k = cfg["tokens"], cfg["K"], cfg["N"], cfg["E"], cfg["k"]
+    M = T * k
+    E_local = E // world
+    gen = torch.Generator().manual_seed(1234 + rank)
+    bf = torch.bfloat16
+
+    # ---- synthetic inputs (host, pinned) ----
+    logits_h, ids_h = make_routing(cfg, seed=rank)
+    hidden_h = torch.randn(T, K, generator=gen).to(bf).pin_memory()
+    dy_h = torch.randn(M, N, generator=gen).to(bf).pin_memory()
+    if logits_h is not None:
+        logits_h = logits_h.pin_memory()
+    else:
+        ids_h = ids_h.pin_memory()
+    w = (torch.randn(E_local, N, K, generator=torch.Generator().manual_seed(99 + rank)) * 0.02).to(bf).to(dev)
+
+    if world > 1:
+        from qwen3_moe_fused.parallel_ep import ExpertParallelPlan
+
+    def route_and_sort(logits_d, ids_d):
+        if logits_d is not None:
+            _, sel = softmax_topk(logits_d, k, True, bf)
+            sel = sel.view(-1)
+        else:
+            sel = ids_d
+        return get_expert_counts_and_idx(sel, E)
+
+    # ---- resident inputs for the kernel-only measurement ----
+    logits_d = logits_h.to(dev) if logits_h is not None else None
+    ids_d = ids_h.to(dev) if ids_h is not None else None
+    hidden_d = hidden_h.to(dev)
+    dy_d = dy_h.to(dev)
+    m_sizes, sort_idx, inv_sort_idx = route_and_sort(logits_d, ids_d)
+    x_d = _gather_rows(hidden_d, sort_idx, k)
+    plan = None
+    if world > 1:
+        plan = ExpertParallelPlan.build(m_sizes, world, rank, dev)
+    torch.cuda.synchronize()
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    kernel_ms = {"fwd": [], "dx": [], "dw": []}
+    launches_per_step = 3
+
+    def step_resident(record: bool):
+        if world == 1:
+            marks = [ev() for _ in range(4)]
+            marks[0].record()
+            y = grouped_gemm_forward(x_d, w, m_sizes)
+            marks[1].record()
+            dx = grouped_gemm_forward_transposed(dy_d, w, m_sizes)
+            marks[2].record()
+            dw = grouped_gemm_backward_dw(x_d, dy_d, m_sizes, bf)
+            marks[3].record()
+            return marks if record else None, (y, dx, dw)
+        # expert parallel: rows to their experts, compute, results back
+        marks = [ev() for _ in range(4)]
+        xl = plan.dispatch(x_d)
+        dyl = plan.dispatch(dy_d)
+        marks[0].record()
+        y = plan.grouped(grouped_gemm_forward, xl, w)
+        marks[1].record()
+        dx = plan.grouped(grouped_gemm_forward_transposed, dyl, w)
+        marks[2].record()
+        dw = plan.grouped_dw(grouped_gemm_backward_dw, xl, dyl, bf, E_local)
+        marks[3].record()
+        y_back = plan.combine(y)
+        dx_back = plan.combine(dx)
+        return marks if record else None, (y_back, dx_back, dw)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident(False)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    t_start, t_end = ev(), ev()
+    all_marks = []
+    t_start.record()
+    for _ in range(args.steps):
+        marks, _ = step_resident(True)
+        all_marks.append(marks)
+    t_end.record()
+    barrier()
+    resident_ms = t_start.elapsed_time(t_end) / args.steps
+    for marks in all_marks:
+        kernel_ms["fwd"].append(marks[0].elapsed_time(marks[1]))
+        kernel_ms["dx"].append(marks[1].elapsed_time(marks[2]))
+        kernel_ms["dw"].append(marks[2].elapsed_time(marks[3]))
+
+    # ---- end to end through the public API, inputs in pinned host memory ----
+    h2d = hidden_h.numel() * 2 + dy_h.numel() * 2 + (logits_h.numel() * 4 if logits_h is not None else ids_h.numel() * 8)
+    d2h = 3 * 4 + E * 4
+
+    def step_e2e():
+        hd = hidden_h.to(dev, non_blocking=True)
+        dyd = dy_h.to(dev, non_blocking=True)
+        lg = logits_h.to(dev, non_blocking=True) if logits_h is not None else None
+        idd = ids_h.to(dev, non_blocking=True) if ids_h is not None else None
+        ms, si, _ = route_and_sort(lg, idd)
+        xs = _gather_rows(hd, si, k)
+        if world == 1:
+            y = grouped_gemm_forward(xs, w, ms)
+            dx = grouped_gemm_forward_transposed(dyd, w, ms)
+            dw = grouped_gemm_backward_dw(xs, dyd, ms, bf)
+        else:
+            pl = ExpertParallelPlan.build(ms, world, rank, dev)
+            xl, dyl = pl.dispatch(xs), pl.dispatch(dyd)
+            y = pl.combine(pl.grouped(grouped_gemm_forward, xl, w))
+            dx = pl.combine(pl.grouped(grouped_gemm_forward_transposed, dyl, w))
+            dw = pl.grouped_dw(grouped_gemm_backward_dw, xl, dyl, bf, E_local)
+        stats = torch.stack([y[0].float().sum(), dx[0].float().sum(), dw[0, 0].float().sum()])
+        return stats.cpu(), ms.cpu()  # device -> host read of the step's result
+
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(args.steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    # max over ranks
+    times = torch.tensor([resident_ms, e2e_ms, float(np.mean(kernel_ms["fwd"])), float(np.mean(kernel_ms["dx"])),
+                          float(np.mean(kernel_ms["dw"]))], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    resident_ms, e2e_ms, fwd_ms, dx_ms, dw_ms = times.tolist()
+    err_flag = _lib.read_error_flag()
+
+    if rank == 0:
+        peaks, peaks_kind = measured_peaks()
+        flops_one = 2.0 * M * N * K  # per GEMM per GPU
+        total_flops = 3 * flops_one * world
+        per_kernel = {"fwd": fwd_ms, "dx": dx_ms, "dw": dw_ms}
+        dominant = max(per_kernel, key=per_kernel.get)
+        achieved = flops_one / (per_kernel[dominant] * 1e-3) / 1e12
+        peak = peaks["bf16_tflops_sustained"]
+        alg_bytes = 2.0 * (M * K + E_local * N * K + M * N)
+        line = {
+            "metric": "moe_fused_linear fwd+dX+dW algorithmic TFLOP/s", "value": total_flops / (resident_ms * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": resident_ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": config_dict(args, cfg),
+            "kernels": {name: {"ms": ms, "tflops": flops_one / (ms * 1e-3) / 1e12,
+                               "frac_of_sustained_peak": flops_one / (ms * 1e-3) / 1e12 / peak,
+                               "frac_of_burst_peak": flops_one / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+                               "frac_of_nominal_2250": flops_one / (ms * 1e-3) / 1e12 / 2250.0,
+                               "algorithmic_gbs": alg_bytes / (ms * 1e-3) / 1e9}
+                        for name, ms in per_kernel.items()},
+            "roofline": {"bound": "tensor", "kernel": f"tc grouped gemm {dominant}", "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak, "peak_kind": f"bf16_tflops_sustained, {peaks_kind}",
+                         "traffic": None},
+            "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "tokens_per_s": T * world / (e2e_ms * 1e-3)},
+            "gpu_launches": args.steps * launches_per_step,
+            "tokens_per_s": T * world / (resident_ms * 1e-3),
+            "clocks": clocks, "kernel_wait_errors": err_flag,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            tf, dt, cores = cpu_reference_arm(cfg, 1, 0, args.cpu_rows)
+            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                    "sample": f"{args.cpu_rows} of {M} sorted rows, fp32, fwd+dX+dW row loops, 1 pass, {dt:.1f} s"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,169 @@
+/*
+ * moe_b200.h - C ABI of libmoe_b200.so: the sm_100a implementation of the
+ * `moe_fused_linear` hot path of transformers-qwen3-moe-fused.
+ *
+ * Conventions shared by every entry point
+ *   - Every pointer except `stream` is a DEVICE pointer owned by the caller.  The
+ *     library never allocates, frees or retains device memory.
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the call
+ *     returns without synchronising.  `m_sizes` is only ever read on the device.
+ *   - Return value: 0 = success; < 0 = argument error, nothing was launched
+ *     (see MOE_ERR_*); > 0 = a cudaError_t reported by the runtime.
+ *   - dtype codes: MOE_F32 / MOE_BF16 / MOE_F16 for floating point tensors,
+ *     MOE_I32 / MOE_I64 for integer tensors.
+ *   - All tensors are dense row-major ("contiguous" in torch terms).
+ *
+ * The comment on each function names the reference interface it stands in for
+ * (path inside the reference project : lines).
+ */
+#ifndef MOE_B200_H_
+#define MOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { MOE_F32 = 0, MOE_BF16 = 1, MOE_F16 = 2, MOE_I32 = 3, MOE_I64 = 4 };
+
+enum {
+  MOE_OK = 0,
+  MOE_ERR_DTYPE = -1,      /* unsupported dtype code or dtype combination        */
+  MOE_ERR_SHAPE = -2,      /* negative / inconsistent / unsupported extent       */
+  MOE_ERR_NULL = -3,       /* a required pointer is NULL                         */
+  MOE_ERR_WORKSPACE = -4,  /* workspace missing or smaller than the query said   */
+  MOE_ERR_UNSUPPORTED = -5,/* valid request that this build has no kernel for    */
+  MOE_ERR_ALIGN = -6,      /* pointer or pitch not aligned as the kernel needs   */
+  MOE_ERR_DEVICE = -7      /* device is not sm_100 or a driver entry is missing  */
+};
+
+/* Which kernel family a grouped GEMM call may use.
+ * AUTO: tcgen05 when the shape and dtype are eligible, SIMT otherwise.
+ * SIMT: CUDA-core kernel (any shape, fp32 math for fp32 inputs).
+ * TC:   tcgen05 kernel or MOE_ERR_UNSUPPORTED. */
+enum { MOE_PATH_AUTO = 0, MOE_PATH_SIMT = 1, MOE_PATH_TC = 2 };
+
+/* Library build version (monotonic integer). */
+int moe_b200_version(void);
+
+/* Human readable text for a status returned by any function below. */
+const char* moe_status_string(int status);
+
+/* Set / get the kernel family used by the grouped GEMM entry points (process wide,
+ * MOE_PATH_*; default AUTO).  Returns the previous value. */
+int moe_set_gemm_path(int path);
+int moe_get_gemm_path(void);
+
+/* ---------------------------------------------------------------------------------
+ * Stable sort of rows by expert id.
+ * Replaces qwen3_moe_fused/kernels/indexing.py:48-65 (get_expert_counts_and_idx) and,
+ * with idx/inv_idx NULL, :18-23 (get_expert_counts).
+ *   s        (M,)  expert id per row, s_dtype = MOE_I32 or MOE_I64, values in [0,E)
+ *   counts   (E,)  int32  rows per expert
+ *   inv_idx  (M,)  int32  inv_idx[j] = original row at sorted position j (gather index)
+ *   idx      (M,)  int32  idx[b]     = sorted position of original row b
+ * Ties keep their original order (identical to a stable argsort).
+ * ws must hold moe_sort_workspace_bytes(M, E) bytes; its contents are scratch.
+ * ------------------------------------------------------------------------------- */
+size_t moe_sort_workspace_bytes(int64_t M, int E);
+int moe_sort_by_expert(const void* s, int s_dtype, int64_t M, int E,
+                       int32_t* counts, int32_t* inv_idx, int32_t* idx,
+                       void* ws, size_t ws_bytes, void* stream);
+
+/* Begin/end row of every expert in an already sorted id vector.
+ * Replaces qwen3_moe_fused/kernels/indexing.py:7-14 (get_batch_begins_ends).
+ *   begins_ends (E,2) int32: [e,0] = #rows with id < e, [e,1] = #rows with id <= e */
+int moe_batch_begins_ends(const void* s_sorted, int s_dtype, int64_t M, int E,
+                          int32_t* begins_ends, void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * Grouped GEMMs.  Rows of x / y are sorted by expert; expert e owns m_sizes[e]
+ * consecutive rows (m_sizes_dtype MOE_I32 or MOE_I64, sum = M, zeros allowed).
+ * Accumulation is fp32; the result is rounded once to dtype_out.
+ * ws/ws_bytes: moe_grouped_gemm_workspace_bytes(); may be NULL/0 when that is 0.
+ * ------------------------------------------------------------------------------- */
+size_t moe_grouped_gemm_workspace_bytes(int which /*0 fwd, 1 dx, 2 dw*/, int64_t M, int N, int K, int E);
+
+/* y[m,n] = sum_k w[e(m),n,k] * x[m,k];  x (M,K), w (E,N,K), y (M,N).
+ * Replaces qwen3_moe_fused/grouped_gemm/forward.py:116-160 (grouped_gemm_forward). */
+int moe_grouped_gemm_fwd(const void* x, const void* w, const void* m_sizes, int m_sizes_dtype,
+                         void* y, int64_t M, int N, int K, int E, int dtype_in, int dtype_out,
+                         void* ws, size_t ws_bytes, void* stream);
+
+/* y[m,n] = sum_k w[e(m),k,n] * x[m,k];  x (M,K), w (E,K,N), y (M,N)  (this is dX).
+ * Replaces qwen3_moe_fused/grouped_gemm/forward_transposed.py:107-151
+ * (grouped_gemm_forward_transposed). */
+int moe_grouped_gemm_dx(const void* x, const void* w, const void* m_sizes, int m_sizes_dtype,
+                        void* y, int64_t M, int N, int K, int E, int dtype_in, int dtype_out,
+                        void* ws, size_t ws_bytes, void* stream);
+
+/* w[e,n,k] = sum_{m in group e} y[m,n] * x[m,k];  x (M,K), y (M,N), w (E,N,K).
+ * Experts without rows get zeros.
+ * Replaces qwen3_moe_fused/grouped_gemm/backward_dw.py:92-134 (grouped_gemm_backward_dw). */
+int moe_grouped_gemm_dw(const void* x, const void* y, const void* m_sizes, int m_sizes_dtype,
+                        void* w, int64_t M, int N, int K, int E, int dtype_in, int dtype_out,
+                        void* ws, size_t ws_bytes, void* stream);
+
+/* Forward with an NF4 weight decoded inside the kernel:
+ *   w[e,n,k] = code[nibble(e,n,k)] * absmax[(e*N*K + n*K + k) / blocksize], rounded to
+ *   dtype_in, then as moe_grouped_gemm_fwd.  packed: E*N*K/2 bytes, element 2j in the
+ *   HIGH nibble of byte j and element 2j+1 in the low nibble; code: 16 fp32;
+ *   absmax: E*N*K/blocksize fp32 (already un-nested); blocksize a power of two.
+ * Replaces qwen3_moe_fused/grouped_gemm/forward_4bit.py:135-208 (grouped_gemm_forward_4bit). */
+int moe_grouped_gemm_fwd_nf4(const void* x, const uint8_t* packed, const float* code,
+                             const float* absmax, int blocksize,
+                             const void* m_sizes, int m_sizes_dtype, void* y,
+                             int64_t M, int N, int K, int E, int dtype_in, int dtype_out,
+                             void* ws, size_t ws_bytes, void* stream);
+
+/* Stand-alone NF4 decode of n_elems weights (same format as above) to dtype_out.
+ * Stands in for the bitsandbytes dequantize_4bit call at
+ * qwen3_moe_fused/quantize/layer.py:21 and qwen3_moe_fused/kernels/fast_lora.py:62. */
+int moe_nf4_dequant(const uint8_t* packed, const float* code, const float* absmax, int blocksize,
+                    void* out, int64_t n_elems, int dtype_out, void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * SiLU-mul.  Replaces qwen3_moe_fused/kernels/silu_mul.py:114-161.
+ *   fwd:         h = dtype(silu_f32(e)) * g
+ *   bwd:         de, dg from dh, e, g
+ *   bwd_inplace: (dh, e, g) overwritten by (h, de, dg)
+ * ------------------------------------------------------------------------------- */
+int moe_silu_mul_fwd(const void* e, const void* g, void* h, int64_t n, int dtype, void* stream);
+int moe_silu_mul_bwd(const void* dh, const void* e, const void* g, void* de, void* dg,
+                     int64_t n, int dtype, void* stream);
+int moe_silu_mul_bwd_inplace(void* dh, void* e, void* g, int64_t n, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * Router: softmax over E logits in fp32, top-k (value descending, ties by ascending
+ * expert id), optional renormalisation, weights rounded to dtype_w.
+ * Replaces qwen3_moe_fused/modular_qwen3_moe_fused.py:87-93.
+ *   logits (T,E) dtype_logits; weights (T,k) dtype_w; experts (T,k) int64
+ * ------------------------------------------------------------------------------- */
+int moe_router_softmax_topk(const void* logits, int dtype_logits, int64_t T, int E, int k,
+                            int norm_topk, void* weights, int dtype_w, int64_t* experts,
+                            void* stream);
+
+/* out[j,:] = hidden[sort_idx[j] / k, :]   (expand by k then gather, in one pass).
+ * Replaces qwen3_moe_fused/modular_qwen3_moe_fused.py:95-103. */
+int moe_gather_rows(const void* hidden, const int32_t* sort_idx, int k, void* out,
+                    int64_t rows, int H, int dtype, void* stream);
+
+/* out[t,:] = sum_j weights[t,j] * y[inv_sort_idx[t*k+j], :]  with the reference's
+ * rounding (product and sum in fp32, one rounding to dtype).
+ * Replaces qwen3_moe_fused/modular_qwen3_moe_fused.py:112-115. */
+int moe_combine(const void* y, const int32_t* inv_sort_idx, const void* weights, void* out,
+                int64_t T, int k, int H, int dtype, void* stream);
+
+/* Diagnostics.  Every wait inside the tensor-core kernels is bounded; a wait that gave up
+ * records (reason << 16 | CTA index) in a device-side word.  This call copies that word to
+ * *flag_out (0 = no wait was ever abandoned) and optionally clears it.  It synchronises
+ * the device, so it is meant for tests and post-mortems, not for the hot path.
+ * No counterpart in the reference. */
+int moe_debug_read_error(int* flag_out, int clear);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_B200_H_ */

@@ -1,0 +1,69 @@
+"""NF4-fused forward (CUDA-core and tcgen05 forms) vs the oracle's decode + GEMM."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+from tests.helpers import DT, assert_close, random_m_sizes, rounded, to_dev, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+def make(cuda, rng, M, K, N, E, bs, dtype, empty=0.0):
+    from qwen3_moe_fused.quantize.nf4 import Nf4State
+
+    code = O.nf4_code()
+    w = (rng.standard_normal((E, N, K)) / np.sqrt(K)).astype(np.float32)
+    packed, absmax = O.nf4_quantize(w, bs, code)
+    w_deq = O.nf4_dequantize(packed, absmax, code, bs, w.shape, dtype)  # rounded to the activation dtype
+    x = rounded(rng.standard_normal((M, K)), dtype)
+    m_sizes = random_m_sizes(rng, M, E, empty)
+    state = Nf4State(absmax=torch.from_numpy(absmax).to(cuda), code=torch.from_numpy(code).to(cuda), blocksize=bs,
+                     shape=torch.Size(w.shape), dtype=DT[dtype])
+    return x, torch.from_numpy(packed).to(cuda), state, m_sizes, O.grouped_gemm_fwd(x, w_deq, m_sizes, dtype)
+
+
+@pytest.mark.parametrize("path", ["simt", "tc"])
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("M,K,N,E,bs,empty", [
+    (1024, 2048, 768, 128, 256, 0.0),   # the reference's kernel test shape and block size
+    (512, 256, 320, 8, 64, 0.2),
+    (300, 128, 64, 5, 128, 0.0),
+    (4096, 2048, 1536, 4, 64, 0.0),     # gate_up width, block size 64
+])
+def test_fused_forward(cuda, path, dtype, M, K, N, E, bs, empty):
+    from qwen3_moe_fused import _lib
+    from qwen3_moe_fused.grouped_gemm.forward_4bit import grouped_gemm_forward_4bit
+
+    rng = np.random.default_rng(M + K + N + E + bs)
+    x, packed, state, m_sizes, ref = make(cuda, rng, M, K, N, E, bs, dtype, empty)
+    prev = _lib.set_gemm_path(_lib.PATH_SIMT if path == "simt" else _lib.PATH_TC)
+    try:
+        y = grouped_gemm_forward_4bit(to_dev(x, dtype, cuda), packed, state, torch.from_numpy(m_sizes).to(cuda))
+        torch.cuda.synchronize()
+    finally:
+        _lib.set_gemm_path(prev)
+    assert _lib.read_error_flag() == 0
+    assert_close(to_np(y), ref, dtype, f"nf4 fwd {path}")
+
+
+def test_small_blocksize_and_odd_shapes_use_cuda_cores(cuda):
+    from qwen3_moe_fused.grouped_gemm.forward_4bit import grouped_gemm_forward_4bit
+
+    rng = np.random.default_rng(3)
+    x, packed, state, m_sizes, ref = make(cuda, rng, 77, 6, 10, 4, 4, "f32", 0.0)
+    y = grouped_gemm_forward_4bit(to_dev(x, "f32", cuda), packed, state, torch.from_numpy(m_sizes).to(cuda))
+    assert_close(to_np(y), ref, "f32", "nf4 fwd tiny", scale=5)
+
+
+def test_fused_equals_decode_then_gemm(cuda):
+    from qwen3_moe_fused.quantize.linear4bit import moe_fused_linear_4bit
+
+    rng = np.random.default_rng(4)
+    x, packed, state, m_sizes, ref = make(cuda, rng, 2048, 512, 512, 16, 64, "bf16", 0.1)
+    tx = to_dev(x, "bf16", cuda)
+    tm = torch.from_numpy(m_sizes).to(cuda)
+    a = moe_fused_linear_4bit(tx, packed, state, tm, fused=True)
+    b = moe_fused_linear_4bit(tx, packed, state, tm, fused=False)
+    assert_close(to_np(a), to_np(b), "bf16", "fused vs unfused")
+    assert_close(to_np(a), ref, "bf16", "fused vs oracle")

@@ -1,0 +1,310 @@
+// HBM-bound kernels around the grouped GEMMs: SiLU-mul (forward, backward, in-place
+// backward), NF4 decode, expand+gather of token rows, un-permute+weighted combine.
+// All of them move 16 bytes per thread per access when pointers and extents allow it
+// and fall back to scalar accesses otherwise; grids are a multiple of the SM count and
+// loop with a grid stride.
+#include "common.cuh"
+
+namespace moe {
+
+constexpr int EW_THREADS = 256;
+
+static inline int ew_grid(int64_t work_items) {
+  const int64_t want = (work_items + EW_THREADS - 1) / EW_THREADS;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  int64_t g = want < cap ? want : cap;
+  return (int)(g < 1 ? 1 : g);
+}
+
+static inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+template <typename T> struct Vec { static constexpr int N = 16 / sizeof(T); T v[N]; };
+
+template <typename T>
+__device__ __forceinline__ Vec<T> load_vec(const T* p) {
+  Vec<T> r;
+  *reinterpret_cast<uint4*>(r.v) = *reinterpret_cast<const uint4*>(p);
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* p, const Vec<T>& r) {
+  *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(r.v);
+}
+
+__device__ __forceinline__ float sigmoid_f32(float x) { return 1.f / (1.f + __expf(-x)); }
+
+// Rounding points follow qwen3_moe_fused/kernels/silu_mul.py:34-39 (forward) and
+// :66-73 / :101-111 (backward): f = T(e*sigmoid(e)) with e in fp32; h = f*g, df = dh*g,
+// dg = f*dh in T; de = T(f32(df) * sigmoid * (1 + e - e*sigmoid)).
+template <typename T>
+__device__ __forceinline__ T mul_t(T a, T b) { return from_f32<T>(to_f32(a) * to_f32(b)); }
+
+template <typename T>
+__device__ __forceinline__ T silu_fwd_one(T e, T g) {
+  const float e32 = to_f32(e);
+  const T f = from_f32<T>(e32 * sigmoid_f32(e32));
+  return mul_t(f, g);
+}
+
+template <typename T>
+__device__ __forceinline__ void silu_bwd_one(T dh, T e, T g, T& h, T& de, T& dg) {
+  const float e32 = to_f32(e);
+  const float se = sigmoid_f32(e32);
+  const float ese = e32 * se;
+  const T f = from_f32<T>(ese);
+  h = mul_t(f, g);
+  const T df = mul_t(dh, g);
+  dg = mul_t(f, dh);
+  de = from_f32<T>(to_f32(df) * se * (1.f + e32 - ese));
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(EW_THREADS)
+silu_fwd_kernel(const T* __restrict__ e, const T* __restrict__ g, T* __restrict__ h, int64_t n) {
+  constexpr int V = VEC ? Vec<T>::N : 1;
+  const int64_t nv = n / V;
+  for (int64_t i = (int64_t)blockIdx.x * EW_THREADS + threadIdx.x; i < nv; i += (int64_t)gridDim.x * EW_THREADS) {
+    if constexpr (VEC) {
+      const Vec<T> ve = load_vec(e + i * V), vg = load_vec(g + i * V);
+      Vec<T> vh;
+#pragma unroll
+      for (int j = 0; j < V; ++j) vh.v[j] = silu_fwd_one(ve.v[j], vg.v[j]);
+      store_vec(h + i * V, vh);
+    } else {
+      h[i] = silu_fwd_one(e[i], g[i]);
+    }
+  }
+  if constexpr (VEC) {  // tail
+    const int64_t t = nv * V + (int64_t)blockIdx.x * EW_THREADS + threadIdx.x;
+    if (t < n) h[t] = silu_fwd_one(e[t], g[t]);
+  }
+}
+
+// dh/e/g may alias h/de/dg (in-place form), so no __restrict__ here.
+template <typename T, bool VEC, bool WRITE_H>
+__global__ void __launch_bounds__(EW_THREADS)
+silu_bwd_kernel(const T* dh, const T* e, const T* g, T* h, T* de, T* dg, int64_t n) {
+  constexpr int V = VEC ? Vec<T>::N : 1;
+  const int64_t nv = n / V;
+  for (int64_t i = (int64_t)blockIdx.x * EW_THREADS + threadIdx.x; i < nv; i += (int64_t)gridDim.x * EW_THREADS) {
+    if constexpr (VEC) {
+      const Vec<T> vdh = load_vec(dh + i * V), ve = load_vec(e + i * V), vg = load_vec(g + i * V);
+      Vec<T> vh, vde, vdg;
+#pragma unroll
+      for (int j = 0; j < V; ++j) silu_bwd_one(vdh.v[j], ve.v[j], vg.v[j], vh.v[j], vde.v[j], vdg.v[j]);
+      if constexpr (WRITE_H) store_vec(h + i * V, vh);
+      store_vec(de + i * V, vde);
+      store_vec(dg + i * V, vdg);
+    } else {
+      T oh, ode, odg;
+      silu_bwd_one(dh[i], e[i], g[i], oh, ode, odg);
+      if constexpr (WRITE_H) h[i] = oh;
+      de[i] = ode;
+      dg[i] = odg;
+    }
+  }
+  if constexpr (VEC) {
+    const int64_t t = nv * V + (int64_t)blockIdx.x * EW_THREADS + threadIdx.x;
+    if (t < n) {
+      T oh, ode, odg;
+      silu_bwd_one(dh[t], e[t], g[t], oh, ode, odg);
+      if constexpr (WRITE_H) h[t] = oh;
+      de[t] = ode;
+      dg[t] = odg;
+    }
+  }
+}
+
+// NF4 decode, 16 weights (8 packed bytes) per thread iteration.
+// Element 2j is the high nibble of byte j, element 2j+1 the low nibble
+// (qwen3_moe_fused/grouped_gemm/forward_4bit.py:99-104).
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS)
+nf4_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ code,
+                   const float* __restrict__ absmax, int bs_shift, T* __restrict__ out,
+                   int64_t n_elems, bool vec_ok) {
+  __shared__ float tbl[16];
+  if (threadIdx.x < 16) tbl[threadIdx.x] = code[threadIdx.x];
+  __syncthreads();
+  const int64_t ngroups = vec_ok ? n_elems / 16 : 0;
+  for (int64_t gi = (int64_t)blockIdx.x * EW_THREADS + threadIdx.x; gi < ngroups; gi += (int64_t)gridDim.x * EW_THREADS) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(packed + gi * 8);
+    const int64_t base = gi * 16;
+    const uint32_t words[2] = {raw.x, raw.y};
+    T vals[16];
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      const uint32_t byte = (words[b >> 2] >> ((b & 3) * 8)) & 0xffu;
+      const float a0 = absmax[(base + 2 * b) >> bs_shift];
+      const float a1 = absmax[(base + 2 * b + 1) >> bs_shift];
+      vals[2 * b] = from_f32<T>(tbl[byte >> 4] * a0);
+      vals[2 * b + 1] = from_f32<T>(tbl[byte & 15] * a1);
+    }
+    constexpr int NV = 16 * sizeof(T) / 16;
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+      reinterpret_cast<uint4*>(out + base)[v] = reinterpret_cast<const uint4*>(vals)[v];
+  }
+  // scalar remainder (or everything when the buffers are not 16-byte aligned)
+  const int64_t start = ngroups * 16;
+  for (int64_t i = start + (int64_t)blockIdx.x * EW_THREADS + threadIdx.x; i < n_elems; i += (int64_t)gridDim.x * EW_THREADS) {
+    const uint8_t byte = packed[i >> 1];
+    const int nib = (i & 1) ? (byte & 15) : (byte >> 4);
+    out[i] = from_f32<T>(tbl[nib] * absmax[i >> bs_shift]);
+  }
+}
+
+// out[j,:] = hidden[sort_idx[j] / k, :].  One CTA walks whole rows.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(EW_THREADS)
+gather_rows_kernel(const T* __restrict__ hidden, const int32_t* __restrict__ sort_idx, int k,
+                   T* __restrict__ out, int64_t rows, int H) {
+  constexpr int V = VEC ? Vec<T>::N : 1;
+  const int hv = H / V;
+  for (int64_t j = blockIdx.x; j < rows; j += gridDim.x) {
+    const int64_t src = (int64_t)(sort_idx[j] / k);
+    const T* s = hidden + src * H;
+    T* d = out + j * H;
+    for (int c = threadIdx.x; c < hv; c += EW_THREADS) {
+      if constexpr (VEC) store_vec(d + c * V, load_vec(s + c * V));
+      else d[c] = s[c];
+    }
+  }
+}
+
+// out[t,:] = T( sum_j f32(weights[t,j]) * f32(y[inv_sort_idx[t*k+j],:]) )
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(EW_THREADS)
+combine_kernel(const T* __restrict__ y, const int32_t* __restrict__ inv_sort_idx,
+               const T* __restrict__ weights, T* __restrict__ out, int64_t tokens, int k, int H) {
+  constexpr int V = VEC ? Vec<T>::N : 1;
+  const int hv = H / V;
+  for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+    for (int c = threadIdx.x; c < hv; c += EW_THREADS) {
+      float acc[V];
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = 0.f;
+      for (int j = 0; j < k; ++j) {
+        const int64_t src = inv_sort_idx[t * k + j];
+        const float wj = to_f32(weights[t * k + j]);
+        if constexpr (VEC) {
+          const Vec<T> v = load_vec(y + src * H + c * V);
+#pragma unroll
+          for (int i = 0; i < V; ++i) acc[i] = fmaf(wj, to_f32(v.v[i]), acc[i]);
+        } else {
+          acc[0] = fmaf(wj, to_f32(y[src * H + c]), acc[0]);
+        }
+      }
+      if constexpr (VEC) {
+        Vec<T> o;
+#pragma unroll
+        for (int i = 0; i < V; ++i) o.v[i] = from_f32<T>(acc[i]);
+        store_vec(out + t * H + c * V, o);
+      } else {
+        out[t * H + c] = from_f32<T>(acc[0]);
+      }
+    }
+  }
+}
+
+static inline int ilog2_exact(int v) {
+  if (v <= 0 || (v & (v - 1)) != 0) return -1;
+  int s = 0;
+  while ((1 << s) < v) ++s;
+  return s;
+}
+
+}  // namespace moe
+
+using namespace moe;
+
+MOE_API int moe_silu_mul_fwd(const void* e, const void* g, void* h, int64_t n, int dtype, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (n < 0) return MOE_ERR_SHAPE;
+  if (n == 0) return MOE_OK;
+  if (!e || !g || !h) return MOE_ERR_NULL;
+  const bool vec = aligned16(e) && aligned16(g) && aligned16(h);
+  MOE_DISPATCH_FLOAT(dtype, T, {
+    const int64_t items = vec ? (n + Vec<T>::N - 1) / Vec<T>::N : n;
+    if (vec) silu_fwd_kernel<T, true><<<ew_grid(items), EW_THREADS, 0, stream>>>((const T*)e, (const T*)g, (T*)h, n);
+    else silu_fwd_kernel<T, false><<<ew_grid(items), EW_THREADS, 0, stream>>>((const T*)e, (const T*)g, (T*)h, n);
+  });
+  return launch_status();
+}
+
+static int silu_bwd_impl(const void* dh, const void* e, const void* g, void* h, void* de, void* dg,
+                         int64_t n, int dtype, bool write_h, cudaStream_t stream) {
+  if (n < 0) return MOE_ERR_SHAPE;
+  if (n == 0) return MOE_OK;
+  if (!dh || !e || !g || !de || !dg || (write_h && !h)) return MOE_ERR_NULL;
+  const bool vec = aligned16(dh) && aligned16(e) && aligned16(g) && aligned16(de) && aligned16(dg) && (!write_h || aligned16(h));
+  MOE_DISPATCH_FLOAT(dtype, T, {
+    const int64_t items = vec ? (n + Vec<T>::N - 1) / Vec<T>::N : n;
+    const int grid = ew_grid(items);
+    // The tail of the vector form is handled by the first CTAs; it needs at least
+    // Vec::N-1 threads in total, which one CTA always has.
+    if (vec && write_h) silu_bwd_kernel<T, true, true><<<grid, EW_THREADS, 0, stream>>>((const T*)dh, (const T*)e, (const T*)g, (T*)h, (T*)de, (T*)dg, n);
+    else if (vec) silu_bwd_kernel<T, true, false><<<grid, EW_THREADS, 0, stream>>>((const T*)dh, (const T*)e, (const T*)g, (T*)h, (T*)de, (T*)dg, n);
+    else if (write_h) silu_bwd_kernel<T, false, true><<<grid, EW_THREADS, 0, stream>>>((const T*)dh, (const T*)e, (const T*)g, (T*)h, (T*)de, (T*)dg, n);
+    else silu_bwd_kernel<T, false, false><<<grid, EW_THREADS, 0, stream>>>((const T*)dh, (const T*)e, (const T*)g, (T*)h, (T*)de, (T*)dg, n);
+  });
+  return launch_status();
+}
+
+MOE_API int moe_silu_mul_bwd(const void* dh, const void* e, const void* g, void* de, void* dg,
+                             int64_t n, int dtype, void* stream) {
+  return silu_bwd_impl(dh, e, g, nullptr, de, dg, n, dtype, false, (cudaStream_t)stream);
+}
+
+MOE_API int moe_silu_mul_bwd_inplace(void* dh, void* e, void* g, int64_t n, int dtype, void* stream) {
+  // (dh, e, g) <- (h, de, dg): every element is read before it is overwritten by the
+  // same thread, so aliasing inputs and outputs is safe.
+  return silu_bwd_impl(dh, e, g, dh, e, g, n, dtype, true, (cudaStream_t)stream);
+}
+
+MOE_API int moe_nf4_dequant(const uint8_t* packed, const float* code, const float* absmax, int blocksize,
+                            void* out, int64_t n_elems, int dtype_out, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const int shift = ilog2_exact(blocksize);
+  if (shift < 0 || n_elems < 0 || (n_elems & 1)) return MOE_ERR_SHAPE;
+  if (n_elems == 0) return MOE_OK;
+  if (!packed || !code || !absmax || !out) return MOE_ERR_NULL;
+  const bool vec_ok = (((uintptr_t)packed & 7) == 0) && aligned16(out);
+  MOE_DISPATCH_FLOAT(dtype_out, T, {
+    nf4_dequant_kernel<T><<<ew_grid((n_elems + 15) / 16), EW_THREADS, 0, stream>>>(
+        packed, code, absmax, shift, (T*)out, n_elems, vec_ok);
+  });
+  return launch_status();
+}
+
+MOE_API int moe_gather_rows(const void* hidden, const int32_t* sort_idx, int k, void* out,
+                            int64_t rows, int H, int dtype, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (rows < 0 || H < 0 || k <= 0) return MOE_ERR_SHAPE;
+  if (rows == 0 || H == 0) return MOE_OK;
+  if (!hidden || !sort_idx || !out) return MOE_ERR_NULL;
+  const int64_t g64 = rows < (int64_t)sm_count() * 16 ? rows : (int64_t)sm_count() * 16;
+  const int grid = (int)g64;
+  MOE_DISPATCH_FLOAT(dtype, T, {
+    const bool vec = aligned16(hidden) && aligned16(out) && (H % Vec<T>::N == 0);
+    if (vec) gather_rows_kernel<T, true><<<grid, EW_THREADS, 0, stream>>>((const T*)hidden, sort_idx, k, (T*)out, rows, H);
+    else gather_rows_kernel<T, false><<<grid, EW_THREADS, 0, stream>>>((const T*)hidden, sort_idx, k, (T*)out, rows, H);
+  });
+  return launch_status();
+}
+
+MOE_API int moe_combine(const void* y, const int32_t* inv_sort_idx, const void* weights, void* out,
+                        int64_t T_, int k, int H, int dtype, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (T_ < 0 || H < 0 || k <= 0) return MOE_ERR_SHAPE;
+  if (T_ == 0 || H == 0) return MOE_OK;
+  if (!y || !inv_sort_idx || !weights || !out) return MOE_ERR_NULL;
+  const int64_t g64 = T_ < (int64_t)sm_count() * 16 ? T_ : (int64_t)sm_count() * 16;
+  const int grid = (int)g64;
+  MOE_DISPATCH_FLOAT(dtype, T, {
+    const bool vec = aligned16(y) && aligned16(out) && (H % Vec<T>::N == 0);
+    if (vec) combine_kernel<T, true><<<grid, EW_THREADS, 0, stream>>>((const T*)y, inv_sort_idx, (const T*)weights, (T*)out, T_, k, H);
+    else combine_kernel<T, false><<<grid, EW_THREADS, 0, stream>>>((const T*)y, inv_sort_idx, (const T*)weights, (T*)out, T_, k, H);
+  });
+  return launch_status();
+}

@@ -1,0 +1,120 @@
+// Router: fp32 softmax over the E logits of a token, top-k by (probability descending,
+// expert id ascending), optional renormalisation over the k winners, cast to the
+// activation dtype.  One warp per token; every lane keeps E/32 probabilities in
+// registers (expert id = lane + 32*i, so logits are read with coalesced accesses) and
+// the k arg-max rounds are warp-shuffle reductions.
+// Stands in for the softmax / topk / divide / cast sequence at
+// qwen3_moe_fused/modular_qwen3_moe_fused.py:87-93.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace moe {
+
+constexpr int RT_WARPS = 8;
+
+template <typename TL, typename TW, int NPL>
+__global__ void __launch_bounds__(RT_WARPS * 32)
+router_kernel(const TL* __restrict__ logits, int64_t T, int E, int k, int norm,
+              TW* __restrict__ weights, int64_t* __restrict__ experts) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = (int64_t)blockIdx.x * RT_WARPS + (threadIdx.x >> 5);
+  const int64_t warp_stride = (int64_t)gridDim.x * RT_WARPS;
+  for (int64_t t = warp_global; t < T; t += warp_stride) {
+    const TL* row = logits + t * E;
+    float p[NPL];
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int e = lane + 32 * i;
+      p[i] = e < E ? to_f32(row[e]) : -CUDART_INF_F;
+      mx = fmaxf(mx, p[i]);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int e = lane + 32 * i;
+      p[i] = e < E ? expf(p[i] - mx) : 0.f;
+      sum += p[i];
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int e = lane + 32 * i;
+      p[i] = e < E ? p[i] * inv : -1.f;  // -1 never wins against a probability
+    }
+    // k rounds of arg-max.
+    float top_sum = 0.f;
+    float my_w = 0.f;
+    int my_e = 0;
+    for (int r = 0; r < k; ++r) {
+      float bv = -2.f;
+      int be = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) {
+        const int e = lane + 32 * i;
+        if (p[i] > bv) { bv = p[i]; be = e; }  // ascending e inside a lane: first hit wins
+      }
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
+        const int oe = __shfl_xor_sync(0xffffffffu, be, d);
+        if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+      }
+      // remove the winner
+#pragma unroll
+      for (int i = 0; i < NPL; ++i)
+        if (lane + 32 * i == be) p[i] = -1.f;
+      top_sum += bv;
+      if (r == lane) { my_w = bv; my_e = be; }  // lane r keeps the r-th winner (k <= 32)
+    }
+    if (lane < k) {
+      experts[t * k + lane] = (int64_t)my_e;
+      // Same operation as the reference: each probability divided by the winners' sum.
+      weights[t * k + lane] = from_f32<TW>(norm ? my_w / top_sum : my_w);
+    }
+  }
+}
+
+// k is limited to 32 (one winner per lane); Qwen3-MoE uses 8.
+
+template <typename TL, typename TW>
+static int launch_router(const void* logits, int64_t T, int E, int k, int norm, void* weights,
+                         int64_t* experts, cudaStream_t stream) {
+  const int64_t want = (T + RT_WARPS - 1) / RT_WARPS;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  const int grid = (int)(want < cap ? want : cap);
+  const int npl = (E + 31) / 32;
+#define MOE_RT_CASE(NPL)                                                                           \
+  router_kernel<TL, TW, NPL><<<grid, RT_WARPS * 32, 0, stream>>>((const TL*)logits, T, E, k, norm, \
+                                                                 (TW*)weights, experts)
+  if (npl <= 1) MOE_RT_CASE(1);
+  else if (npl <= 2) MOE_RT_CASE(2);
+  else if (npl <= 4) MOE_RT_CASE(4);
+  else if (npl <= 8) MOE_RT_CASE(8);
+  else if (npl <= 16) MOE_RT_CASE(16);
+  else MOE_RT_CASE(32);
+#undef MOE_RT_CASE
+  return launch_status();
+}
+
+}  // namespace moe
+
+using namespace moe;
+
+MOE_API int moe_router_softmax_topk(const void* logits, int dtype_logits, int64_t T, int E, int k,
+                                    int norm_topk, void* weights, int dtype_w, int64_t* experts,
+                                    void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (T < 0 || E <= 0 || E > 1024 || k <= 0 || k > E || k > 32) return MOE_ERR_SHAPE;
+  if (T == 0) return MOE_OK;
+  if (!logits || !weights || !experts) return MOE_ERR_NULL;
+  MOE_DISPATCH_FLOAT(dtype_logits, TL, {
+    MOE_DISPATCH_FLOAT(dtype_w, TW, { return launch_router<TL, TW>(logits, T, E, k, norm_topk, weights, experts, stream); });
+  });
+  return MOE_ERR_DTYPE;
+}

@@ -1,0 +1,916 @@
+// Tensor-core grouped GEMMs for sm_100a: tcgen05.mma with fp32 accumulators in TMEM,
+// operands staged by TMA into 128-byte-swizzled shared memory, warp-specialised
+// persistent CTAs (one per SM) that walk a tile list derived on the device from m_sizes.
+//
+//   tc_fwd_kernel<BN, false> : y[m,n] = sum_k x[m,k] w[e,n,k]   (B operand K-major)
+//   tc_fwd_kernel<BN, true>  : y[m,n] = sum_k x[m,k] w[e,k,n]   (B operand MN-major; dX)
+//   tc_dw_kernel             : w[e,n,k] = sum_m y[m,n] x[m,k]   (both operands MN-major)
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
+// warps 2..5 = epilogue (TMEM -> registers -> global).  The accumulator is double
+// buffered in TMEM so the epilogue of tile i overlaps the main loop of tile i+1.
+// No tile ever crosses an expert boundary on the store side: an M tile starts at a group's
+// first row and rows past the group's end are computed but not stored.
+#include "tc_common.cuh"
+
+namespace moe {
+namespace tc {
+
+constexpr int BM = 128;          // rows of the accumulator tile (UMMA M)
+constexpr int BK = 64;           // 16-bit elements per 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int MAX_E = 1024;      // group tables live in shared memory
+constexpr int SMEM_LIMIT = 232448;  // 227 KB opt-in maximum per CTA
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
+
+struct GemmParams {
+  const void* m_sizes;
+  void* out;
+  int64_t M;
+  int N, K, E;
+  int ms64;
+  int dtype_out;  // MOE_F32 / MOE_BF16 / MOE_F16
+  uint32_t idesc;
+};
+
+struct Control {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int total_m_tiles;
+  int pad;
+};
+
+enum WaitCode { W_EMPTY = 1, W_FULL = 2, W_TMEM_EMPTY = 3, W_TMEM_FULL = 4 };
+
+// Fills row_start[0..E] (first row of each group, saturated at M) and mt_start[0..E]
+// (number of BM-row tiles before each group).  Called by every thread of the CTA.
+__device__ void build_group_tables(const void* m_sizes, int ms64, int E, int64_t M, int tile_rows,
+                                   int* row_start, int* mt_start) {
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int64_t v = load_index(m_sizes, ms64, e);
+    v = v < 0 ? 0 : (v > M ? M : v);
+    row_start[e + 1] = (int)v;  // raw size for now
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int64_t carry_rows = 0;
+    int carry_tiles = 0;
+    if (lane == 0) { row_start[0] = 0; mt_start[0] = 0; }
+    for (int base = 0; base < E; base += 32) {
+      const int e = base + lane;
+      const int64_t v = e < E ? row_start[e + 1] : 0;
+      int64_t incl = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int64_t o = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += o;
+      }
+      int64_t end = carry_rows + incl;
+      int64_t begin = end - v;
+      end = end > M ? M : end;
+      begin = begin > M ? M : begin;
+      const int tiles = (int)((end - begin + tile_rows - 1) / tile_rows);
+      int tincl = tiles;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, tincl, d);
+        if (lane >= d) tincl += o;
+      }
+      if (e < E) {
+        row_start[e + 1] = (int)end;
+        mt_start[e + 1] = carry_tiles + tincl;
+      }
+      carry_rows += __shfl_sync(0xffffffffu, incl, 31);
+      carry_tiles += __shfl_sync(0xffffffffu, tincl, 31);
+    }
+  }
+  __syncthreads();
+}
+
+// Largest e with table[e] <= q (table is non-decreasing, table[0] = 0, q < table[E]).
+__device__ __forceinline__ int find_group(const int* table, int E, int q) {
+  int lo = 0, hi = E;  // invariant: table[lo] <= q < table[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (table[mid] <= q) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+template <typename T>
+__device__ __forceinline__ void store_row_chunk(T* dst, const uint32_t (&acc)[32], int ncols, bool vec);
+
+template <>
+__device__ __forceinline__ void store_row_chunk<float>(float* dst, const uint32_t (&acc)[32], int ncols, bool vec) {
+  if (vec && ncols == 32) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      reinterpret_cast<uint4*>(dst)[i] = make_uint4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < ncols) dst[i] = __uint_as_float(acc[i]);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <typename T>
+__device__ __forceinline__ void store_row_chunk16(T* dst, const uint32_t (&acc)[32], int ncols, bool vec) {
+  if (vec && ncols == 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 v;
+      v.x = pack2<T>(__uint_as_float(acc[8 * i + 0]), __uint_as_float(acc[8 * i + 1]));
+      v.y = pack2<T>(__uint_as_float(acc[8 * i + 2]), __uint_as_float(acc[8 * i + 3]));
+      v.z = pack2<T>(__uint_as_float(acc[8 * i + 4]), __uint_as_float(acc[8 * i + 5]));
+      v.w = pack2<T>(__uint_as_float(acc[8 * i + 6]), __uint_as_float(acc[8 * i + 7]));
+      reinterpret_cast<uint4*>(dst)[i] = v;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < ncols) dst[i] = from_f32<T>(__uint_as_float(acc[i]));
+  }
+}
+template <>
+__device__ __forceinline__ void store_row_chunk<__nv_bfloat16>(__nv_bfloat16* dst, const uint32_t (&acc)[32], int ncols, bool vec) {
+  store_row_chunk16(dst, acc, ncols, vec);
+}
+template <>
+__device__ __forceinline__ void store_row_chunk<__half>(__half* dst, const uint32_t (&acc)[32], int ncols, bool vec) {
+  store_row_chunk16(dst, acc, ncols, vec);
+}
+
+// Writes 32 accumulator columns of one output row.  `dst_elem` is the element offset of the
+// first column in the output tensor.
+__device__ __forceinline__ void store_acc(void* out, int dtype_out, int64_t dst_elem, const uint32_t (&acc)[32], int ncols, bool vec) {
+  if (dtype_out == MOE_BF16) store_row_chunk((__nv_bfloat16*)out + dst_elem, acc, ncols, vec);
+  else if (dtype_out == MOE_F16) store_row_chunk((__half*)out + dst_elem, acc, ncols, vec);
+  else store_row_chunk((float*)out + dst_elem, acc, ncols, vec);
+}
+
+// ---------------------------------------------------------------------------------------
+// Forward / dX
+// ---------------------------------------------------------------------------------------
+template <int BN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+              const GemmParams p) {
+  constexpr int B_STAGE_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  constexpr int STAGES = (BN == 256) ? 4 : 6;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators (256 or 512 columns)
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Control* ctl = reinterpret_cast<Control*>(smem + STAGES * STAGE_BYTES);
+  int* row_start = reinterpret_cast<int*>(ctl + 1);
+  int* mt_start = row_start + (p.E + 1);
+  volatile int* abort_flag = &ctl->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 4); }
+    ctl->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  build_group_tables(p.m_sizes, p.ms64, p.E, p.M, BM, row_start, mt_start);  // contains __syncthreads
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int k_blocks = (p.K + BK - 1) / BK;
+  const int64_t total_tiles = (int64_t)mt_start[p.E] * n_tiles;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int q = (int)(tile / n_tiles);
+        const int e = find_group(mt_start, p.E, q);
+        const int mt_e = mt_start[e + 1] - mt_start[e];
+        const int j = (int)(tile - (int64_t)mt_start[e] * n_tiles);
+        const int m0 = row_start[e] + (j % mt_e) * BM;
+        const int n0 = (j / mt_e) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, W_EMPTY)) { ok = false; break; }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
+          mbar_expect_tx(&ctl->full[s], STAGE_BYTES);
+          tma_load_2d(sa, &tmap_a, &ctl->full[s], kb * BK, m0);
+          if constexpr (!B_MN) {
+            tma_load_3d(sb, &tmap_b, &ctl->full[s], kb * BK, n0, e);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_3d(sb + c * (BK * 128), &tmap_b, &ctl->full[s], n0 + c * 64, kb * BK, e);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (elect_one()) {
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++acc_it) {
+        const uint32_t acc = acc_it & 1;
+        const uint32_t acc_ph = (acc_it >> 1) & 1;
+        if (!mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1, abort_flag, W_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&ctl->full[s], ph, abort_flag, W_FULL)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          const uint64_t da = make_smem_desc(sa, 16, 1024);
+          const uint64_t db = B_MN ? make_smem_desc(sb, BK * 128, 1024) : make_smem_desc(sb, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: 16 elements = 32 bytes inside the swizzle row; MN-major: 16 rows of 128 B.
+            const uint64_t a_adv = (uint64_t)((k * UMMA_K * 2) >> 4);
+            const uint64_t b_adv = B_MN ? (uint64_t)((k * UMMA_K * 128) >> 4) : a_adv;
+            umma_f16(d_tmem, da + a_adv, db + b_adv, p.idesc, (kb | k) != 0);
+          }
+          umma_commit(&ctl->empty[s]);  // frees the stage when these MMAs have read it
+        }
+        if (ok) umma_commit(&ctl->tmem_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, +32)
+    const int row_in_tile = quarter * 32 + lane;
+    const bool vec = ((p.N * (int)dtype_size(p.dtype_out)) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++acc_it) {
+      const int q = (int)(tile / n_tiles);
+      const int e = find_group(mt_start, p.E, q);
+      const int mt_e = mt_start[e + 1] - mt_start[e];
+      const int j = (int)(tile - (int64_t)mt_start[e] * n_tiles);
+      const int m0 = row_start[e] + (j % mt_e) * BM;
+      const int n0 = (j / mt_e) * BN;
+      const int64_t grow = (int64_t)m0 + row_in_tile;
+      const bool row_ok = grow < row_start[e + 1] && grow < p.M;
+      const uint32_t acc = acc_it & 1;
+      const uint32_t acc_ph = (acc_it >> 1) & 1;
+      if (!mbar_wait(&ctl->tmem_full[acc], acc_ph, abort_flag, W_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        if (n0 + c >= p.N) break;  // warp-uniform
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c, v);
+        tmem_ld_wait();
+        if (row_ok) {
+          const int ncols = min(32, p.N - (n0 + c));
+          store_acc(p.out, p.dtype_out, grow * p.N + n0 + c, v, ncols, vec);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->tmem_empty[acc]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// dW: one work item = (expert, 128-wide slice of N, BN-wide slice of K); the reduction
+// runs over the expert's rows in blocks of 64.  Rows of the last block that belong to the
+// next expert are zeroed in shared memory before the MMA reads them.  Work items are
+// ordered by decreasing group size and dealt to the CTAs in snake order, which keeps the
+// per-CTA totals balanced under skewed routing without any global scheduler state.
+// ---------------------------------------------------------------------------------------
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+tc_dw_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_x,
+             const GemmParams p) {
+  constexpr int B_STAGE_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  constexpr int STAGES = (BN == 256) ? 4 : 6;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  constexpr int CHUNK_BYTES = BK * 128;  // one 64-wide MN chunk: 64 reduction rows x 128 B
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Control* ctl = reinterpret_cast<Control*>(smem + STAGES * STAGE_BYTES);
+  int* row_start = reinterpret_cast<int*>(ctl + 1);
+  int* order = row_start + (p.E + 1);  // order[r] = expert with the r-th largest group
+  volatile int* abort_flag = &ctl->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 4); }
+    ctl->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_dy);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  build_group_tables(p.m_sizes, p.ms64, p.E, p.M, BK, row_start, order);  // `order` used as scratch here
+  // rank by (size descending, expert ascending)
+  __syncthreads();
+  for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+    const int me = row_start[e + 1] - row_start[e];
+    int rank = 0;
+    for (int o = 0; o < p.E; ++o) {
+      const int mo = row_start[o + 1] - row_start[o];
+      rank += (mo > me) || (mo == me && o < e);
+    }
+    // written after everybody has finished reading `order` as scratch (no reader: the tile
+    // prefix is not used by this kernel), so a plain store is fine
+    order[p.E + 1 + rank] = e;
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const int* sorted = order + p.E + 1;
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  const int n_tiles = (p.N + BM - 1) / BM;   // slices of the output's row dimension (N)
+  const int k_tiles = (p.K + BN - 1) / BN;   // slices of the output's column dimension (K)
+  const int per_expert = n_tiles * k_tiles;
+  const int64_t total_items = (int64_t)p.E * per_expert;
+  const int G = gridDim.x;
+
+  // item handled by this CTA in round r (snake order)
+  auto item_of = [&](int64_t r) -> int64_t {
+    return r * G + ((r & 1) ? (G - 1 - (int)blockIdx.x) : (int)blockIdx.x);
+  };
+  const int64_t rounds = (total_items + G - 1) / G;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int64_t r = 0; r < rounds && ok; ++r) {
+        const int64_t item = item_of(r);
+        if (item >= total_items) continue;
+        const int e = sorted[item / per_expert];
+        const int j = (int)(item % per_expert);
+        const int n0 = (j % n_tiles) * BM;
+        const int k0 = (j / n_tiles) * BN;
+        const int r0 = row_start[e];
+        const int m_blocks = (row_start[e + 1] - r0 + BK - 1) / BK;
+        for (int mb = 0; mb < m_blocks; ++mb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, W_EMPTY)) { ok = false; break; }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
+          mbar_expect_tx(&ctl->full[s], STAGE_BYTES);
+#pragma unroll
+          for (int c = 0; c < BM / 64; ++c)
+            tma_load_2d(sa + c * CHUNK_BYTES, &tmap_dy, &ctl->full[s], n0 + c * 64, r0 + mb * BK);
+#pragma unroll
+          for (int c = 0; c < BN / 64; ++c)
+            tma_load_2d(sb + c * CHUNK_BYTES, &tmap_x, &ctl->full[s], k0 + c * 64, r0 + mb * BK);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // Whole warp stays converged: lanes share the waits and the tail fix-up, lane 0 issues.
+    uint32_t it = 0, acc_it = 0;
+    bool ok = true;
+    for (int64_t r = 0; r < rounds && ok; ++r) {
+      const int64_t item = item_of(r);
+      if (item >= total_items) continue;
+      const int e = sorted[item / per_expert];
+      const int rows = row_start[e + 1] - row_start[e];
+      const int m_blocks = (rows + BK - 1) / BK;
+      if (m_blocks == 0) continue;  // empty expert: the epilogue writes zeros on its own
+      const uint32_t acc = acc_it & 1;
+      const uint32_t acc_ph = (acc_it >> 1) & 1;
+      if (!mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1, abort_flag, W_TMEM_EMPTY)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (int mb = 0; mb < m_blocks; ++mb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(&ctl->full[s], ph, abort_flag, W_FULL)) { ok = false; break; }
+        tc_fence_after_sync();
+        uint8_t* sa_ptr = smem + s * STAGE_BYTES;
+        const int valid = rows - mb * BK;  // reduction rows of this block that belong to e
+        if (valid < BK) {
+          // zero rows [valid, 64) of every 64-wide chunk of both operands (128 B per row)
+          constexpr int CHUNKS = (BM + BN) / 64;
+          const int bad = BK - valid;
+          for (int i = lane; i < CHUNKS * bad * 8; i += 32) {
+            const int c = i / (bad * 8);
+            const int rem = i % (bad * 8);
+            const int row = valid + rem / 8;
+            *reinterpret_cast<uint4*>(sa_ptr + c * CHUNK_BYTES + row * 128 + (rem % 8) * 16) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
+        }
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t sa = smem_u32(sa_ptr);
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          const uint64_t da = make_smem_desc(sa, CHUNK_BYTES, 1024);
+          const uint64_t db = make_smem_desc(sb, CHUNK_BYTES, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adv = (uint64_t)((k * UMMA_K * 128) >> 4);
+            umma_f16(d_tmem, da + adv, db + adv, p.idesc, (mb | k) != 0);
+          }
+          umma_commit(&ctl->empty[s]);
+        }
+        __syncwarp();
+      }
+      if (ok && lane == 0) umma_commit(&ctl->tmem_full[acc]);
+      __syncwarp();
+      ++acc_it;
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const bool vec = ((p.K * (int)dtype_size(p.dtype_out)) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int64_t r = 0; r < rounds && ok; ++r) {
+      const int64_t item = item_of(r);
+      if (item >= total_items) continue;
+      const int e = sorted[item / per_expert];
+      const int j = (int)(item % per_expert);
+      const int n0 = (j % n_tiles) * BM;
+      const int k0 = (j / n_tiles) * BN;
+      const int rows = row_start[e + 1] - row_start[e];
+      const int n = n0 + row_in_tile;
+      const bool row_ok = n < p.N;
+      const int64_t out_row = ((int64_t)e * p.N + n) * p.K;
+      if (rows == 0) {
+        uint32_t z[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) z[i] = 0;
+        for (int c = 0; c < BN; c += 32) {
+          if (k0 + c >= p.K) break;
+          if (row_ok) store_acc(p.out, p.dtype_out, out_row + k0 + c, z, min(32, p.K - (k0 + c)), vec);
+        }
+        continue;
+      }
+      const uint32_t acc = acc_it & 1;
+      const uint32_t acc_ph = (acc_it >> 1) & 1;
+      if (!mbar_wait(&ctl->tmem_full[acc], acc_ph, abort_flag, W_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        if (k0 + c >= p.K) break;
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c, v);
+        tmem_ld_wait();
+        if (row_ok) store_acc(p.out, p.dtype_out, out_row + k0 + c, v, min(32, p.K - (k0 + c)), vec);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->tmem_empty[acc]);
+      ++acc_it;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Forward with the NF4 weight decoded into the B stage.
+// Per k-block the producer brings the activation tile (TMA, swizzled) and the packed
+// weight bytes of the 256 x 64 weight tile (TMA, 8 KB, linear) into shared memory; eight
+// decode warps turn the bytes into the swizzled 16-bit K-major B tile (one weight row per
+// thread: 32 packed bytes -> 64 values -> eight 16-byte chunks), publish it to the async
+// proxy and signal the MMA warp.  HBM sees 0.5 byte + 4/blocksize bytes per weight.
+// Extra warps: 6..13 = decode.
+// ---------------------------------------------------------------------------------------
+constexpr int NF4_THREADS = 448;
+constexpr int NF4_BN = 256;
+constexpr int NF4_STAGES = 3;
+constexpr int NF4_PACKED_BYTES = NF4_BN * (BK / 2);                               // 8 KB
+constexpr int NF4_STAGE_BYTES = A_STAGE_BYTES + NF4_BN * BK * 2 + NF4_PACKED_BYTES;  // 56 KB
+
+struct Nf4Params {
+  const float* code;
+  const float* absmax;
+  int shift;  // log2(blocksize), blocksize >= 64
+};
+
+struct Nf4Control {
+  uint64_t ready[8];  // decoded B tile published (8 warp arrivals)
+  float2 lut[256];    // byte -> (code[hi nibble], code[lo nibble])
+};
+
+template <bool IS_BF16>
+__global__ void __launch_bounds__(NF4_THREADS, 1)
+tc_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_q,
+                  const GemmParams p, const Nf4Params q) {
+  constexpr int BN = NF4_BN;
+  constexpr int STAGES = NF4_STAGES;
+  constexpr int STAGE_BYTES = NF4_STAGE_BYTES;
+  constexpr int B_OFF = A_STAGE_BYTES;
+  constexpr int Q_OFF = A_STAGE_BYTES + BN * BK * 2;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Control* ctl = reinterpret_cast<Control*>(smem + STAGES * STAGE_BYTES);
+  Nf4Control* nctl = reinterpret_cast<Nf4Control*>(ctl + 1);
+  int* row_start = reinterpret_cast<int*>(nctl + 1);
+  int* mt_start = row_start + (p.E + 1);
+  volatile int* abort_flag = &ctl->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&ctl->full[s], 1);
+      mbar_init(&ctl->empty[s], 1);
+      mbar_init(&nctl->ready[s], 8);
+    }
+    for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 4); }
+    ctl->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_q);
+  }
+  if (threadIdx.x < 256) nctl->lut[threadIdx.x] = make_float2(q.code[threadIdx.x >> 4], q.code[threadIdx.x & 15]);
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  build_group_tables(p.m_sizes, p.ms64, p.E, p.M, BM, row_start, mt_start);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int k_blocks = (p.K + BK - 1) / BK;
+  const int64_t total_tiles = (int64_t)mt_start[p.E] * n_tiles;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int qd = (int)(tile / n_tiles);
+        const int e = find_group(mt_start, p.E, qd);
+        const int mt_e = mt_start[e + 1] - mt_start[e];
+        const int j = (int)(tile - (int64_t)mt_start[e] * n_tiles);
+        const int m0 = row_start[e] + (j % mt_e) * BM;
+        const int n0 = (j / mt_e) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, W_EMPTY)) { ok = false; break; }
+          uint8_t* st = smem + s * STAGE_BYTES;
+          mbar_expect_tx(&ctl->full[s], A_STAGE_BYTES + NF4_PACKED_BYTES);
+          tma_load_2d(st, &tmap_a, &ctl->full[s], kb * BK, m0);
+          tma_load_3d(st + Q_OFF, &tmap_q, &ctl->full[s], kb * (BK / 2), n0, e);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++acc_it) {
+        const uint32_t acc = acc_it & 1;
+        const uint32_t acc_ph = (acc_it >> 1) & 1;
+        if (!mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1, abort_flag, W_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&ctl->full[s], ph, abort_flag, W_FULL)) { ok = false; break; }
+          if (!mbar_wait(&nctl->ready[s], ph, abort_flag, W_FULL)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t da = make_smem_desc(sa, 16, 1024);
+          const uint64_t db = make_smem_desc(sa + B_OFF, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adv = (uint64_t)((k * UMMA_K * 2) >> 4);
+            umma_f16(d_tmem, da + adv, db + adv, p.idesc, (kb | k) != 0);
+          }
+          umma_commit(&ctl->empty[s]);
+        }
+        if (ok) umma_commit(&ctl->tmem_full[acc]);
+      }
+    }
+  } else if (warp < 6) {
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const bool vec = ((p.N * (int)dtype_size(p.dtype_out)) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++acc_it) {
+      const int qd = (int)(tile / n_tiles);
+      const int e = find_group(mt_start, p.E, qd);
+      const int mt_e = mt_start[e + 1] - mt_start[e];
+      const int j = (int)(tile - (int64_t)mt_start[e] * n_tiles);
+      const int m0 = row_start[e] + (j % mt_e) * BM;
+      const int n0 = (j / mt_e) * BN;
+      const int64_t grow = (int64_t)m0 + row_in_tile;
+      const bool row_ok = grow < row_start[e + 1] && grow < p.M;
+      const uint32_t acc = acc_it & 1;
+      const uint32_t acc_ph = (acc_it >> 1) & 1;
+      if (!mbar_wait(&ctl->tmem_full[acc], acc_ph, abort_flag, W_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        if (n0 + c >= p.N) break;
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c, v);
+        tmem_ld_wait();
+        if (row_ok) store_acc(p.out, p.dtype_out, grow * p.N + n0 + c, v, min(32, p.N - (n0 + c)), vec);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->tmem_empty[acc]);
+    }
+  } else {
+    // ------------------------------ decode warps ------------------------------
+    const int t = threadIdx.x - 6 * 32;  // weight row inside the tile, 0..255
+    uint32_t it = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int qd = (int)(tile / n_tiles);
+      const int e = find_group(mt_start, p.E, qd);
+      const int mt_e = mt_start[e + 1] - mt_start[e];
+      const int j = (int)(tile - (int64_t)mt_start[e] * n_tiles);
+      const int n0 = (j / mt_e) * BN;
+      const int n = n0 + t;
+      const bool n_ok = n < p.N;
+      const int64_t row_flat = ((int64_t)e * p.N + (n_ok ? n : 0)) * p.K;
+      float am_next = n_ok ? __ldg(q.absmax + (row_flat >> q.shift)) : 0.f;
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        const float am = am_next;
+        if (kb + 1 < k_blocks && n_ok) am_next = __ldg(q.absmax + ((row_flat + (int64_t)(kb + 1) * BK) >> q.shift));
+        if (!mbar_wait(&ctl->full[s], ph, abort_flag, W_FULL)) { ok = false; break; }
+        uint8_t* st = smem + s * STAGE_BYTES;
+        const uint4* src = reinterpret_cast<const uint4*>(st + Q_OFF + t * (BK / 2));
+        uint8_t* dst_row = st + B_OFF + t * 128;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint4 raw = src[h];
+          const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {  // 4 bytes -> 8 values -> one 16-byte chunk
+            uint32_t outw[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              const float2 c = nctl->lut[(words[w] >> (8 * b)) & 0xffu];
+              if constexpr (IS_BF16) outw[b] = pack2<__nv_bfloat16>(c.x * am, c.y * am);
+              else outw[b] = pack2<__half>(c.x * am, c.y * am);
+            }
+            const int chunk = h * 4 + w;
+            *reinterpret_cast<uint4*>(dst_row + ((chunk ^ (t & 7)) << 4)) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&nctl->ready[s]);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess) return nullptr;
+    if (qres != cudaDriverEntryPointSuccess) return nullptr;
+    return (EncodeTiledFn)ptr;
+  }();
+  return fn;
+}
+
+// Tensor map over a dense 16-bit tensor viewed as (d2, d1, d0) with d0 contiguous.
+// Box = (b0 = 64 elements, b1 rows, 1).  rank 2 when d2 == 0.
+static int make_map(CUtensorMap* map, int dtype, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                    uint32_t b1) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return MOE_ERR_DEVICE;
+  const CUtensorMapDataType dt = dtype == MOE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const cuuint32_t rank = d2 ? 3 : 2;
+  cuuint64_t dims[3] = {d0, d1, d2 ? d2 : 1};
+  cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
+  cuuint32_t box[3] = {64, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(map, dt, rank, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MOE_OK : MOE_ERR_UNSUPPORTED;
+}
+
+template <int BN>
+static constexpr int smem_bytes_for(int E, int tables) {
+  return ((BN == 256) ? 4 : 6) * (A_STAGE_BYTES + BN * BK * 2) + (int)sizeof(Control) + tables * (E + 1) * 4 + 1024;
+}
+
+template <typename K>
+static int set_smem(K kernel, int bytes) {
+  return cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+}
+
+}  // namespace tc
+
+// Shapes the tensor-core kernels accept.  N, K are the output columns / contraction
+// length of the call (for dW: rows / columns of one expert's weight).
+bool tc_eligible(int which, const void* a, const void* b, const void* out, int64_t M, int N, int K, int E,
+                 int dtype_in, int dtype_out) {
+  if (dtype_in != MOE_BF16 && dtype_in != MOE_F16) return false;
+  if (!is_float_dtype(dtype_out)) return false;
+  if (E < 1 || E > tc::MAX_E || M < 1 || M > 0x7fffffffLL - 1024) return false;
+  if (N < 64 || K < 64 || (N % 8) || (K % 8)) return false;
+  if (((uintptr_t)a & 15) || ((uintptr_t)b & 15) || ((uintptr_t)out & 3)) return false;
+  (void)which;
+  return true;
+}
+
+// which: 0 forward, 1 dX, 2 dW (a = x, b = dy).
+int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes, int ms64, void* out,
+                    int64_t M, int N, int K, int E, int dtype_in, int dtype_out, cudaStream_t stream) {
+  using namespace tc;
+  GemmParams p;
+  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out;
+  const int fmt = dtype_in == MOE_BF16 ? 1 : 0;
+  const int grid = sm_count();
+  CUtensorMap ma, mb;
+  int st;
+  if (which == 0 || which == 1) {
+    const bool wide = N > 128;
+    const int bn = wide ? 256 : 128;
+    if ((st = make_map(&ma, dtype_in, a, (uint64_t)K, (uint64_t)M, 0, BM)) != MOE_OK) return st;
+    if (which == 0) st = make_map(&mb, dtype_in, b, (uint64_t)K, (uint64_t)N, (uint64_t)E, (uint32_t)bn);
+    else st = make_map(&mb, dtype_in, b, (uint64_t)N, (uint64_t)K, (uint64_t)E, BK);
+    if (st != MOE_OK) return st;
+    p.idesc = make_idesc(fmt, 0, which == 1, BM, bn);
+#define MOE_TC_LAUNCH(BN_, BMN_)                                                              \
+  do {                                                                                        \
+    const int bytes = smem_bytes_for<BN_>(E, 2);                                              \
+    if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;                                       \
+    if ((st = set_smem(tc_fwd_kernel<BN_, BMN_>, bytes)) != MOE_OK) return st;                \
+    tc_fwd_kernel<BN_, BMN_><<<grid, NUM_THREADS, bytes, stream>>>(ma, mb, p);                \
+  } while (0)
+    if (which == 0) { if (wide) MOE_TC_LAUNCH(256, false); else MOE_TC_LAUNCH(128, false); }
+    else { if (wide) MOE_TC_LAUNCH(256, true); else MOE_TC_LAUNCH(128, true); }
+#undef MOE_TC_LAUNCH
+    return launch_status();
+  }
+  // dW: accumulator rows = N (out_features), columns = K (in_features)
+  const bool wide = K > 128;
+  const int bn = wide ? 256 : 128;
+  if ((st = make_map(&ma, dtype_in, b, (uint64_t)N, (uint64_t)M, 0, BK)) != MOE_OK) return st;  // dy (M,N)
+  if ((st = make_map(&mb, dtype_in, a, (uint64_t)K, (uint64_t)M, 0, BK)) != MOE_OK) return st;  // x  (M,K)
+  p.idesc = make_idesc(fmt, 1, 1, BM, bn);
+  if (wide) {
+    const int bytes = smem_bytes_for<256>(E, 3);
+    if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
+    if ((st = set_smem(tc_dw_kernel<256>, bytes)) != MOE_OK) return st;
+    tc_dw_kernel<256><<<grid, NUM_THREADS, bytes, stream>>>(ma, mb, p);
+  } else {
+    const int bytes = smem_bytes_for<128>(E, 3);
+    if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
+    if ((st = set_smem(tc_dw_kernel<128>, bytes)) != MOE_OK) return st;
+    tc_dw_kernel<128><<<grid, NUM_THREADS, bytes, stream>>>(ma, mb, p);
+  }
+  return launch_status();
+}
+
+
+bool tc_nf4_eligible(const void* x, const void* packed, const void* absmax, const void* out, int64_t M, int N, int K,
+                     int E, int blocksize, int dtype_in, int dtype_out) {
+  if (!tc_eligible(0, x, packed, out, M, N, K, E, dtype_in, dtype_out)) return false;
+  if (blocksize < 64 || (K % 64) != 0) return false;  // one absmax per (row, 64-wide k-block); packed pitch % 16 B
+  if ((uintptr_t)absmax & 3) return false;
+  return true;
+}
+
+int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code, const float* absmax, int blocksize,
+                        const void* m_sizes, int ms64, void* out, int64_t M, int N, int K, int E,
+                        int dtype_in, int dtype_out, cudaStream_t stream) {
+  using namespace tc;
+  GemmParams p;
+  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out;
+  p.idesc = make_idesc(dtype_in == MOE_BF16 ? 1 : 0, 0, 0, BM, NF4_BN);
+  Nf4Params q;
+  q.code = code; q.absmax = absmax; q.shift = 0;
+  while ((1 << q.shift) < blocksize) ++q.shift;
+  CUtensorMap ma, mq;
+  int st;
+  if ((st = make_map(&ma, dtype_in, x, (uint64_t)K, (uint64_t)M, 0, BM)) != MOE_OK) return st;
+  {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return MOE_ERR_DEVICE;
+    cuuint64_t dims[3] = {(cuuint64_t)K / 2, (cuuint64_t)N, (cuuint64_t)E};
+    cuuint64_t strides[2] = {(cuuint64_t)K / 2, (cuuint64_t)K / 2 * (cuuint64_t)N};
+    cuuint32_t box[3] = {BK / 2, NF4_BN, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(packed), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return MOE_ERR_UNSUPPORTED;
+  }
+  const int bytes = NF4_STAGES * NF4_STAGE_BYTES + (int)sizeof(Control) + (int)sizeof(Nf4Control) + 2 * (E + 1) * 4 + 1024;
+  if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
+  const int grid = sm_count();
+  if (dtype_in == MOE_BF16) {
+    if ((st = set_smem(tc_fwd_nf4_kernel<true>, bytes)) != MOE_OK) return st;
+    tc_fwd_nf4_kernel<true><<<grid, NF4_THREADS, bytes, stream>>>(ma, mq, p, q);
+  } else {
+    if ((st = set_smem(tc_fwd_nf4_kernel<false>, bytes)) != MOE_OK) return st;
+    tc_fwd_nf4_kernel<false><<<grid, NF4_THREADS, bytes, stream>>>(ma, mq, p, q);
+  }
+  return launch_status();
+}
+
+// Reads and clears the device-side error word written by an abandoned wait.
+int tc_read_error(int* flag_out, bool clear) {
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, tc::g_tc_error, sizeof(int));
+  if (e != cudaSuccess) return cuda_status(e);
+  if (clear && v != 0) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(tc::g_tc_error, &zero, sizeof(int));
+    if (e != cudaSuccess) return cuda_status(e);
+  }
+  *flag_out = v;
+  return MOE_OK;
+}
+
+}  // namespace moe

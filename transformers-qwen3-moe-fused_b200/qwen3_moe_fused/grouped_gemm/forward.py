@@ -1,0 +1,51 @@
+"""y[m, n] = sum_k w[s[m], n, k] * x[m, k] with rows grouped by expert.
+
+Same contract as the reference's `grouped_gemm_forward`
+(qwen3_moe_fused/grouped_gemm/forward.py:116-160): identical argument checks, output
+allocated with torch, kernel enqueued on the current CUDA stream, `m_sizes` never read
+on the host.
+"""
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from .._lib import is_int_tensor  # re-exported: the reference defines it here
+
+
+def _launch(name: str, which: int, a, b, m_sizes, out, M: int, N: int, K: int, E: int) -> None:
+    lib = _lib.load()
+    m_sizes = _lib.as_index_tensor(m_sizes)
+    fn = getattr(lib, name)
+    status = fn(
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(m_sizes), _lib.int_code(m_sizes.dtype), _lib.ptr(out),
+        M, N, K, E, _lib.float_code(a.dtype), _lib.float_code(out.dtype), None, 0, _lib.stream_ptr(a.device),
+    )
+    _lib.check(status, name)
+
+
+def grouped_gemm_forward(
+    x: torch.Tensor, w: torch.Tensor, m_sizes: torch.Tensor, dtype: Optional[torch.dtype] = None
+) -> torch.Tensor:
+    assert x.is_cuda
+    assert w.device == x.device
+    assert m_sizes.device == x.device
+    assert is_int_tensor(m_sizes)
+    assert x.is_contiguous()
+    assert w.is_contiguous()
+    assert m_sizes.is_contiguous()
+    assert x.ndim == 2
+    assert w.ndim == 3
+    assert m_sizes.ndim == 1
+    assert w.dtype == x.dtype
+    M, K = x.shape
+    E, N, _ = w.shape
+    assert w.shape[2] == K
+    assert m_sizes.numel() == E
+
+    if dtype is None:
+        dtype = x.dtype
+    y = torch.empty((M, N), device=x.device, dtype=dtype)
+    with torch.cuda.device(x.device):
+        _launch("moe_grouped_gemm_fwd", 0, x, w, m_sizes, y, M, N, K, E)
+    return y

@@ -1,0 +1,86 @@
+"""Forward grouped GEMM with the NF4 weight decoded inside the kernel.
+
+Same contract as the reference's `grouped_gemm_forward_4bit`
+(qwen3_moe_fused/grouped_gemm/forward_4bit.py:135-208).  `w_quant_state` is any object
+with the bitsandbytes `QuantState` attributes that function reads: `quant_type`,
+`blocksize`, `code`, `absmax`, `shape`, `nested` and, when nested, `state2` / `offset`
+(`qwen3_moe_fused.quantize.nf4.Nf4State` provides them without bitsandbytes).
+"""
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from .forward import is_int_tensor
+
+
+def _unnest_absmax(state) -> torch.Tensor:
+    """fp32 absmax per block; expands a double-quantised absmax
+    (qwen3_moe_fused/grouped_gemm/forward_4bit.py:149-153)."""
+    absmax = state.absmax
+    if getattr(state, "nested", False):
+        state2 = state.state2
+        if hasattr(state2, "dequantize"):  # own container
+            absmax = state2.dequantize(absmax)
+        else:  # bitsandbytes QuantState
+            from bitsandbytes.functional import dequantize_blockwise
+
+            absmax = dequantize_blockwise(absmax, state2)
+        absmax = absmax + state.offset
+    return absmax
+
+
+def grouped_gemm_forward_4bit(
+    x: torch.Tensor,
+    w_quant: torch.Tensor,
+    w_quant_state,
+    m_sizes: torch.Tensor,
+    dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    assert w_quant_state.quant_type == "nf4"
+    blocksize = int(w_quant_state.blocksize)
+    assert blocksize > 0 and blocksize & (blocksize - 1) == 0
+
+    w_code = w_quant_state.code
+    assert w_code.dtype == torch.float32
+    w_absmax = _unnest_absmax(w_quant_state)
+    assert w_absmax.dtype == torch.float32
+
+    assert x.is_cuda
+    assert w_quant.device == x.device
+    assert w_code.device == x.device
+    assert w_absmax.device == x.device
+    assert m_sizes.device == x.device
+    assert is_int_tensor(w_quant)
+    assert is_int_tensor(m_sizes)
+    assert x.is_contiguous()
+    assert w_quant.is_contiguous()
+    assert w_code.is_contiguous()
+    assert w_absmax.is_contiguous()
+    assert m_sizes.is_contiguous()
+    assert x.ndim == 2
+    assert len(w_quant_state.shape) == 3
+    assert m_sizes.ndim == 1
+    M, K = x.shape
+    E, N, _ = w_quant_state.shape
+    assert w_quant_state.shape[2] == K
+    assert K % 2 == 0
+    assert E * N * K % blocksize == 0
+    assert w_quant.numel() * w_quant.element_size() == E * N * K // 2
+    assert w_absmax.numel() == E * N * K // blocksize
+    assert w_code.numel() == 16
+    assert m_sizes.numel() == E
+
+    if dtype is None:
+        dtype = x.dtype
+    y = torch.empty((M, N), device=x.device, dtype=dtype)
+    lib = _lib.load()
+    m_sizes = _lib.as_index_tensor(m_sizes)
+    with torch.cuda.device(x.device):
+        status = lib.moe_grouped_gemm_fwd_nf4(
+            _lib.ptr(x), _lib.ptr(w_quant), _lib.ptr(w_code), _lib.ptr(w_absmax), blocksize,
+            _lib.ptr(m_sizes), _lib.int_code(m_sizes.dtype), _lib.ptr(y), M, N, K, E,
+            _lib.float_code(x.dtype), _lib.float_code(dtype), None, 0, _lib.stream_ptr(x.device),
+        )
+    _lib.check(status, "moe_grouped_gemm_fwd_nf4")
+    return y

@@ -1,0 +1,75 @@
+"""`MoeFusedLinear` and the sparse MoE block on the kernels of this package.
+
+`MoeFusedLinear` mirrors the reference module
+(qwen3_moe_fused/modular_qwen3_moe_fused.py:29-59): parameter `weight` of shape
+(num_experts, out_features, in_features), Kaiming-uniform initialisation with bound
+sqrt(15 / in_features), `forward(input, m_sizes)`.
+
+`moe_block_forward` computes what `Qwen3MoeFusedSparseMoeBlock.forward` computes
+(:79-118), using one kernel each for the router epilogue (softmax + top-k + renormalise +
+cast), the expand+gather, and the un-permute + weighted combine.
+"""
+import math
+from typing import Optional
+
+import torch
+from torch import nn
+
+from .functional import moe_fused_linear
+from .kernels.indexing import get_expert_counts_and_idx
+from .kernels.routing import combine, gather_rows, softmax_topk
+from .kernels.silu_mul import silu_mul
+
+
+def moe_fused_kaiming_uniform_(weight: torch.Tensor) -> None:
+    bound = math.sqrt(3 * 5 / weight.shape[-1])
+    nn.init.uniform_(weight, -bound, bound)
+
+
+class MoeFusedLinear(nn.Module):
+    __constants__ = ["in_features", "out_features", "num_experts"]
+
+    def __init__(self, in_features: int, out_features: int, num_experts: int,
+                 device: Optional[torch.device] = None, dtype: Optional[torch.dtype] = None) -> None:
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.num_experts = num_experts
+        self.weight = nn.Parameter(torch.empty((num_experts, out_features, in_features), device=device, dtype=dtype))
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        moe_fused_kaiming_uniform_(self.weight)
+
+    def forward(self, input: torch.Tensor, m_sizes: torch.Tensor) -> torch.Tensor:
+        return moe_fused_linear(input, self.weight, m_sizes)
+
+    def extra_repr(self) -> str:
+        return f"in_features={self.in_features}, out_features={self.out_features}, num_experts={self.num_experts}"
+
+
+def route(router_logits: torch.Tensor, num_selected: int, norm_topk_prob: bool, dtype: torch.dtype):
+    """(routing_weights (T,k) dtype, selected_experts (T,k) int64)."""
+    return softmax_topk(router_logits.contiguous(), num_selected, norm_topk_prob, dtype)
+
+
+def moe_block_forward(hidden_states: torch.Tensor, gate_weight: torch.Tensor, gate_proj: torch.Tensor,
+                      up_proj: torch.Tensor, down_proj: torch.Tensor, num_selected: int,
+                      norm_topk_prob: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
+    """hidden_states (B, S, H); gate_weight (E, H); gate_proj/up_proj (E, I, H); down_proj (E, H, I).
+    Returns (output (B, S, H), router_logits (B*S, E))."""
+    B, S, H = hidden_states.shape
+    T = B * S
+    E = gate_weight.shape[0]
+    k = num_selected
+    x = hidden_states.reshape(T, H)
+    router_logits = torch.nn.functional.linear(x, gate_weight)
+    routing_weights, selected = route(router_logits, k, norm_topk_prob, x.dtype)
+    m_sizes, sort_idx, inv_sort_idx = get_expert_counts_and_idx(selected.view(T * k), E)
+    xs = gather_rows(x.contiguous(), sort_idx, inv_sort_idx, k)
+    gate_h = moe_fused_linear(xs, gate_proj, m_sizes)
+    up_h = moe_fused_linear(xs, up_proj, m_sizes)
+    h = silu_mul(gate_h, up_h)
+    y = moe_fused_linear(h, down_proj, m_sizes)
+    out = combine(y, sort_idx, inv_sort_idx, routing_weights)
+    return out.view(B, S, H), router_logits
