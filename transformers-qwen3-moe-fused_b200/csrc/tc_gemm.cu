@@ -11,6 +11,8 @@
 // buffered in TMEM so the epilogue of tile i overlaps the main loop of tile i+1.
 // No tile ever crosses an expert boundary on the store side: an M tile starts at a group's
 // first row and rows past the group's end are computed but not stored.
+#include <cstdio>
+
 #include "tc_common.cuh"
 
 namespace moe {
@@ -742,6 +744,14 @@ tc_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   }
 }
 
+}  // namespace tc
+}  // namespace moe
+
+#include "tc_gemm_pair.cuh"
+
+namespace moe {
+namespace tc {
+
 // ---------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------
@@ -762,6 +772,8 @@ static EncodeTiledFn encode_fn() {
 
 // Tensor map over a dense 16-bit tensor viewed as (d2, d1, d0) with d0 contiguous.
 // Box = (b0 = 64 elements, b1 rows, 1).  rank 2 when d2 == 0.
+thread_local char g_detail[320] = "";
+
 static int make_map(CUtensorMap* map, int dtype, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                     uint32_t b1) {
   EncodeTiledFn fn = encode_fn();
@@ -774,6 +786,9 @@ static int make_map(CUtensorMap* map, int dtype, const void* base, uint64_t d0, 
   cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = fn(map, dt, rank, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    snprintf(g_detail, sizeof(g_detail), "cuTensorMapEncodeTiled -> %d: base=%p dims=(%llu,%llu,%llu) box=(64,%u,1) rank=%u",
+             (int)r, base, (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2, b1, rank);
   return r == CUDA_SUCCESS ? MOE_OK : MOE_ERR_UNSUPPORTED;
 }
 
@@ -802,10 +817,95 @@ bool tc_eligible(int which, const void* a, const void* b, const void* out, int64
   return true;
 }
 
-// which: 0 forward, 1 dX, 2 dW (a = x, b = dy).
-int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes, int ms64, void* out,
-                    int64_t M, int N, int K, int E, int dtype_in, int dtype_out, cudaStream_t stream) {
+// The driver's tensor-map encoder needs a current context on the calling thread; threads
+// that have not yet issued a runtime call of this library (autograd worker threads) get the
+// primary context bound here, once per thread and device.
+static void bind_context_once() {
+  thread_local int bound = -1;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  if (bound != dev) {
+    cudaFree(nullptr);
+    bound = dev;
+  }
+}
+
+// Number of CTA pairs that can be resident at once (persistent grid = 2 x this).
+template <typename Kern>
+static int resident_pairs(Kern kernel, int smem_bytes) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * sm_count());
+  cfg.blockDim = dim3(tc::PAIR_THREADS);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+    (void)cudaGetLastError();
+    n = sm_count() / 2;
+  }
+  const int cap = sm_count() / 2;
+  return n < cap ? n : cap;
+}
+
+static int pair_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes, int ms64, void* out,
+                             int64_t M, int N, int K, int E, int dtype_in, int dtype_out, cudaStream_t stream) {
   using namespace tc;
+  GemmParams p;
+  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out;
+  const int fmt = dtype_in == MOE_BF16 ? 1 : 0;
+  CUtensorMap mw, mx, mo;
+  int st;
+  if (which == 0 || which == 1) {
+    // A = weight (accumulator rows), B = activations (accumulator columns = tokens)
+    if (which == 0) st = make_map(&mw, dtype_in, b, (uint64_t)K, (uint64_t)N, (uint64_t)E, 128);
+    else st = make_map(&mw, dtype_in, b, (uint64_t)N, (uint64_t)K, (uint64_t)E, BK);
+    if (st != MOE_OK) return st;
+    if ((st = make_map(&mx, dtype_in, a, (uint64_t)K, (uint64_t)M, 0, 128)) != MOE_OK) return st;
+    p.idesc = make_idesc(fmt, which == 1, 0, 256, 0);  // N field is filled per tile
+    const int bytes = 6 * 2 * PAIR_HALF_BYTES + (int)sizeof(PairControl) + 2 * (E + 1) * 4 + 1024;
+    if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
+    if (which == 0) {
+      if ((st = set_smem(pair_fwd_kernel<false>, bytes)) != MOE_OK) return st;
+      const int grid = 2 * resident_pairs(pair_fwd_kernel<false>, bytes);
+      pair_fwd_kernel<false><<<grid, PAIR_THREADS, bytes, stream>>>(mw, mx, p);
+    } else {
+      if ((st = set_smem(pair_fwd_kernel<true>, bytes)) != MOE_OK) return st;
+      const int grid = 2 * resident_pairs(pair_fwd_kernel<true>, bytes);
+      pair_fwd_kernel<true><<<grid, PAIR_THREADS, bytes, stream>>>(mw, mx, p);
+    }
+    return launch_status();
+  }
+  // dW: a = x (M,K), b = dy (M,N), out (E,N,K) 16-bit
+  if ((st = make_map(&mw, dtype_in, b, (uint64_t)N, (uint64_t)M, 0, BK)) != MOE_OK) return st;
+  if ((st = make_map(&mx, dtype_in, a, (uint64_t)K, (uint64_t)M, 0, BK)) != MOE_OK) return st;
+  if ((st = make_map(&mo, dtype_out, out, (uint64_t)K, (uint64_t)N, (uint64_t)E, 128)) != MOE_OK) return st;
+  p.idesc = make_idesc(fmt, 1, 1, 256, 256);
+  const int bytes = 5 * 2 * PAIR_HALF_BYTES + 2 * 128 * 128 + (int)sizeof(PairControl) + 3 * (E + 1) * 4 + 1024;
+  if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
+  if ((st = set_smem(pair_dw_kernel, bytes)) != MOE_OK) return st;
+  const int grid = 2 * resident_pairs(pair_dw_kernel, bytes);
+  pair_dw_kernel<<<grid, PAIR_THREADS, bytes, stream>>>(mw, mx, mo, p);
+  return launch_status();
+}
+
+// which: 0 forward, 1 dX, 2 dW (a = x, b = dy).  single_cta selects the one-CTA kernels.
+int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes, int ms64, void* out,
+                    int64_t M, int N, int K, int E, int dtype_in, int dtype_out, cudaStream_t stream,
+                    bool single_cta) {
+  using namespace tc;
+  bind_context_once();
+  if (!single_cta) {
+    // a pair covers 256 weight rows (and, for dW, 256 weight columns): narrower problems
+    // would leave most of the tile empty
+    const bool pair_ok = which != 2 ? (which == 0 ? N >= 192 : N >= 192)
+                                    : (N >= 192 && K >= 192 && (dtype_out == MOE_BF16 || dtype_out == MOE_F16) &&
+                                       (((uintptr_t)out & 15) == 0));
+    if (pair_ok) return pair_grouped_gemm(which, a, b, m_sizes, ms64, out, M, N, K, E, dtype_in, dtype_out, stream);
+  }
   GemmParams p;
   p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out;
   const int fmt = dtype_in == MOE_BF16 ? 1 : 0;
@@ -865,6 +965,7 @@ int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code,
                         const void* m_sizes, int ms64, void* out, int64_t M, int N, int K, int E,
                         int dtype_in, int dtype_out, cudaStream_t stream) {
   using namespace tc;
+  bind_context_once();
   GemmParams p;
   p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out;
   p.idesc = make_idesc(dtype_in == MOE_BF16 ? 1 : 0, 0, 0, BM, NF4_BN);
@@ -898,6 +999,9 @@ int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code,
   }
   return launch_status();
 }
+
+// Text describing the most recent host-side failure on the calling thread ("" if none).
+const char* tc_last_detail() { return tc::g_detail; }
 
 // Reads and clears the device-side error word written by an abandoned wait.
 int tc_read_error(int* flag_out, bool clear) {

@@ -13,7 +13,7 @@ from pathlib import Path
 import torch
 
 F32, BF16, F16, I32, I64 = 0, 1, 2, 3, 4
-PATH_AUTO, PATH_SIMT, PATH_TC = 0, 1, 2
+PATH_AUTO, PATH_SIMT, PATH_TC, PATH_TC_SINGLE = 0, 1, 2, 3
 
 _FLOAT_CODES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 _INT_CODES = {torch.int32: I32, torch.int64: I64}
@@ -43,6 +43,7 @@ SIGNATURES = {
     "moe_gather_rows": (_I, [_P, _P, _I, _P, _L, _I, _I, _P]),
     "moe_combine": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _P]),
     "moe_debug_read_error": (_I, [_P, _I]),
+    "moe_debug_last_detail": (c_char_p, []),
 }
 
 _lib = None
@@ -78,7 +79,8 @@ def load() -> ctypes.CDLL:
 def check(status: int, what: str) -> None:
     if status != 0:
         msg = load().moe_status_string(status).decode()
-        raise MoeB200Error(f"{what} failed with status {status}: {msg}")
+        detail = load().moe_debug_last_detail().decode()
+        raise MoeB200Error(f"{what} failed with status {status}: {msg}" + (f" [{detail}]" if detail else ""))
 
 
 def float_code(dtype: torch.dtype) -> int:

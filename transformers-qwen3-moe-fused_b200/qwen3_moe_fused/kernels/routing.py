@@ -26,6 +26,36 @@ def softmax_topk(router_logits: torch.Tensor, k: int, norm_topk_prob: bool, out_
     return weights, experts
 
 
+class SoftmaxTopk(torch.autograd.Function):
+    """Differentiable wrapper: the forward is one kernel; the backward recomputes the fp32
+    softmax of the (T, E) logits and differentiates gather -> renormalise -> cast, which is
+    what autograd does for the reference's sequence of ATen calls."""
+
+    @staticmethod
+    def forward(ctx, router_logits, k, norm_topk_prob, out_dtype):
+        weights, experts = softmax_topk(router_logits, k, norm_topk_prob, out_dtype)
+        ctx.save_for_backward(router_logits, experts)
+        ctx.norm = norm_topk_prob
+        ctx.out_dtype = out_dtype
+        ctx.mark_non_differentiable(experts)
+        return weights, experts
+
+    @staticmethod
+    def backward(ctx, dweights, _dexperts):
+        logits, experts = ctx.saved_tensors
+        with torch.enable_grad():
+            lg = logits.detach().requires_grad_()
+            sel = torch.softmax(lg, dim=1, dtype=torch.float32).gather(1, experts)
+            if ctx.norm:
+                sel = sel / sel.sum(dim=-1, keepdim=True)
+            (grad,) = torch.autograd.grad(sel.to(ctx.out_dtype), lg, dweights)
+        return grad, None, None, None
+
+
+def softmax_topk_autograd(router_logits, k, norm_topk_prob, out_dtype):
+    return SoftmaxTopk.apply(router_logits, k, norm_topk_prob, out_dtype)
+
+
 def _gather_rows(hidden: torch.Tensor, sort_idx: torch.Tensor, k: int) -> torch.Tensor:
     assert hidden.is_cuda and hidden.ndim == 2 and hidden.is_contiguous()
     assert sort_idx.dtype == torch.int32 and sort_idx.is_contiguous()

@@ -17,7 +17,7 @@ from torch import nn
 
 from .functional import moe_fused_linear
 from .kernels.indexing import get_expert_counts_and_idx
-from .kernels.routing import combine, gather_rows, softmax_topk
+from .kernels.routing import combine, gather_rows, softmax_topk_autograd
 from .kernels.silu_mul import silu_mul
 
 
@@ -50,7 +50,7 @@ class MoeFusedLinear(nn.Module):
 
 def route(router_logits: torch.Tensor, num_selected: int, norm_topk_prob: bool, dtype: torch.dtype):
     """(routing_weights (T,k) dtype, selected_experts (T,k) int64)."""
-    return softmax_topk(router_logits.contiguous(), num_selected, norm_topk_prob, dtype)
+    return softmax_topk_autograd(router_logits.contiguous(), num_selected, norm_topk_prob, dtype)
 
 
 def moe_block_forward(hidden_states: torch.Tensor, gate_weight: torch.Tensor, gate_proj: torch.Tensor,
