@@ -12,6 +12,7 @@
 // No tile ever crosses an expert boundary on the store side: an M tile starts at a group's
 // first row and rows past the group's end are computed but not stored.
 #include <cstdio>
+#include <cstdlib>
 
 #include "tc_common.cuh"
 
@@ -34,6 +35,7 @@ struct GemmParams {
   int ms64;
   int dtype_out;  // MOE_F32 / MOE_BF16 / MOE_F16
   uint32_t idesc;
+  int debug;      // experiment switches (MOE_B200_DEBUG): 1 = no global stores, 2 = no TMEM loads, 4 = no MMA
 };
 
 struct Control {
@@ -268,7 +270,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             // K-major: 16 elements = 32 bytes inside the swizzle row; MN-major: 16 rows of 128 B.
             const uint64_t a_adv = (uint64_t)((k * UMMA_K * 2) >> 4);
             const uint64_t b_adv = B_MN ? (uint64_t)((k * UMMA_K * 128) >> 4) : a_adv;
-            umma_f16(d_tmem, da + a_adv, db + b_adv, p.idesc, (kb | k) != 0);
+            if (!(p.debug & 4)) umma_f16(d_tmem, da + a_adv, db + b_adv, p.idesc, (kb | k) != 0);
           }
           umma_commit(&ctl->empty[s]);  // frees the stage when these MMAs have read it
         }
@@ -300,9 +302,14 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       for (int c = 0; c < BN; c += 32) {
         if (n0 + c >= p.N) break;  // warp-uniform
         uint32_t v[32];
-        tmem_ld_32x32(taddr + c, v);
-        tmem_ld_wait();
-        if (row_ok) {
+        if (!(p.debug & 2)) {
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = c + i;
+        }
+        if (row_ok && !(p.debug & 1)) {
           const int ncols = min(32, p.N - (n0 + c));
           store_acc(p.out, p.dtype_out, grow * p.N + n0 + c, v, ncols, vec);
         }
@@ -445,14 +452,12 @@ tc_dw_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
         uint8_t* sa_ptr = smem + s * STAGE_BYTES;
         const int valid = rows - mb * BK;  // reduction rows of this block that belong to e
         if (valid < BK) {
-          // zero rows [valid, 64) of every 64-wide chunk of both operands (128 B per row)
+          // zero rows [valid, 64) of every 64-wide chunk of both operands (128 B per row);
+          // lane -> 16-byte column lane % 8 of chunks lane / 8, lane / 8 + 4
           constexpr int CHUNKS = (BM + BN) / 64;
-          const int bad = BK - valid;
-          for (int i = lane; i < CHUNKS * bad * 8; i += 32) {
-            const int c = i / (bad * 8);
-            const int rem = i % (bad * 8);
-            const int row = valid + rem / 8;
-            *reinterpret_cast<uint4*>(sa_ptr + c * CHUNK_BYTES + row * 128 + (rem % 8) * 16) = make_uint4(0, 0, 0, 0);
+          for (int c = lane >> 3; c < CHUNKS; c += 4) {
+            uint8_t* col = sa_ptr + c * CHUNK_BYTES + (lane & 7) * 16;
+            for (int row = valid; row < BK; ++row) *reinterpret_cast<uint4*>(col + row * 128) = make_uint4(0, 0, 0, 0);
           }
           fence_proxy_async_smem();
         }
@@ -465,7 +470,7 @@ tc_dw_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t adv = (uint64_t)((k * UMMA_K * 128) >> 4);
-            umma_f16(d_tmem, da + adv, db + adv, p.idesc, (mb | k) != 0);
+            if (!(p.debug & 4)) umma_f16(d_tmem, da + adv, db + adv, p.idesc, (mb | k) != 0);
           }
           umma_commit(&ctl->empty[s]);
         }
@@ -511,9 +516,14 @@ tc_dw_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
       for (int c = 0; c < BN; c += 32) {
         if (k0 + c >= p.K) break;
         uint32_t v[32];
-        tmem_ld_32x32(taddr + c, v);
-        tmem_ld_wait();
-        if (row_ok) store_acc(p.out, p.dtype_out, out_row + k0 + c, v, min(32, p.K - (k0 + c)), vec);
+        if (!(p.debug & 2)) {
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = c + i;
+        }
+        if (row_ok && !(p.debug & 1)) store_acc(p.out, p.dtype_out, out_row + k0 + c, v, min(32, p.K - (k0 + c)), vec);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -820,6 +830,11 @@ bool tc_eligible(int which, const void* a, const void* b, const void* out, int64
 // The driver's tensor-map encoder needs a current context on the calling thread; threads
 // that have not yet issued a runtime call of this library (autograd worker threads) get the
 // primary context bound here, once per thread and device.
+static int debug_flags() {
+  static int v = []() { const char* e = getenv("MOE_B200_DEBUG"); return e ? atoi(e) : 0; }();
+  return v;
+}
+
 static void bind_context_once() {
   thread_local int bound = -1;
   int dev = 0;
@@ -855,7 +870,7 @@ static int pair_grouped_gemm(int which, const void* a, const void* b, const void
                              int64_t M, int N, int K, int E, int dtype_in, int dtype_out, cudaStream_t stream) {
   using namespace tc;
   GemmParams p;
-  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out;
+  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags();
   const int fmt = dtype_in == MOE_BF16 ? 1 : 0;
   CUtensorMap mw, mx, mo;
   int st;
@@ -907,7 +922,7 @@ int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes
     if (pair_ok) return pair_grouped_gemm(which, a, b, m_sizes, ms64, out, M, N, K, E, dtype_in, dtype_out, stream);
   }
   GemmParams p;
-  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out;
+  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags();
   const int fmt = dtype_in == MOE_BF16 ? 1 : 0;
   const int grid = sm_count();
   CUtensorMap ma, mb;
@@ -967,7 +982,7 @@ int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code,
   using namespace tc;
   bind_context_once();
   GemmParams p;
-  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out;
+  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags();
   p.idesc = make_idesc(dtype_in == MOE_BF16 ? 1 : 0, 0, 0, BM, NF4_BN);
   Nf4Params q;
   q.code = code; q.absmax = absmax; q.shift = 0;

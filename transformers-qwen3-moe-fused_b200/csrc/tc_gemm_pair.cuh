@@ -157,7 +157,7 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t b_adv = (uint64_t)((k * UMMA_K * 2) >> 4);
             const uint64_t a_adv = W_MN ? (uint64_t)((k * UMMA_K * 128) >> 4) : b_adv;
-            umma_f16_pair(d_tmem, da + a_adv, db + b_adv, idesc, (kb | k) != 0);
+            if (!(p.debug & 4)) umma_f16_pair(d_tmem, da + a_adv, db + b_adv, idesc, (kb | k) != 0);
           }
           umma_commit_pair(&ctl->empty[s], 3);
         }
@@ -184,9 +184,14 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll 1
       for (int c = 0; c < n_mma; c += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(taddr + c, v);
-        tmem_ld_wait();
-        if (n_ok) {
+        if (!(p.debug & 2)) {
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = c + i;
+        }
+        if (n_ok && !(p.debug & 1)) {
           const int64_t base = (int64_t)(t0 + c) * p.N + n;
           const int valid = min(32, t_end - (t0 + c));  // tokens of this chunk that belong to the expert
           if (p.dtype_out == MOE_BF16) {
@@ -344,12 +349,9 @@ pair_dw_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constan
         uint8_t* sa_ptr = smem + s * STAGE_BYTES;
         const int valid = rows - mb * BK;
         if (valid < BK) {
-          const int bad = BK - valid;
-          for (int i = lane; i < 4 * bad * 8; i += 32) {  // 4 chunks (2 of A, 2 of B)
-            const int c = i / (bad * 8);
-            const int rem = i % (bad * 8);
-            *reinterpret_cast<uint4*>(sa_ptr + c * CHUNK_BYTES + (valid + rem / 8) * 128 + (rem % 8) * 16) = make_uint4(0, 0, 0, 0);
-          }
+          // lane -> (chunk = lane / 8 of the 4 chunks, 16-byte column = lane % 8); rows past `valid`
+          uint8_t* col = sa_ptr + (lane >> 3) * CHUNK_BYTES + (lane & 7) * 16;
+          for (int row = valid; row < BK; ++row) *reinterpret_cast<uint4*>(col + row * 128) = make_uint4(0, 0, 0, 0);
           fence_proxy_async_smem();
         }
         __syncwarp();
@@ -366,7 +368,7 @@ pair_dw_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constan
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
               const uint64_t adv = (uint64_t)((k * UMMA_K * 128) >> 4);
-              umma_f16_pair(d_tmem, da + adv, db + adv, p.idesc, (mb | k) != 0);
+              if (!(p.debug & 4)) umma_f16_pair(d_tmem, da + adv, db + adv, p.idesc, (mb | k) != 0);
             }
             umma_commit_pair(&ctl->empty[s], 3);
           }
@@ -409,7 +411,7 @@ pair_dw_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constan
         if (epi_tid == 0) tma_store_wait_read<1>();
         named_barrier_sync(1, 128);
         uint32_t v[64];
-        if (rows > 0) {
+        if (rows > 0 && !(p.debug & 2)) {
           tmem_ld_32x32(taddr + c * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
           tmem_ld_32x32(taddr + c * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
           tmem_ld_wait();
@@ -435,7 +437,7 @@ pair_dw_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constan
         }
         fence_proxy_async_smem();
         named_barrier_sync(1, 128);
-        if (epi_tid == 0) {
+        if (epi_tid == 0 && !(p.debug & 1)) {
           tma_store_3d(&tmap_out, buf, k0 + c * 64, n0, e);  // rows/columns past N/K are clipped
           tma_store_commit();
         }
