@@ -13,7 +13,8 @@ int simt_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* cod
 bool tc_eligible(int which, const void* a, const void* b, const void* out, int64_t M, int N, int K, int E,
                  int dtype_in, int dtype_out);
 int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes, int ms64, void* out,
-                    int64_t M, int N, int K, int E, int dtype_in, int dtype_out, cudaStream_t stream, bool single_cta);
+                    int64_t M, int N, int K, int E, int dtype_in, int dtype_out, void* ws, size_t ws_bytes,
+                    cudaStream_t stream, bool single_cta);
 bool tc_nf4_eligible(const void* x, const void* packed, const void* absmax, const void* out, int64_t M, int N, int K,
                      int E, int blocksize, int dtype_in, int dtype_out);
 int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code, const float* absmax, int blocksize,
@@ -47,14 +48,14 @@ static int check_common(const void* a, const void* b, const void* m_sizes, int m
 }
 
 static int run(int which, const void* a, const void* b, const void* m_sizes, int msd, void* out, int64_t M,
-               int N, int K, int E, int dtype_in, int dtype_out, cudaStream_t stream) {
+               int N, int K, int E, int dtype_in, int dtype_out, void* ws, size_t ws_bytes, cudaStream_t stream) {
   if (!device_is_sm100()) return MOE_ERR_DEVICE;
   const int ms64 = msd == MOE_I64;
   const int path = g_path.load(std::memory_order_relaxed);
   const bool can_tc = tc_eligible(which, a, b, out, M, N, K, E, dtype_in, dtype_out);
   if ((path == MOE_PATH_TC || path == MOE_PATH_TC_SINGLE) && !can_tc) return MOE_ERR_UNSUPPORTED;
   if (can_tc && path != MOE_PATH_SIMT)
-    return tc_grouped_gemm(which, a, b, m_sizes, ms64, out, M, N, K, E, dtype_in, dtype_out, stream, path == MOE_PATH_TC_SINGLE);
+    return tc_grouped_gemm(which, a, b, m_sizes, ms64, out, M, N, K, E, dtype_in, dtype_out, ws, ws_bytes, stream, path == MOE_PATH_TC_SINGLE);
   return simt_grouped_gemm(which, a, b, m_sizes, ms64, out, M, N, K, E, dtype_in, dtype_out, stream);
 }
 
@@ -85,35 +86,38 @@ MOE_API int moe_set_gemm_path(int path) {
 }
 MOE_API int moe_get_gemm_path(void) { return g_path.load(); }
 
-MOE_API size_t moe_grouped_gemm_workspace_bytes(int, int64_t, int, int, int) { return 0; }
+MOE_API size_t moe_grouped_gemm_workspace_bytes(int, int64_t, int, int, int E) {
+  // room for up to four per-expert tensor maps (128 bytes each)
+  return E > 0 ? (size_t)4 * (size_t)E * 128 : 0;
+}
 
 MOE_API int moe_grouped_gemm_fwd(const void* x, const void* w, const void* m_sizes, int msd, void* y, int64_t M,
-                                 int N, int K, int E, int dtype_in, int dtype_out, void*, size_t, void* stream) {
+                                 int N, int K, int E, int dtype_in, int dtype_out, void* ws, size_t ws_bytes, void* stream) {
   int st = check_common(x, w, m_sizes, msd, y, M, N, K, E, dtype_in, dtype_out);
   if (st != MOE_OK) return st;
   if (M == 0 || N == 0) return MOE_OK;
   if (K == 0) return cuda_status(cudaMemsetAsync(y, 0, (size_t)M * N * dtype_size(dtype_out), (cudaStream_t)stream));
-  return run(0, x, w, m_sizes, msd, y, M, N, K, E, dtype_in, dtype_out, (cudaStream_t)stream);
+  return run(0, x, w, m_sizes, msd, y, M, N, K, E, dtype_in, dtype_out, ws, ws_bytes, (cudaStream_t)stream);
 }
 
 MOE_API int moe_grouped_gemm_dx(const void* x, const void* w, const void* m_sizes, int msd, void* y, int64_t M,
-                                int N, int K, int E, int dtype_in, int dtype_out, void*, size_t, void* stream) {
+                                int N, int K, int E, int dtype_in, int dtype_out, void* ws, size_t ws_bytes, void* stream) {
   int st = check_common(x, w, m_sizes, msd, y, M, N, K, E, dtype_in, dtype_out);
   if (st != MOE_OK) return st;
   if (M == 0 || N == 0) return MOE_OK;
   if (K == 0) return cuda_status(cudaMemsetAsync(y, 0, (size_t)M * N * dtype_size(dtype_out), (cudaStream_t)stream));
-  return run(1, x, w, m_sizes, msd, y, M, N, K, E, dtype_in, dtype_out, (cudaStream_t)stream);
+  return run(1, x, w, m_sizes, msd, y, M, N, K, E, dtype_in, dtype_out, ws, ws_bytes, (cudaStream_t)stream);
 }
 
 MOE_API int moe_grouped_gemm_dw(const void* x, const void* y, const void* m_sizes, int msd, void* w, int64_t M,
-                                int N, int K, int E, int dtype_in, int dtype_out, void*, size_t, void* stream) {
+                                int N, int K, int E, int dtype_in, int dtype_out, void* ws, size_t ws_bytes, void* stream) {
   if (!is_float_dtype(dtype_in) || !is_float_dtype(dtype_out) || !is_int_dtype(msd)) return MOE_ERR_DTYPE;
   if (M < 0 || N < 0 || K < 0 || E <= 0 || M > 0x7fffffffLL) return MOE_ERR_SHAPE;
   if (!m_sizes) return MOE_ERR_NULL;
   if (N == 0 || K == 0) return MOE_OK;
   if (!w || (M > 0 && (!x || !y))) return MOE_ERR_NULL;
   if (M == 0) return cuda_status(cudaMemsetAsync(w, 0, (size_t)E * N * K * dtype_size(dtype_out), (cudaStream_t)stream));
-  return run(2, x, y, m_sizes, msd, w, M, N, K, E, dtype_in, dtype_out, (cudaStream_t)stream);
+  return run(2, x, y, m_sizes, msd, w, M, N, K, E, dtype_in, dtype_out, ws, ws_bytes, (cudaStream_t)stream);
 }
 
 MOE_API int moe_grouped_gemm_fwd_nf4(const void* x, const uint8_t* packed, const float* code, const float* absmax,

@@ -135,6 +135,25 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------
+// Tensor maps edited on the device.  A copy of a host-encoded map is patched in shared
+// memory (here: the extent of one dimension), published to global memory through the
+// tensormap proxy, and acquired by whichever thread later issues TMA operations with it.
+// ---------------------------------------------------------------------------------------
+template <int ORD>
+__device__ __forceinline__ void tensormap_replace_dim(void* smem_map, uint32_t extent) {
+  asm volatile("tensormap.replace.tile.global_dim.shared::cta.b1024.b32 [%0], %1, %2;"
+               ::"l"((uint64_t)smem_u32(smem_map)), "n"(ORD), "r"(extent) : "memory");
+}
+// Whole warp: copies the 128-byte map from shared to global memory with release semantics.
+__device__ __forceinline__ void tensormap_publish(void* gmem_dst, void* smem_src) {
+  asm volatile("tensormap.cp_fenceproxy.global.shared::cta.tensormap::generic.release.gpu.sync.aligned [%0], [%1], 128;"
+               ::"l"((uint64_t)gmem_dst), "r"(smem_u32(smem_src)) : "memory");
+}
+__device__ __forceinline__ void tensormap_acquire(const void* gmem_map) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"((uint64_t)gmem_map) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------
 // CTA pairs (cluster of 2, tcgen05 cta_group::2).  CTA rank 0 of the pair is the leader: it
 // issues the MMAs, which read both CTAs' shared memory and write both CTAs' TMEM.
 // ---------------------------------------------------------------------------------------
@@ -204,6 +223,12 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void*
   asm volatile(
       "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
       ::"l"((uint64_t)map), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+      ::"l"((uint64_t)map), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
       : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }

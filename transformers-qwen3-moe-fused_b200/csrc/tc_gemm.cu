@@ -4,7 +4,7 @@
 //
 //   tc_fwd_kernel<BN, false> : y[m,n] = sum_k x[m,k] w[e,n,k]   (B operand K-major)
 //   tc_fwd_kernel<BN, true>  : y[m,n] = sum_k x[m,k] w[e,k,n]   (B operand MN-major; dX)
-//   tc_dw_kernel             : w[e,n,k] = sum_m y[m,n] x[m,k]   (both operands MN-major)
+//   dw_kernel (tc_gemm_dw.cuh): w[e,n,k] = sum_m y[m,n] x[m,k]   (both operands MN-major)
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
 // warps 2..5 = epilogue (TMEM -> registers -> global).  The accumulator is double
@@ -13,6 +13,7 @@
 // first row and rows past the group's end are computed but not stored.
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 
 #include "tc_common.cuh"
 
@@ -35,6 +36,7 @@ struct GemmParams {
   int ms64;
   int dtype_out;  // MOE_F32 / MOE_BF16 / MOE_F16
   uint32_t idesc;
+  const CUtensorMap* group_maps;  // per-expert tensor maps in workspace ([slot][expert]), or null
   int debug;      // experiment switches (MOE_B200_DEBUG): 1 = no global stores, 2 = no TMEM loads, 4 = no MMA
 };
 
@@ -329,218 +331,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------
-// dW: one work item = (expert, 128-wide slice of N, BN-wide slice of K); the reduction
-// runs over the expert's rows in blocks of 64.  Rows of the last block that belong to the
-// next expert are zeroed in shared memory before the MMA reads them.  Work items are
-// ordered by decreasing group size and dealt to the CTAs in snake order, which keeps the
-// per-CTA totals balanced under skewed routing without any global scheduler state.
-// ---------------------------------------------------------------------------------------
-template <int BN>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-tc_dw_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_x,
-             const GemmParams p) {
-  constexpr int B_STAGE_BYTES = BN * BK * 2;
-  constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  constexpr int STAGES = (BN == 256) ? 4 : 6;
-  constexpr uint32_t TMEM_COLS = 2 * BN;
-  constexpr int CHUNK_BYTES = BK * 128;  // one 64-wide MN chunk: 64 reduction rows x 128 B
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  Control* ctl = reinterpret_cast<Control*>(smem + STAGES * STAGE_BYTES);
-  int* row_start = reinterpret_cast<int*>(ctl + 1);
-  int* order = row_start + (p.E + 1);  // order[r] = expert with the r-th largest group
-  volatile int* abort_flag = &ctl->abort_flag;
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 4); }
-    ctl->abort_flag = 0;
-    fence_barrier_init();
-    tma_prefetch_desc(&tmap_dy);
-    tma_prefetch_desc(&tmap_x);
-  }
-  if (warp == 1) {
-    tmem_alloc(&ctl->tmem_base, TMEM_COLS);
-    tmem_relinquish();
-  }
-  build_group_tables(p.m_sizes, p.ms64, p.E, p.M, BK, row_start, order);  // `order` used as scratch here
-  // rank by (size descending, expert ascending)
-  __syncthreads();
-  for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
-    const int me = row_start[e + 1] - row_start[e];
-    int rank = 0;
-    for (int o = 0; o < p.E; ++o) {
-      const int mo = row_start[o + 1] - row_start[o];
-      rank += (mo > me) || (mo == me && o < e);
-    }
-    // written after everybody has finished reading `order` as scratch (no reader: the tile
-    // prefix is not used by this kernel), so a plain store is fine
-    order[p.E + 1 + rank] = e;
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const int* sorted = order + p.E + 1;
-  const uint32_t tmem_base = ctl->tmem_base;
-
-  const int n_tiles = (p.N + BM - 1) / BM;   // slices of the output's row dimension (N)
-  const int k_tiles = (p.K + BN - 1) / BN;   // slices of the output's column dimension (K)
-  const int per_expert = n_tiles * k_tiles;
-  const int64_t total_items = (int64_t)p.E * per_expert;
-  const int G = gridDim.x;
-
-  // item handled by this CTA in round r (snake order)
-  auto item_of = [&](int64_t r) -> int64_t {
-    return r * G + ((r & 1) ? (G - 1 - (int)blockIdx.x) : (int)blockIdx.x);
-  };
-  const int64_t rounds = (total_items + G - 1) / G;
-
-  if (warp == 0) {
-    if (elect_one()) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int64_t r = 0; r < rounds && ok; ++r) {
-        const int64_t item = item_of(r);
-        if (item >= total_items) continue;
-        const int e = sorted[item / per_expert];
-        const int j = (int)(item % per_expert);
-        const int n0 = (j % n_tiles) * BM;
-        const int k0 = (j / n_tiles) * BN;
-        const int r0 = row_start[e];
-        const int m_blocks = (row_start[e + 1] - r0 + BK - 1) / BK;
-        for (int mb = 0; mb < m_blocks; ++mb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, W_EMPTY)) { ok = false; break; }
-          uint8_t* sa = smem + s * STAGE_BYTES;
-          uint8_t* sb = sa + A_STAGE_BYTES;
-          mbar_expect_tx(&ctl->full[s], STAGE_BYTES);
-#pragma unroll
-          for (int c = 0; c < BM / 64; ++c)
-            tma_load_2d(sa + c * CHUNK_BYTES, &tmap_dy, &ctl->full[s], n0 + c * 64, r0 + mb * BK);
-#pragma unroll
-          for (int c = 0; c < BN / 64; ++c)
-            tma_load_2d(sb + c * CHUNK_BYTES, &tmap_x, &ctl->full[s], k0 + c * 64, r0 + mb * BK);
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // Whole warp stays converged: lanes share the waits and the tail fix-up, lane 0 issues.
-    uint32_t it = 0, acc_it = 0;
-    bool ok = true;
-    for (int64_t r = 0; r < rounds && ok; ++r) {
-      const int64_t item = item_of(r);
-      if (item >= total_items) continue;
-      const int e = sorted[item / per_expert];
-      const int rows = row_start[e + 1] - row_start[e];
-      const int m_blocks = (rows + BK - 1) / BK;
-      if (m_blocks == 0) continue;  // empty expert: the epilogue writes zeros on its own
-      const uint32_t acc = acc_it & 1;
-      const uint32_t acc_ph = (acc_it >> 1) & 1;
-      if (!mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1, abort_flag, W_TMEM_EMPTY)) { ok = false; break; }
-      tc_fence_after_sync();
-      const uint32_t d_tmem = tmem_base + acc * BN;
-      for (int mb = 0; mb < m_blocks; ++mb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        if (!mbar_wait(&ctl->full[s], ph, abort_flag, W_FULL)) { ok = false; break; }
-        tc_fence_after_sync();
-        uint8_t* sa_ptr = smem + s * STAGE_BYTES;
-        const int valid = rows - mb * BK;  // reduction rows of this block that belong to e
-        if (valid < BK) {
-          // zero rows [valid, 64) of every 64-wide chunk of both operands (128 B per row);
-          // lane -> 16-byte column lane % 8 of chunks lane / 8, lane / 8 + 4
-          constexpr int CHUNKS = (BM + BN) / 64;
-          for (int c = lane >> 3; c < CHUNKS; c += 4) {
-            uint8_t* col = sa_ptr + c * CHUNK_BYTES + (lane & 7) * 16;
-            for (int row = valid; row < BK; ++row) *reinterpret_cast<uint4*>(col + row * 128) = make_uint4(0, 0, 0, 0);
-          }
-          fence_proxy_async_smem();
-        }
-        __syncwarp();
-        if (lane == 0) {
-          const uint32_t sa = smem_u32(sa_ptr);
-          const uint32_t sb = sa + A_STAGE_BYTES;
-          const uint64_t da = make_smem_desc(sa, CHUNK_BYTES, 1024);
-          const uint64_t db = make_smem_desc(sb, CHUNK_BYTES, 1024);
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t adv = (uint64_t)((k * UMMA_K * 128) >> 4);
-            if (!(p.debug & 4)) umma_f16(d_tmem, da + adv, db + adv, p.idesc, (mb | k) != 0);
-          }
-          umma_commit(&ctl->empty[s]);
-        }
-        __syncwarp();
-      }
-      if (ok && lane == 0) umma_commit(&ctl->tmem_full[acc]);
-      __syncwarp();
-      ++acc_it;
-    }
-  } else {
-    const int quarter = warp & 3;
-    const int row_in_tile = quarter * 32 + lane;
-    const bool vec = ((p.K * (int)dtype_size(p.dtype_out)) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
-    uint32_t acc_it = 0;
-    bool ok = true;
-    for (int64_t r = 0; r < rounds && ok; ++r) {
-      const int64_t item = item_of(r);
-      if (item >= total_items) continue;
-      const int e = sorted[item / per_expert];
-      const int j = (int)(item % per_expert);
-      const int n0 = (j % n_tiles) * BM;
-      const int k0 = (j / n_tiles) * BN;
-      const int rows = row_start[e + 1] - row_start[e];
-      const int n = n0 + row_in_tile;
-      const bool row_ok = n < p.N;
-      const int64_t out_row = ((int64_t)e * p.N + n) * p.K;
-      if (rows == 0) {
-        uint32_t z[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) z[i] = 0;
-        for (int c = 0; c < BN; c += 32) {
-          if (k0 + c >= p.K) break;
-          if (row_ok) store_acc(p.out, p.dtype_out, out_row + k0 + c, z, min(32, p.K - (k0 + c)), vec);
-        }
-        continue;
-      }
-      const uint32_t acc = acc_it & 1;
-      const uint32_t acc_ph = (acc_it >> 1) & 1;
-      if (!mbar_wait(&ctl->tmem_full[acc], acc_ph, abort_flag, W_TMEM_FULL)) { ok = false; break; }
-      tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        if (k0 + c >= p.K) break;
-        uint32_t v[32];
-        if (!(p.debug & 2)) {
-          tmem_ld_32x32(taddr + c, v);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = c + i;
-        }
-        if (row_ok && !(p.debug & 1)) store_acc(p.out, p.dtype_out, out_row + k0 + c, v, min(32, p.K - (k0 + c)), vec);
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->tmem_empty[acc]);
-      ++acc_it;
-    }
-  }
-
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, TMEM_COLS);
-  }
-}
-
-// ---------------------------------------------------------------------------------------
 // Forward with the NF4 weight decoded into the B stage.
 // Per k-block the producer brings the activation tile (TMA, swizzled) and the packed
 // weight bytes of the 256 x 64 weight tile (TMA, 8 KB, linear) into shared memory; eight
@@ -758,6 +548,7 @@ tc_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 }  // namespace moe
 
 #include "tc_gemm_pair.cuh"
+#include "tc_gemm_dw.cuh"
 
 namespace moe {
 namespace tc {
@@ -872,7 +663,8 @@ static int pair_grouped_gemm(int which, const void* a, const void* b, const void
   GemmParams p;
   p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags();
   const int fmt = dtype_in == MOE_BF16 ? 1 : 0;
-  CUtensorMap mw, mx, mo;
+  p.group_maps = nullptr;
+  CUtensorMap mw, mx;
   int st;
   if (which == 0 || which == 1) {
     // A = weight (accumulator rows), B = activations (accumulator columns = tokens)
@@ -894,31 +686,99 @@ static int pair_grouped_gemm(int which, const void* a, const void* b, const void
     }
     return launch_status();
   }
-  // dW: a = x (M,K), b = dy (M,N), out (E,N,K) 16-bit
-  if ((st = make_map(&mw, dtype_in, b, (uint64_t)N, (uint64_t)M, 0, BK)) != MOE_OK) return st;
-  if ((st = make_map(&mx, dtype_in, a, (uint64_t)K, (uint64_t)M, 0, BK)) != MOE_OK) return st;
-  if ((st = make_map(&mo, dtype_out, out, (uint64_t)K, (uint64_t)N, (uint64_t)E, 128)) != MOE_OK) return st;
-  p.idesc = make_idesc(fmt, 1, 1, 256, 256);
-  const int bytes = 5 * 2 * PAIR_HALF_BYTES + 2 * 128 * 128 + (int)sizeof(PairControl) + 3 * (E + 1) * 4 + 1024;
-  if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
-  if ((st = set_smem(pair_dw_kernel, bytes)) != MOE_OK) return st;
-  const int grid = 2 * resident_pairs(pair_dw_kernel, bytes);
-  pair_dw_kernel<<<grid, PAIR_THREADS, bytes, stream>>>(mw, mx, mo, p);
+  return MOE_ERR_UNSUPPORTED;
+}
+
+// Launch with a cluster of 2 CTAs.
+template <typename... KArgs, typename... Args>
+static int launch_pair(void (*kernel)(KArgs...), int grid, int smem_bytes, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cuda_status(cudaLaunchKernelEx(&cfg, kernel, args...));
+}
+
+// dW on tensor cores: per-expert maps are built into `ws`, then one GEMM launch.
+static int dw_grouped_gemm(const void* x, const void* dy, const void* m_sizes, int ms64, void* out, int64_t M, int N,
+                           int K, int E, int dtype_in, int dtype_out, void* ws, size_t ws_bytes, cudaStream_t stream,
+                           bool single_cta) {
+  using namespace tc;
+  if (ws == nullptr || ((uintptr_t)ws & 127) || ws_bytes < (size_t)2 * E * sizeof(CUtensorMap)) return MOE_ERR_WORKSPACE;
+  GemmParams p;
+  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags();
+  p.group_maps = reinterpret_cast<const CUtensorMap*>(ws);
+  const int fmt = dtype_in == MOE_BF16 ? 1 : 0;
+  int st;
+  GroupMapTemplates tm;
+  tm.count = 2;
+  if ((st = make_map(&tm.t[GM_DY], dtype_in, dy, (uint64_t)N, (uint64_t)M, 0, BK)) != MOE_OK) return st;
+  if ((st = make_map(&tm.t[GM_X], dtype_in, x, (uint64_t)K, (uint64_t)M, 0, BK)) != MOE_OK) return st;
+  const int gm_smem = 8 * 128 + 2 * (E + 1) * 4 + 128;
+  build_group_maps_kernel<<<(E + 7) / 8, 256, gm_smem, stream>>>(tm, m_sizes, ms64, E, M, reinterpret_cast<CUtensorMap*>(ws));
+  if ((st = launch_status()) != MOE_OK) return st;
+
+  const bool staged = dtype_out != MOE_F32;
+  CUtensorMap mo;
+  if (staged) {
+    if ((st = make_map(&mo, dtype_out, out, (uint64_t)K, (uint64_t)N, (uint64_t)E, 128)) != MOE_OK) return st;
+  } else {
+    memset(&mo, 0, sizeof(mo));
+  }
+  const int tables = 2 * (E + 1) * 4 + (int)sizeof(DwControl) + 1024 + 2 * 128 * 128;
+  const bool pair = !single_cta && staged && N >= 192 && K >= 192 && (((uintptr_t)out & 15) == 0);
+  if (pair) {
+    constexpr int ST = 5;
+    const int bytes = ST * 4 * BK * 128 + tables;
+    if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
+    p.idesc = make_idesc(fmt, 1, 1, 256, 256);
+    auto kern = dw_kernel<true, 256, ST>;
+    if ((st = set_smem(kern, bytes)) != MOE_OK) return st;
+    return launch_pair(kern, 2 * resident_pairs(kern, bytes), bytes, stream, mo, p);
+  }
+  if (K > 128) {
+    p.idesc = make_idesc(fmt, 1, 1, BM, 256);
+    const int bytes4 = 4 * 6 * BK * 128 + tables;
+    if (bytes4 <= SMEM_LIMIT) {
+      auto kern = dw_kernel<false, 256, 4>;
+      if ((st = set_smem(kern, bytes4)) != MOE_OK) return st;
+      kern<<<sm_count(), 192, bytes4, stream>>>(mo, p);
+    } else {
+      const int bytes3 = 3 * 6 * BK * 128 + tables;
+      if (bytes3 > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
+      auto kern = dw_kernel<false, 256, 3>;
+      if ((st = set_smem(kern, bytes3)) != MOE_OK) return st;
+      kern<<<sm_count(), 192, bytes3, stream>>>(mo, p);
+    }
+  } else {
+    p.idesc = make_idesc(fmt, 1, 1, BM, 128);
+    const int bytes = 6 * 4 * BK * 128 + tables;
+    if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
+    auto kern = dw_kernel<false, 128, 6>;
+    if ((st = set_smem(kern, bytes)) != MOE_OK) return st;
+    kern<<<sm_count(), 192, bytes, stream>>>(mo, p);
+  }
   return launch_status();
 }
 
 // which: 0 forward, 1 dX, 2 dW (a = x, b = dy).  single_cta selects the one-CTA kernels.
 int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes, int ms64, void* out,
-                    int64_t M, int N, int K, int E, int dtype_in, int dtype_out, cudaStream_t stream,
-                    bool single_cta) {
+                    int64_t M, int N, int K, int E, int dtype_in, int dtype_out, void* ws, size_t ws_bytes,
+                    cudaStream_t stream, bool single_cta) {
   using namespace tc;
   bind_context_once();
+  if (which == 2)
+    return dw_grouped_gemm(a, b, m_sizes, ms64, out, M, N, K, E, dtype_in, dtype_out, ws, ws_bytes, stream, single_cta);
   if (!single_cta) {
     // a pair covers 256 weight rows (and, for dW, 256 weight columns): narrower problems
     // would leave most of the tile empty
-    const bool pair_ok = which != 2 ? (which == 0 ? N >= 192 : N >= 192)
-                                    : (N >= 192 && K >= 192 && (dtype_out == MOE_BF16 || dtype_out == MOE_F16) &&
-                                       (((uintptr_t)out & 15) == 0));
+    const bool pair_ok = N >= 192;
     if (pair_ok) return pair_grouped_gemm(which, a, b, m_sizes, ms64, out, M, N, K, E, dtype_in, dtype_out, stream);
   }
   GemmParams p;
@@ -947,26 +807,8 @@ int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes
 #undef MOE_TC_LAUNCH
     return launch_status();
   }
-  // dW: accumulator rows = N (out_features), columns = K (in_features)
-  const bool wide = K > 128;
-  const int bn = wide ? 256 : 128;
-  if ((st = make_map(&ma, dtype_in, b, (uint64_t)N, (uint64_t)M, 0, BK)) != MOE_OK) return st;  // dy (M,N)
-  if ((st = make_map(&mb, dtype_in, a, (uint64_t)K, (uint64_t)M, 0, BK)) != MOE_OK) return st;  // x  (M,K)
-  p.idesc = make_idesc(fmt, 1, 1, BM, bn);
-  if (wide) {
-    const int bytes = smem_bytes_for<256>(E, 3);
-    if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
-    if ((st = set_smem(tc_dw_kernel<256>, bytes)) != MOE_OK) return st;
-    tc_dw_kernel<256><<<grid, NUM_THREADS, bytes, stream>>>(ma, mb, p);
-  } else {
-    const int bytes = smem_bytes_for<128>(E, 3);
-    if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
-    if ((st = set_smem(tc_dw_kernel<128>, bytes)) != MOE_OK) return st;
-    tc_dw_kernel<128><<<grid, NUM_THREADS, bytes, stream>>>(ma, mb, p);
-  }
-  return launch_status();
+  return MOE_ERR_UNSUPPORTED;
 }
-
 
 bool tc_nf4_eligible(const void* x, const void* packed, const void* absmax, const void* out, int64_t M, int N, int K,
                      int E, int blocksize, int dtype_in, int dtype_out) {
@@ -982,7 +824,7 @@ int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code,
   using namespace tc;
   bind_context_once();
   GemmParams p;
-  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags();
+  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags(); p.group_maps = nullptr;
   p.idesc = make_idesc(dtype_in == MOE_BF16 ? 1 : 0, 0, 0, BM, NF4_BN);
   Nf4Params q;
   q.code = code; q.absmax = absmax; q.shift = 0;
