@@ -30,6 +30,8 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
 
 struct GemmParams {
   const void* m_sizes;
+  const void* a;   // activations (forward / dX) or x (dW), as passed by the caller
+  const void* b;   // weights (forward / dX) or dy (dW)
   void* out;
   int64_t M;
   int N, K, E;
@@ -37,7 +39,8 @@ struct GemmParams {
   int dtype_out;  // MOE_F32 / MOE_BF16 / MOE_F16
   uint32_t idesc;
   const CUtensorMap* group_maps;  // per-expert tensor maps in workspace ([slot][expert]), or null
-  int debug;      // experiment switches (MOE_B200_DEBUG): 1 = no global stores, 2 = no TMEM loads, 4 = no MMA
+  int debug;      // experiment switches (MOE_B200_DEBUG): 1 = no global stores, 2 = no TMEM loads, 4 = no MMA,
+                  // 32 = 512-token pair kernel (tc_gemm_pair2.cuh) instead of the 256-token one
 };
 
 struct Control {
@@ -549,6 +552,7 @@ tc_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
 #include "tc_gemm_pair.cuh"
 #include "tc_gemm_dw.cuh"
+#include "tc_gemm_pair2.cuh"
 
 namespace moe {
 namespace tc {
@@ -657,10 +661,15 @@ static int resident_pairs(Kern kernel, int smem_bytes) {
   return n < cap ? n : cap;
 }
 
+template <typename... KArgs, typename... Args>
+static int launch_pair(void (*kernel)(KArgs...), int grid, int smem_bytes, cudaStream_t stream, Args... args);
+
 static int pair_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes, int ms64, void* out,
-                             int64_t M, int N, int K, int E, int dtype_in, int dtype_out, cudaStream_t stream) {
+                             int64_t M, int N, int K, int E, int dtype_in, int dtype_out, void* ws, size_t ws_bytes,
+                             cudaStream_t stream) {
   using namespace tc;
   GemmParams p;
+  p.a = a; p.b = b;
   p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags();
   const int fmt = dtype_in == MOE_BF16 ? 1 : 0;
   p.group_maps = nullptr;
@@ -673,7 +682,30 @@ static int pair_grouped_gemm(int which, const void* a, const void* b, const void
     if (st != MOE_OK) return st;
     if ((st = make_map(&mx, dtype_in, a, (uint64_t)K, (uint64_t)M, 0, 128)) != MOE_OK) return st;
     p.idesc = make_idesc(fmt, which == 1, 0, 256, 0);  // N field is filled per tile
-    const int bytes = 6 * 2 * PAIR_HALF_BYTES + (int)sizeof(PairControl) + 2 * (E + 1) * 4 + 1024;
+    {
+      // 512-token tiles on per-expert maps (needs workspace and the larger shared-memory layout)
+      const int bytes2 = P2_STAGES * P2_STAGE_BYTES + 4 * P2_STAGING_BYTES + (int)sizeof(PairControl) + 2 * (E + 1) * 4 + 1024;
+      const bool ws_ok = ws != nullptr && (((uintptr_t)ws & 127) == 0) && ws_bytes >= (size_t)2 * E * sizeof(CUtensorMap);
+      if (ws_ok && bytes2 <= SMEM_LIMIT && (p.debug & 32) && (((uintptr_t)out & 15) == 0 || dtype_out == MOE_F32)) {
+        GroupMapTemplates tm;
+        tm.count = dtype_out == MOE_F32 ? 1 : 2;
+        tm.t[GM_IN] = mx;
+        if (tm.count == 2 && (st = make_map(&tm.t[GM_OUT], dtype_out, out, (uint64_t)N, (uint64_t)M, 0, 64)) != MOE_OK) return st;
+        const int gm_smem = 8 * 128 + 2 * (E + 1) * 4 + 128;
+        build_group_maps_kernel<<<(E + 7) / 8, 256, gm_smem, stream>>>(tm, m_sizes, ms64, E, M, reinterpret_cast<CUtensorMap*>(ws));
+        if ((st = launch_status()) != MOE_OK) return st;
+        p.group_maps = reinterpret_cast<const CUtensorMap*>(ws);
+        if (which == 0) {
+          auto kern = pair_fwd2_kernel<false>;
+          if ((st = set_smem(kern, bytes2)) != MOE_OK) return st;
+          return launch_pair(kern, 2 * resident_pairs(kern, bytes2), bytes2, stream, mw, p);
+        }
+        auto kern = pair_fwd2_kernel<true>;
+        if ((st = set_smem(kern, bytes2)) != MOE_OK) return st;
+        return launch_pair(kern, 2 * resident_pairs(kern, bytes2), bytes2, stream, mw, p);
+      }
+    }
+    const int bytes = PAIR_STAGES * 2 * PAIR_HALF_BYTES + (int)sizeof(PairControl) + 2 * (E + 1) * 4 + 1024;
     if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
     if (which == 0) {
       if ((st = set_smem(pair_fwd_kernel<false>, bytes)) != MOE_OK) return st;
@@ -779,7 +811,7 @@ int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes
     // a pair covers 256 weight rows (and, for dW, 256 weight columns): narrower problems
     // would leave most of the tile empty
     const bool pair_ok = N >= 192;
-    if (pair_ok) return pair_grouped_gemm(which, a, b, m_sizes, ms64, out, M, N, K, E, dtype_in, dtype_out, stream);
+    if (pair_ok) return pair_grouped_gemm(which, a, b, m_sizes, ms64, out, M, N, K, E, dtype_in, dtype_out, ws, ws_bytes, stream);
   }
   GemmParams p;
   p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags();

@@ -20,6 +20,7 @@ namespace moe {
 namespace tc {
 
 constexpr int PAIR_THREADS = 192;
+constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_TOKENS = 256;             // token columns per tile (MMA N), upper bound
 constexpr int PAIR_HALF_BYTES = 128 * BK * 2;  // 16 KB: 128 rows x 64 x 16-bit
 
@@ -47,7 +48,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                 const GemmParams p) {
   constexpr int STAGE_BYTES = 2 * PAIR_HALF_BYTES;  // A half-tile + B half-tile per CTA
-  constexpr int STAGES = 6;
+  constexpr int STAGES = PAIR_STAGES;
   constexpr uint32_t TMEM_COLS = 512;  // two accumulators of up to 256 token columns
 
   extern __shared__ uint8_t smem_raw[];
