@@ -165,6 +165,142 @@ def config_dict(args, cfg):
             "parallelism": "single GPU" if args.gpus == 1 else f"expert parallel ep{args.gpus} (all-to-all dispatch/combine)"}
 
 
+def time_cuda(fn, iters: int = 20, warmup: int = 3, flush=None) -> float:
+    """Median device time of fn() in ms (CUDA events around every call; an optional buffer larger
+    than L2 is rewritten between calls so that small inputs are not served from cache)."""
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.add_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        times.append(a.elapsed_time(b))
+    return float(np.median(times))
+
+
+def run_kernel_suite(args):
+    """Roofline figures for the HBM-bound kernels of the path and for the NF4 / LoRA / block
+    compositions.  One JSON line per measurement."""
+    import __graft_entry__ as entry
+
+    entry.build()
+    from qwen3_moe_fused import _lib
+    from qwen3_moe_fused.grouped_gemm.forward import grouped_gemm_forward
+    from qwen3_moe_fused.grouped_gemm.forward_4bit import grouped_gemm_forward_4bit
+    from qwen3_moe_fused.kernels.fast_lora import fast_lora
+    from qwen3_moe_fused.kernels.indexing import get_expert_counts_and_idx
+    from qwen3_moe_fused.kernels.routing import _combine, _gather_rows, softmax_topk
+    from qwen3_moe_fused.kernels.silu_mul import silu_mul_backward_inplace, silu_mul_forward
+    from qwen3_moe_fused.moe_block import moe_block_forward
+    from qwen3_moe_fused.quantize.nf4 import dequantize_4bit, quantize_nf4
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks, kind = measured_peaks()
+    hbm = peaks["hbm_gbs"]
+    bf = torch.bfloat16
+    flush = torch.zeros(64 * 1024 * 1024, device=dev, dtype=torch.float32)  # 256 MB
+    torch.manual_seed(0)
+
+    def emit(name, ms, nbytes=None, flops=None, **extra):
+        line = {"suite": "kernels", "kernel": name, "ms": ms}
+        if nbytes is not None:
+            line.update(algorithmic_bytes=nbytes, gbs=nbytes / ms / 1e6, frac_of_hbm=nbytes / ms / 1e6 / hbm, hbm_peak_gbs=hbm, peak_kind=kind)
+        if flops is not None:
+            line.update(flops=flops, tflops=flops / ms / 1e9)
+        line.update(extra)
+        print(json.dumps(line), flush=True)
+
+    # ---- SiLU-mul at the down-projection input size ----
+    n = 65536 * 768
+    e, g, dh = (torch.randn(n, device=dev, dtype=bf) for _ in range(3))
+    emit("silu_mul_fwd bf16 65536x768", time_cuda(lambda: silu_mul_forward(e, g)), 3 * 2 * n)
+    emit("silu_mul_bwd_inplace bf16 65536x768", time_cuda(lambda: silu_mul_backward_inplace(dh, e, g)), 6 * 2 * n)
+    del e, g, dh
+
+    # ---- router ----
+    for T in (8192, 16384, 1 << 20):
+        logits = torch.randn(T, 128, device=dev)
+        fl = flush if T < (1 << 20) else None
+        emit(f"router softmax-top8 fp32 logits T={T}", time_cuda(lambda: softmax_topk(logits, 8, True, bf), flush=fl),
+             4 * T * 128 + T * 8 * (8 + 2))
+        del logits
+
+    # ---- sort by expert ----
+    for M in (65536, 131072, 1 << 24):
+        s = torch.randint(0, 128, (M,), device=dev)
+        fl = flush if M < (1 << 24) else None
+        emit(f"sort_by_expert int64 ids M={M} E=128", time_cuda(lambda: get_expert_counts_and_idx(s, 128), flush=fl), M * (8 + 8))
+        del s
+
+    # ---- expand+gather and combine at the block size (16384 tokens, top-8, hidden 2048) ----
+    T, k, H = 16384, 8, 2048
+    hidden = torch.randn(T, H, device=dev, dtype=bf)
+    sel = torch.randint(0, 128, (T * k,), device=dev)
+    _, sort_idx, inv_sort_idx = get_expert_counts_and_idx(sel, 128)
+    w = torch.rand(T, k, device=dev, dtype=bf)
+    emit("gather_rows bf16 16384 tokens x8 x2048", time_cuda(lambda: _gather_rows(hidden, sort_idx, k)), 2 * (T * H + T * k * H) + 4 * T * k)
+    y = torch.randn(T * k, H, device=dev, dtype=bf)
+    emit("combine bf16 16384 tokens x8 x2048", time_cuda(lambda: _combine(y, inv_sort_idx, w)), 2 * (T * k * H + T * H) + 6 * T * k)
+    del hidden, y
+
+    # ---- NF4: decode alone, fused forward vs decode + GEMM (BASELINE config 4) ----
+    E, N, K = 128, 1536, 2048
+    wfull = (torch.randn(E, N, K, device=dev) * 0.02).to(bf)
+    packed, state = quantize_nf4(wfull, 64)
+    del wfull
+    nel = E * N * K
+    emit("nf4_dequant 128x1536x2048 -> bf16", time_cuda(lambda: dequantize_4bit(packed, state, bf)), nel // 2 + nel // 64 * 4 + nel * 2)
+    for tokens in (512, 4096, 32768):
+        M = tokens * 8
+        x = torch.randn(M, K, device=dev, dtype=bf)
+        m_sizes = torch.full((E,), M // E, device=dev, dtype=torch.int32)
+        flops = 2.0 * M * N * K
+        fused = time_cuda(lambda: grouped_gemm_forward_4bit(x, packed, state, m_sizes), iters=10)
+        unfused = time_cuda(lambda: grouped_gemm_forward(x, dequantize_4bit(packed, state, bf), m_sizes), iters=10)
+        wbytes = nel // 2 + nel // 64 * 4
+        emit(f"nf4 fused forward M={M}", fused, wbytes + 2 * M * (K + N), flops, unfused_ms=unfused, speedup_vs_unfused=unfused / fused)
+        del x
+    # ---- fused-LoRA expert MLP, rank 16, NF4 base, forward + backward ----
+    I, Hh, R = 768, 2048, 16
+    mk = lambda *shape, sc: (torch.randn(*shape, device=dev) * sc).to(bf)
+    G, U, Wd = mk(E, I, Hh, sc=0.02), mk(E, I, Hh, sc=0.02), mk(E, Hh, I, sc=0.02)
+    (Gq, Gs), (Uq, Us), (Wq, Ws) = (quantize_nf4(t, 64) for t in (G, U, Wd))
+    del G, U, Wd
+    lor = [mk(E, R, Hh, sc=0.02), mk(E, I, R, sc=0.01), mk(E, R, Hh, sc=0.02), mk(E, I, R, sc=0.01), mk(E, R, I, sc=0.02), mk(E, Hh, R, sc=0.01)]
+    for t in lor:
+        t.requires_grad_()
+    for tokens in (512, 4096):
+        M = tokens * 8
+        x = torch.randn(M, Hh, device=dev, dtype=bf, requires_grad=True)
+        m_sizes = torch.full((E,), M // E, device=dev, dtype=torch.int32)
+        dy = torch.randn(M, Hh, device=dev, dtype=bf)
+
+        def step():
+            out = fast_lora(x, Gq, Gs, lor[0], lor[1], 1.0, Uq, Us, lor[2], lor[3], 1.0, Wq, Ws, lor[4], lor[5], 1.0, m_sizes)
+            out.backward(dy)
+
+        emit(f"fast_lora NF4 base r=16 fwd+bwd M={M}", time_cuda(step, iters=5, warmup=2), flops=3 * 3 * 2.0 * M * I * Hh)
+        del x, dy
+    del packed, state, Gq, Uq, Wq, lor
+
+    # ---- one full MoE block forward at the block workload (16384 tokens) ----
+    T = 16384
+    hidden = torch.randn(1, T, 2048, device=dev, dtype=bf)
+    gate = mk(128, 2048, sc=0.02)
+    gp, up, dp = mk(128, 768, 2048, sc=0.02), mk(128, 768, 2048, sc=0.02), mk(128, 2048, 768, sc=0.02)
+    with torch.no_grad():
+        ms = time_cuda(lambda: moe_block_forward(hidden, gate, gp, up, dp, 8, True), iters=10)
+    emit("moe block forward, 16384 tokens, 128 experts top-8", ms, flops=2.0 * T * 2048 * 128 + 3 * 2.0 * T * 8 * 768 * 2048,
+         tokens_per_s=T / ms * 1e3, tokens_per_s_48_layers=T / ms * 1e3 / 48)
+    assert _lib.read_error_flag() == 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -174,6 +310,8 @@ def main():
     ap.add_argument("--workload", default="gate_up", choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-rows", type=int, default=4096, help="rows of the bounded CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--suite", default="hotpath", choices=["hotpath", "kernels"],
+                    help="hotpath: the contract line (default); kernels: roofline lines of the surrounding kernels")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (reduced profiling case)")
     ap.add_argument("--experts", type=int, default=None, help="override the expert count (reduced profiling case)")
@@ -188,6 +326,9 @@ def main():
         cfg["E"] = args.experts
     if args.impl == "reference":
         run_reference(args, cfg)
+        return
+    if args.suite == "kernels":
+        run_kernel_suite(args)
         return
 
     import __graft_entry__ as entry
