@@ -73,6 +73,22 @@ int moe_sort_by_expert(const void* s, int s_dtype, int64_t M, int E,
                        int32_t* counts, int32_t* inv_idx, int32_t* idx,
                        void* ws, size_t ws_bytes, void* stream);
 
+/* moe_sort_by_expert without a workspace argument, for callers that cannot allocate device
+ * memory where they call it (no cudaMalloc allowed there, or no allocator at all): the scratch
+ * is a fixed array of moe_sort_static_capacity_bytes() (256 KB) inside the library's device
+ * image.  Same inputs, outputs and results as moe_sort_by_expert.
+ *   - Sizes whose scratch need (moe_sort_workspace_bytes(M, E)) exceeds the capacity are
+ *     rejected with MOE_ERR_WORKSPACE and nothing is launched.
+ *   - The call itself allocates nothing.  The first call on each device looks up the array's
+ *     device address (with that device current); make that first call before any stream capture.
+ *   - All calls on a device share the one array: two calls whose kernels can overlap on the GPU
+ *     (different streams, no dependency between them) race.  Calls on one stream are safe; the
+ *     array keeps the last call's contents and nothing in it needs clearing between calls.
+ * This entry point has no counterpart in the reference. */
+size_t moe_sort_static_capacity_bytes(void);
+int moe_sort_by_expert_static(const void* s, int s_dtype, int64_t M, int E,
+                              int32_t* counts, int32_t* inv_idx, int32_t* idx, void* stream);
+
 /* Begin/end row of every expert in an already sorted id vector.
  * Replaces qwen3_moe_fused/kernels/indexing.py:7-14 (get_batch_begins_ends).
  *   begins_ends (E,2) int32: [e,0] = #rows with id < e, [e,1] = #rows with id <= e */

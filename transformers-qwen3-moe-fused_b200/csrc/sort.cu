@@ -234,3 +234,74 @@ MOE_API int moe_batch_begins_ends(const void* s_sorted, int s_dtype, int64_t M, 
   begins_ends_kernel<<<1, 1024, E * sizeof(int32_t), stream>>>(s_sorted, s_dtype == MOE_I64, M, E, begins_ends);
   return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------
+// Sort without caller-provided workspace.
+//
+// Some hosts of this library cannot hand it scratch memory: a caller that must not call
+// cudaMalloc at that point (inside a region where allocation is forbidden or would
+// synchronise, such as a latency-critical serving loop or a plugin interface that only
+// passes inputs and outputs), or one that has no allocator of its own at all.  For them the
+// per-chunk histograms and expert offsets live in the fixed device array below, which every
+// GPU that loads the library holds until the process exits.
+// ---------------------------------------------------------------------------------------
+namespace moe {
+
+constexpr size_t SORT_STATIC_BYTES = 256 * 1024;  // e.g. 262144 rows with 128 experts need 66 KB
+static __device__ __align__(256) unsigned char g_sort_scratch[SORT_STATIC_BYTES];
+
+// Device address of g_sort_scratch on the current device.  In host code the array's name
+// is only a handle for the runtime, not a device pointer, so the address is looked up once
+// per device (with that device current) and cached.
+static int sort_static_scratch(void** out) {
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_status(e);
+  if (dev < 0 || dev >= 64) return MOE_ERR_DEVICE;
+  void* p = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    e = cudaGetSymbolAddress(&p, g_sort_scratch);
+    if (e != cudaSuccess) return cuda_status(e);
+    if (p == nullptr) return MOE_ERR_DEVICE;
+    __atomic_store_n(&cached[dev], p, __ATOMIC_RELEASE);
+  }
+  *out = p;
+  return MOE_OK;
+}
+
+}  // namespace moe
+
+MOE_API size_t moe_sort_static_capacity_bytes(void) { return moe::SORT_STATIC_BYTES; }
+
+MOE_API int moe_sort_by_expert_static(const void* s, int s_dtype, int64_t M, int E, int32_t* counts,
+                                      int32_t* inv_idx, int32_t* idx, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!is_int_dtype(s_dtype)) return MOE_ERR_DTYPE;
+  if (M < 0 || E <= 0 || E > SORT_MAX_E || M > 0x7fffffffLL) return MOE_ERR_SHAPE;
+  if (counts == nullptr || (M > 0 && s == nullptr)) return MOE_ERR_NULL;
+  if ((inv_idx == nullptr) != (idx == nullptr)) return MOE_ERR_NULL;
+  // the fixed array bounds the problem size: refuse anything that would not fit
+  if (moe_sort_workspace_bytes(M, E) > SORT_STATIC_BYTES) return MOE_ERR_WORKSPACE;
+  void* scratch = nullptr;
+  const int st = sort_static_scratch(&scratch);
+  if (st != MOE_OK) return st;
+  // Every word of the scratch that the scan and scatter kernels read is written first by
+  // the histogram and scan kernels of this same call, so nothing has to be cleared even
+  // though the array still holds the previous call's contents.
+  const int is64 = s_dtype == MOE_I64;
+  const int nchunks = (int)sort_chunks(M);
+  int32_t* hist = (int32_t*)scratch;
+  int32_t* offsets = hist + (size_t)nchunks * E;
+  if (nchunks > 0) sort_hist_kernel<<<nchunks, SORT_THREADS, E * sizeof(int32_t), stream>>>(s, is64, M, E, hist);
+  sort_scan_kernel<<<1, 1024, 0, stream>>>(hist, nchunks, E, counts, idx ? offsets : nullptr);
+  if (idx != nullptr && nchunks > 0) {
+    const size_t smem = (size_t)SORT_WARPS * E * sizeof(int32_t);
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return cuda_status(e);
+    }
+    sort_scatter_kernel<<<nchunks, SORT_THREADS, smem, stream>>>(s, is64, M, E, hist, offsets, inv_idx, idx);
+  }
+  return launch_status();
+}

@@ -29,6 +29,8 @@ SIGNATURES = {
     "moe_get_gemm_path": (_I, []),
     "moe_sort_workspace_bytes": (_Z, [_L, _I]),
     "moe_sort_by_expert": (_I, [_P, _I, _L, _I, _P, _P, _P, _P, _Z, _P]),
+    "moe_sort_static_capacity_bytes": (_Z, []),
+    "moe_sort_by_expert_static": (_I, [_P, _I, _L, _I, _P, _P, _P, _P]),
     "moe_batch_begins_ends": (_I, [_P, _I, _L, _I, _P, _P]),
     "moe_grouped_gemm_workspace_bytes": (_Z, [_I, _L, _I, _I, _I]),
     "moe_grouped_gemm_fwd": (_I, [_P, _P, _P, _I, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
