@@ -11,7 +11,7 @@ constexpr int EW_THREADS = 256;
 
 static inline int ew_grid(int64_t work_items) {
   const int64_t want = (work_items + EW_THREADS - 1) / EW_THREADS;
-  const int64_t cap = (int64_t)sm_count() * 8;
+  const int64_t cap = (int64_t)sm_count() * 16;
   int64_t g = want < cap ? want : cap;
   return (int)(g < 1 ? 1 : g);
 }

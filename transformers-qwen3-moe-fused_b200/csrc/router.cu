@@ -82,12 +82,89 @@ router_kernel(const TL* __restrict__ logits, int64_t T, int E, int k, int norm,
 
 // k is limited to 32 (one winner per lane); Qwen3-MoE uses 8.
 
+// Faster form for k <= 8: eight lanes per token (four tokens per warp), E/8 logits per lane.
+// The winners are chosen on the logits (the same order as on the probabilities, without the
+// rounding of exp in between); only the softmax denominator needs every exponential.
+template <typename TL, typename TW, int NV>
+__global__ void __launch_bounds__(RT_WARPS * 32)
+router8_kernel(const TL* __restrict__ logits, int64_t T, int E, int k, int norm,
+               TW* __restrict__ weights, int64_t* __restrict__ experts) {
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & 7;                 // lane inside the token's group of 8
+  const unsigned gmask = 0xffu << (lane & 24);
+  const int64_t group_global = ((int64_t)blockIdx.x * (RT_WARPS * 32) + threadIdx.x) >> 3;
+  const int64_t group_stride = ((int64_t)gridDim.x * (RT_WARPS * 32)) >> 3;
+  for (int64_t t0 = group_global - (lane >> 3); t0 < T; t0 += group_stride) {
+    // t0 is the first token of this warp's four; all lanes of the warp loop together
+    const int64_t t = t0 + (lane >> 3);
+    const bool live = t < T;
+    const TL* row = logits + (live ? t : 0) * E;
+    float x[NV];
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int e = sub + 8 * v;
+      x[v] = (live && e < E) ? to_f32(row[e]) : -CUDART_INF_F;
+      mx = fmaxf(mx, x[v]);
+    }
+#pragma unroll
+    for (int d = 4; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    float sum = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) sum += (sub + 8 * v < E) ? __expf(x[v] - mx) : 0.f;
+#pragma unroll
+    for (int d = 4; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+    float top_sum = 0.f, my_p = 0.f;
+    int my_e = 0;
+    for (int r = 0; r < k; ++r) {
+      float bv = -CUDART_INF_F;
+      int be = 0x7fffffff;
+#pragma unroll
+      for (int v = 0; v < NV; ++v)
+        if (x[v] > bv) { bv = x[v]; be = sub + 8 * v; }  // ascending e inside a lane: first hit wins
+#pragma unroll
+      for (int d = 4; d > 0; d >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
+        const int oe = __shfl_xor_sync(0xffffffffu, be, d);
+        if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+      }
+#pragma unroll
+      for (int v = 0; v < NV; ++v)
+        if (sub + 8 * v == be) x[v] = -CUDART_INF_F;
+      const float pr = __expf(bv - mx) / sum;  // softmax probability of the winner
+      top_sum += pr;
+      if (r == sub) { my_p = pr; my_e = be; }
+    }
+    (void)gmask;
+    if (live && sub < k) {
+      experts[t * k + sub] = (int64_t)my_e;
+      weights[t * k + sub] = from_f32<TW>(norm ? my_p / top_sum : my_p);
+    }
+  }
+}
+
 template <typename TL, typename TW>
 static int launch_router(const void* logits, int64_t T, int E, int k, int norm, void* weights,
                          int64_t* experts, cudaStream_t stream) {
   const int64_t want = (T + RT_WARPS - 1) / RT_WARPS;
   const int64_t cap = (int64_t)sm_count() * 8;
   const int grid = (int)(want < cap ? want : cap);
+  if (k <= 8 && E <= 8 * 64 && E >= k) {
+    const int64_t want8 = (T + 31) / 32;  // 32 tokens per CTA
+    const int grid8 = (int)(want8 < cap ? want8 : cap);
+    const int nv = (E + 7) / 8;
+#define MOE_RT8_CASE(NV)                                                                             \
+  router8_kernel<TL, TW, NV><<<grid8, RT_WARPS * 32, 0, stream>>>((const TL*)logits, T, E, k, norm, \
+                                                                  (TW*)weights, experts)
+    if (nv <= 2) MOE_RT8_CASE(2);
+    else if (nv <= 4) MOE_RT8_CASE(4);
+    else if (nv <= 8) MOE_RT8_CASE(8);
+    else if (nv <= 16) MOE_RT8_CASE(16);
+    else if (nv <= 32) MOE_RT8_CASE(32);
+    else MOE_RT8_CASE(64);
+#undef MOE_RT8_CASE
+    return launch_status();
+  }
   const int npl = (E + 31) / 32;
 #define MOE_RT_CASE(NPL)                                                                           \
   router_kernel<TL, TW, NPL><<<grid, RT_WARPS * 32, 0, stream>>>((const TL*)logits, T, E, k, norm, \

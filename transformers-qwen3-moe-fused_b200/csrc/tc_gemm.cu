@@ -40,7 +40,8 @@ struct GemmParams {
   uint32_t idesc;
   const CUtensorMap* group_maps;  // per-expert tensor maps in workspace ([slot][expert]), or null
   int debug;      // experiment switches (MOE_B200_DEBUG): 1 = no global stores, 2 = no TMEM loads, 4 = no MMA,
-                  // 32 = 512-token pair kernel (tc_gemm_pair2.cuh) instead of the 256-token one
+                  // 32 = 512-token pair kernel (tc_gemm_pair2.cuh) instead of the 256-token one,
+                  // 64 = single-CTA NF4 kernel instead of the pair one
 };
 
 struct Control {
@@ -553,6 +554,7 @@ tc_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #include "tc_gemm_pair.cuh"
 #include "tc_gemm_dw.cuh"
 #include "tc_gemm_pair2.cuh"
+#include "tc_gemm_nf4.cuh"
 
 namespace moe {
 namespace tc {
@@ -642,10 +644,10 @@ static void bind_context_once() {
 
 // Number of CTA pairs that can be resident at once (persistent grid = 2 x this).
 template <typename Kern>
-static int resident_pairs(Kern kernel, int smem_bytes) {
+static int resident_pairs(Kern kernel, int smem_bytes, int threads = 192) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * sm_count());
-  cfg.blockDim = dim3(tc::PAIR_THREADS);
+  cfg.blockDim = dim3(threads);
   cfg.dynamicSmemBytes = smem_bytes;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
@@ -663,6 +665,8 @@ static int resident_pairs(Kern kernel, int smem_bytes) {
 
 template <typename... KArgs, typename... Args>
 static int launch_pair(void (*kernel)(KArgs...), int grid, int smem_bytes, cudaStream_t stream, Args... args);
+template <typename... KArgs, typename... Args>
+static int launch_pair_threads(void (*kernel)(KArgs...), int grid, int threads, int smem_bytes, cudaStream_t stream, Args... args);
 
 static int pair_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes, int ms64, void* out,
                              int64_t M, int N, int K, int E, int dtype_in, int dtype_out, void* ws, size_t ws_bytes,
@@ -724,9 +728,14 @@ static int pair_grouped_gemm(int which, const void* a, const void* b, const void
 // Launch with a cluster of 2 CTAs.
 template <typename... KArgs, typename... Args>
 static int launch_pair(void (*kernel)(KArgs...), int grid, int smem_bytes, cudaStream_t stream, Args... args) {
+  return launch_pair_threads(kernel, grid, 192, smem_bytes, stream, args...);
+}
+
+template <typename... KArgs, typename... Args>
+static int launch_pair_threads(void (*kernel)(KArgs...), int grid, int threads, int smem_bytes, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(192);
+  cfg.blockDim = dim3(threads);
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr;
@@ -863,6 +872,31 @@ int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code,
   while ((1 << q.shift) < blocksize) ++q.shift;
   CUtensorMap ma, mq;
   int st;
+  if (N >= 192 && !(p.debug & 64)) {
+    // CTA-pair form: 128 weight rows of packed codes per CTA and stage
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return MOE_ERR_DEVICE;
+    cuuint64_t dims[3] = {(cuuint64_t)K / 2, (cuuint64_t)N, (cuuint64_t)E};
+    cuuint64_t strides[2] = {(cuuint64_t)K / 2, (cuuint64_t)K / 2 * (cuuint64_t)N};
+    cuuint32_t box[3] = {BK / 2, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    if (fn(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(packed), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return MOE_ERR_UNSUPPORTED;
+    if ((st = make_map(&ma, dtype_in, x, (uint64_t)K, (uint64_t)M, 0, 128)) != MOE_OK) return st;
+    p.idesc = make_idesc(dtype_in == MOE_BF16 ? 1 : 0, 0, 0, 256, 0);
+    const int pbytes = NF4P_STAGES * NF4P_STAGE_BYTES + (int)sizeof(Nf4PairControl) + 2 * (E + 1) * 4 + 1024;
+    if (pbytes <= SMEM_LIMIT) {
+      if (dtype_in == MOE_BF16) {
+        auto kern = pair_fwd_nf4_kernel<true>;
+        if ((st = set_smem(kern, pbytes)) != MOE_OK) return st;
+        return launch_pair_threads(kern, 2 * resident_pairs(kern, pbytes, NF4P_THREADS), NF4P_THREADS, pbytes, stream, mq, ma, p, q);
+      }
+      auto kern = pair_fwd_nf4_kernel<false>;
+      if ((st = set_smem(kern, pbytes)) != MOE_OK) return st;
+      return launch_pair_threads(kern, 2 * resident_pairs(kern, pbytes, NF4P_THREADS), NF4P_THREADS, pbytes, stream, mq, ma, p, q);
+    }
+  }
   if ((st = make_map(&ma, dtype_in, x, (uint64_t)K, (uint64_t)M, 0, BM)) != MOE_OK) return st;
   {
     EncodeTiledFn fn = encode_fn();
