@@ -38,6 +38,10 @@ WORKLOADS = {
     "gate_up": dict(tokens=8192, K=2048, N=1536, E=128, k=8, routing="softmax-top8 of N(0,1) logits"),
     "down": dict(tokens=8192, K=768, N=2048, E=128, k=8, routing="zipf(1.2) expert ids, 3 experts emptied"),
 }
+# dram__bytes_read + dram__bytes_write over algorithmic bytes, from one ncu capture per kernel on the
+# reduced case (16384 rows, 32 experts; profiles/pair_kernels_gate_up_16k_rows.md).  Traffic grows in
+# proportion to rows and experts, so the ratio carries over to the full workload.
+NCU_TRAFFIC_RATIO = {"fwd": 0.95, "dx": 0.95, "dw": 0.85}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -526,7 +530,9 @@ def main():
                         for name, ms in per_kernel.items()},
             "roofline": {"bound": "tensor", "kernel": f"tc grouped gemm {dominant}", "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak, "peak_kind": f"bf16_tflops_sustained, {peaks_kind}",
-                         "traffic": None},
+                         "traffic": NCU_TRAFFIC_RATIO[dominant] * alg_bytes if args.gemm_path == "auto" and world == 1 else None,
+                         "traffic_note": "ncu DRAM bytes of the reduced case scaled by units (profiles/pair_kernels_gate_up_16k_rows.md)",
+                         "algorithmic_bytes": alg_bytes},
             "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "tokens_per_s": T * world / (e2e_ms * 1e-3)},
