@@ -78,6 +78,33 @@ def test_dw(cuda, M, K, N, E, empty, dtype):
     assert np.all(to_np(dw)[m_sizes == 0] == 0)
 
 
+THIN = [
+    # LoRA-thin shapes (rank 8..64 as output width or as contraction length): M, K, N, E, empty
+    (1000, 2048, 16, 8, 0.2),    # x @ A^T, rank 16
+    (1000, 16, 1536, 8, 0.2),    # (x A^T) @ B^T, rank 16
+    (777, 64, 24, 5, 0.0),       # rank 24 -> 32-column accumulator
+    (513, 8, 128, 3, 0.0),       # rank 8
+    (2048, 768, 64, 16, 0.3),    # rank 64
+]
+
+
+@pytest.mark.parametrize("M,K,N,E,empty", THIN)
+def test_lora_thin_shapes(cuda, M, K, N, E, empty):
+    from qwen3_moe_fused.grouped_gemm.backward_dw import grouped_gemm_backward_dw
+    from qwen3_moe_fused.grouped_gemm.forward import grouped_gemm_forward
+    from qwen3_moe_fused.grouped_gemm.forward_transposed import grouped_gemm_forward_transposed
+
+    rng = np.random.default_rng(M + K + N)
+    x, w, dy, m_sizes = tensors(cuda, rng, M, K, N, E, "bf16", empty)
+    tm = torch.from_numpy(m_sizes).to(cuda)
+    tx, tw, tdy = to_dev(x, "bf16", cuda), to_dev(w, "bf16", cuda), to_dev(dy, "bf16", cuda)
+    assert_close(to_np(grouped_gemm_forward(tx, tw, tm)), O.grouped_gemm_fwd(x, w, m_sizes, "bf16"), "bf16", "thin fwd")
+    assert_close(to_np(grouped_gemm_forward_transposed(tdy, tw, tm)), O.grouped_gemm_dx(dy, w, m_sizes, "bf16"), "bf16", "thin dx")
+    dw = to_np(grouped_gemm_backward_dw(tx, tdy, tm, torch.bfloat16))
+    assert_close(dw, O.grouped_gemm_dw(x, dy, m_sizes, "bf16"), "bf16", "thin dw")
+    assert np.all(dw[m_sizes == 0] == 0)
+
+
 def test_group_boundaries_every_residue(cuda):
     # group sizes sweep every residue mod 128 and mod 64 so that every tail length of an M
     # tile (forward/dX) and of a reduction block (dW) is exercised

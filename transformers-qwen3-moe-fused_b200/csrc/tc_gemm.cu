@@ -184,10 +184,12 @@ template <int BN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
               const GemmParams p) {
-  constexpr int B_STAGE_BYTES = BN * BK * 2;
-  constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  constexpr int B_CHUNKS = (BN + 63) / 64;  // 64-wide chunks of an MN-major B tile
+  constexpr int B_STAGE_BYTES = B_MN ? B_CHUNKS * BK * 128 : (BN < 8 ? 8 : BN) * BK * 2;
+  constexpr int STAGE_BYTES = A_STAGE_BYTES + ((B_STAGE_BYTES + 1023) & ~1023);
   constexpr int STAGES = (BN == 256) ? 4 : 6;
-  constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators (256 or 512 columns)
+  constexpr int ACC_STRIDE = BN < 32 ? 32 : BN;  // TMEM columns between the two accumulators
+  constexpr uint32_t TMEM_COLS = 2 * ACC_STRIDE;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -239,13 +241,13 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, W_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + s * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
-          mbar_expect_tx(&ctl->full[s], STAGE_BYTES);
+          mbar_expect_tx(&ctl->full[s], A_STAGE_BYTES + B_STAGE_BYTES);
           tma_load_2d(sa, &tmap_a, &ctl->full[s], kb * BK, m0);
           if constexpr (!B_MN) {
             tma_load_3d(sb, &tmap_b, &ctl->full[s], kb * BK, n0, e);
           } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c)
+            for (int c = 0; c < B_CHUNKS; ++c)
               tma_load_3d(sb + c * (BK * 128), &tmap_b, &ctl->full[s], n0 + c * 64, kb * BK, e);
           }
         }
@@ -261,7 +263,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         const uint32_t acc_ph = (acc_it >> 1) & 1;
         if (!mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1, abort_flag, W_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * ACC_STRIDE;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -303,7 +305,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       const uint32_t acc_ph = (acc_it >> 1) & 1;
       if (!mbar_wait(&ctl->tmem_full[acc], acc_ph, abort_flag, W_TMEM_FULL)) { ok = false; break; }
       tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t taddr = tmem_base + acc * ACC_STRIDE + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         if (n0 + c >= p.N) break;  // warp-uniform
@@ -601,7 +603,8 @@ static int make_map(CUtensorMap* map, int dtype, const void* base, uint64_t d0, 
 
 template <int BN>
 static constexpr int smem_bytes_for(int E, int tables) {
-  return ((BN == 256) ? 4 : 6) * (A_STAGE_BYTES + BN * BK * 2) + (int)sizeof(Control) + tables * (E + 1) * 4 + 1024;
+  // upper bound that covers both the K-major and the MN-major B stage of tc_fwd_kernel<BN, *>
+  return ((BN == 256) ? 4 : 6) * (A_STAGE_BYTES + (BN < 64 ? 64 : BN) * BK * 2) + (int)sizeof(Control) + tables * (E + 1) * 4 + 1024;
 }
 
 template <typename K>
@@ -618,7 +621,7 @@ bool tc_eligible(int which, const void* a, const void* b, const void* out, int64
   if (dtype_in != MOE_BF16 && dtype_in != MOE_F16) return false;
   if (!is_float_dtype(dtype_out)) return false;
   if (E < 1 || E > tc::MAX_E || M < 1 || M > 0x7fffffffLL - 1024) return false;
-  if (N < 64 || K < 64 || (N % 8) || (K % 8)) return false;
+  if (N < 8 || K < 8 || (N % 8) || (K % 8)) return false;  // 16-byte row pitches; thin (LoRA) shapes included
   if (((uintptr_t)a & 15) || ((uintptr_t)b & 15) || ((uintptr_t)out & 3)) return false;
   (void)which;
   return true;
@@ -829,8 +832,8 @@ int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes
   CUtensorMap ma, mb;
   int st;
   if (which == 0 || which == 1) {
-    const bool wide = N > 128;
-    const int bn = wide ? 256 : 128;
+    // narrowest accumulator that covers N: thin outputs (LoRA down-projections) do not pay for 128 columns
+    const int bn = N > 128 ? 256 : N > 64 ? 128 : N > 32 ? 64 : N > 16 ? 32 : 16;
     if ((st = make_map(&ma, dtype_in, a, (uint64_t)K, (uint64_t)M, 0, BM)) != MOE_OK) return st;
     if (which == 0) st = make_map(&mb, dtype_in, b, (uint64_t)K, (uint64_t)N, (uint64_t)E, (uint32_t)bn);
     else st = make_map(&mb, dtype_in, b, (uint64_t)N, (uint64_t)K, (uint64_t)E, BK);
@@ -843,8 +846,23 @@ int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes
     if ((st = set_smem(tc_fwd_kernel<BN_, BMN_>, bytes)) != MOE_OK) return st;                \
     tc_fwd_kernel<BN_, BMN_><<<grid, NUM_THREADS, bytes, stream>>>(ma, mb, p);                \
   } while (0)
-    if (which == 0) { if (wide) MOE_TC_LAUNCH(256, false); else MOE_TC_LAUNCH(128, false); }
-    else { if (wide) MOE_TC_LAUNCH(256, true); else MOE_TC_LAUNCH(128, true); }
+    if (which == 0) {
+      switch (bn) {
+        case 256: MOE_TC_LAUNCH(256, false); break;
+        case 128: MOE_TC_LAUNCH(128, false); break;
+        case 64: MOE_TC_LAUNCH(64, false); break;
+        case 32: MOE_TC_LAUNCH(32, false); break;
+        default: MOE_TC_LAUNCH(16, false); break;
+      }
+    } else {
+      switch (bn) {
+        case 256: MOE_TC_LAUNCH(256, true); break;
+        case 128: MOE_TC_LAUNCH(128, true); break;
+        case 64: MOE_TC_LAUNCH(64, true); break;
+        case 32: MOE_TC_LAUNCH(32, true); break;
+        default: MOE_TC_LAUNCH(16, true); break;
+      }
+    }
 #undef MOE_TC_LAUNCH
     return launch_status();
   }
@@ -854,7 +872,7 @@ int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes
 bool tc_nf4_eligible(const void* x, const void* packed, const void* absmax, const void* out, int64_t M, int N, int K,
                      int E, int blocksize, int dtype_in, int dtype_out) {
   if (!tc_eligible(0, x, packed, out, M, N, K, E, dtype_in, dtype_out)) return false;
-  if (blocksize < 64 || (K % 64) != 0) return false;  // one absmax per (row, 64-wide k-block); packed pitch % 16 B
+  if (blocksize < 64 || (K % 64) != 0 || N < 64) return false;  // one absmax per (row, 64-wide k-block); packed pitch % 16 B
   if ((uintptr_t)absmax & 3) return false;
   return true;
 }
