@@ -399,6 +399,7 @@ def main():
         plan = ExpertParallelPlan.build(m_sizes, world, rank, dev)
     torch.cuda.synchronize()
 
+    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
     ev = lambda: torch.cuda.Event(enable_timing=True)
     kernel_ms = {"fwd": [], "dx": [], "dw": []}
     launches_per_step = 3
@@ -418,19 +419,38 @@ def main():
                 dw = grouped_gemm_backward_dw(x_d, dy_d, m_sizes, bf)
             marks[3].record()
             return marks if record else None, (y, dx, dw)
-        # expert parallel: rows to their experts, compute, results back
+        # expert parallel: rows to their experts, compute, results back.  The all-to-alls and
+        # their permutation passes run on a second stream so that they overlap the GEMMs:
+        #   comm:    dispatch x | dispatch dy |            combine y |           combine dx
+        #   compute:            | forward     | dX         | dW
         marks = [ev() for _ in range(4)]
-        xl = plan.dispatch(x_d)
-        dyl = plan.dispatch(dy_d)
+        main = torch.cuda.current_stream()
+        e_x, e_dy, e_y, e_dx, e_done = (torch.cuda.Event() for _ in range(5))
+        comm_stream.wait_stream(main)
+        with torch.cuda.stream(comm_stream):
+            xl = plan.dispatch(x_d)
+            e_x.record()
+            dyl = plan.dispatch(dy_d)
+            e_dy.record()
+        main.wait_event(e_x)
         marks[0].record()
         y = plan.grouped(grouped_gemm_forward, xl, w)
         marks[1].record()
+        e_y.record()
+        with torch.cuda.stream(comm_stream):
+            comm_stream.wait_event(e_y)
+            y_back = plan.combine(y)
+        main.wait_event(e_dy)
         dx = plan.grouped(grouped_gemm_forward_transposed, dyl, w)
         marks[2].record()
+        e_dx.record()
+        with torch.cuda.stream(comm_stream):
+            comm_stream.wait_event(e_dx)
+            dx_back = plan.combine(dx)
+            e_done.record()
         dw = plan.grouped_dw(grouped_gemm_backward_dw, xl, dyl, bf, E_local)
         marks[3].record()
-        y_back = plan.combine(y)
-        dx_back = plan.combine(dx)
+        main.wait_event(e_done)
         return marks if record else None, (y_back, dx_back, dw)
 
     def barrier():

@@ -264,12 +264,20 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const int n = n0 + (int)rank * 128 + row;
       const bool n_ok = n < p.N;
       const int64_t row_flat = ((int64_t)e * p.N + (n_ok ? n : 0)) * p.K + khalf * 32;
-      float am_next = n_ok ? __ldg(q.absmax + (row_flat >> q.shift)) : 0.f;
+      // absmax of this row for the next AM_AHEAD k-blocks is kept in flight: one L2 round trip
+      // per k-block would otherwise sit on the decode path
+      constexpr int AM_AHEAD = 4;
+      float am_ring[AM_AHEAD];
+#pragma unroll
+      for (int i = 0; i < AM_AHEAD; ++i)
+        am_ring[i] = (n_ok && i < k_blocks) ? __ldg(q.absmax + ((row_flat + (int64_t)i * BK) >> q.shift)) : 0.f;
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
-        const float am = am_next;
-        if (kb + 1 < k_blocks && n_ok) am_next = __ldg(q.absmax + ((row_flat + (int64_t)(kb + 1) * BK) >> q.shift));
+        const float am = am_ring[0];
+#pragma unroll
+        for (int i = 0; i + 1 < AM_AHEAD; ++i) am_ring[i] = am_ring[i + 1];
+        am_ring[AM_AHEAD - 1] = (n_ok && kb + AM_AHEAD < k_blocks) ? __ldg(q.absmax + ((row_flat + (int64_t)(kb + AM_AHEAD) * BK) >> q.shift)) : 0.f;
         if (!mbar_wait(&ctl->qfull[s], ph, abort_flag, PW_FULL)) { ok = false; break; }
         uint8_t* st = smem + s * STAGE_BYTES;
         const uint4 raw = *reinterpret_cast<const uint4*>(st + Q_OFF + row * (BK / 2) + khalf * 16);
