@@ -5,13 +5,13 @@
 // 128 per CTA; accumulator columns = up to 256 tokens; two TMEM accumulators so the epilogue
 // overlaps the next tile), but the weight half-tile of a stage is not loaded as 16-bit data:
 // TMA brings the 4 KB of packed 4-bit codes (128 rows x 32 bytes) and eight decode warps per
-// CTA expand them to the swizzled K-major 16-bit tile the MMA reads.  HBM and L2 see
+// CTA (two groups of four, alternating k-blocks) expand them to the swizzled K-major 16-bit tile the MMA reads.  HBM and L2 see
 // 0.5 + 4/blocksize bytes per weight instead of 2.
 //
 // Synchronisation per stage s:
 //   qfull[s]  (local)   packed codes of this CTA have landed            TMA tx
 //   full[s]   (leader)  token tiles of both CTAs have landed            TMA tx from both CTAs
-//   ready[s]  (leader)  decoded weight tiles of both CTAs are written   16 arrivals (8 warps x 2 CTAs)
+//   ready[s]  (leader)  decoded weight tiles of both CTAs are written   8 arrivals (4 warps x 2 CTAs)
 //   empty[s]  (both)    the MMAs that read the stage have completed     tcgen05.commit, multicast
 // The decode warps publish their shared-memory writes to the async proxy
 // (fence.proxy.async) before arriving on the leader's barrier.
@@ -111,7 +111,7 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_init(&ctl->full[s], 1);
       mbar_init(&ctl->empty[s], 1);
       mbar_init(&ctl->qfull[s], 1);
-      mbar_init(&ctl->ready[s], 16);
+      mbar_init(&ctl->ready[s], 8);
     }
     for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 8); }
     ctl->abort_flag = 0;
@@ -248,10 +248,13 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
   } else {
     // ------------------------------ decode warps (both CTAs) ------------------------------
-    // thread -> weight row (t % 128) of this CTA's half-tile and 32-wide half of the k-block (t / 128)
+    // Two groups of four warps take alternate k-blocks, so the decode of one k-block (a few
+    // hundred cycles of dependent work per thread) overlaps the decode of the next.  Inside a
+    // group, thread -> weight row (t % 128) of this CTA's half-tile; it decodes the row's 64
+    // weights of the k-block (32 packed bytes, one absmax).
     const int t = threadIdx.x - 6 * 32;
     const int row = t & 127;
-    const int khalf = t >> 7;
+    const int group = t >> 7;
     const uint32_t ready_leader0 = map_to_cta(smem_u32(&ctl->ready[0]), 0);
     float code[16];
 #pragma unroll
@@ -263,39 +266,50 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       decode(tile, e, t0, n_mma, n0);
       const int n = n0 + (int)rank * 128 + row;
       const bool n_ok = n < p.N;
-      const int64_t row_flat = ((int64_t)e * p.N + (n_ok ? n : 0)) * p.K + khalf * 32;
-      // absmax of this row for the next AM_AHEAD k-blocks is kept in flight: one L2 round trip
-      // per k-block would otherwise sit on the decode path
-      constexpr int AM_AHEAD = 4;
+      const int64_t row_flat = ((int64_t)e * p.N + (n_ok ? n : 0)) * p.K;
+      // k-blocks of this tile that belong to this group: kb0, kb0 + 2, ...
+      const int kb0 = (int)((group - (int)(it & 1)) & 1);
+      // absmax of the next AM_AHEAD own k-blocks is kept in flight: one L2 round trip per
+      // k-block would otherwise sit on the decode path
+      constexpr int AM_AHEAD = 3;
       float am_ring[AM_AHEAD];
 #pragma unroll
-      for (int i = 0; i < AM_AHEAD; ++i)
-        am_ring[i] = (n_ok && i < k_blocks) ? __ldg(q.absmax + ((row_flat + (int64_t)i * BK) >> q.shift)) : 0.f;
-      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
+      for (int i = 0; i < AM_AHEAD; ++i) {
+        const int kbi = kb0 + 2 * i;
+        am_ring[i] = (n_ok && kbi < k_blocks) ? __ldg(q.absmax + ((row_flat + (int64_t)kbi * BK) >> q.shift)) : 0.f;
+      }
+      for (int kb = kb0; kb < k_blocks; kb += 2) {
+        const uint32_t my_it = it + kb;
+        const int s = my_it % STAGES;
+        const uint32_t ph = (my_it / STAGES) & 1;
         const float am = am_ring[0];
 #pragma unroll
         for (int i = 0; i + 1 < AM_AHEAD; ++i) am_ring[i] = am_ring[i + 1];
-        am_ring[AM_AHEAD - 1] = (n_ok && kb + AM_AHEAD < k_blocks) ? __ldg(q.absmax + ((row_flat + (int64_t)(kb + AM_AHEAD) * BK) >> q.shift)) : 0.f;
+        {
+          const int kbn = kb + 2 * AM_AHEAD;
+          am_ring[AM_AHEAD - 1] = (n_ok && kbn < k_blocks) ? __ldg(q.absmax + ((row_flat + (int64_t)kbn * BK) >> q.shift)) : 0.f;
+        }
         if (!mbar_wait(&ctl->qfull[s], ph, abort_flag, PW_FULL)) { ok = false; break; }
         uint8_t* st = smem + s * STAGE_BYTES;
-        const uint4 raw = *reinterpret_cast<const uint4*>(st + Q_OFF + row * (BK / 2) + khalf * 16);
-        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+        const uint4* src = reinterpret_cast<const uint4*>(st + Q_OFF + row * (BK / 2));
+        const uint4 raw0 = src[0], raw1 = src[1];
+        const uint32_t words[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
         uint8_t* dst_row = st + row * 128;
         const Nf4Planes pl = nf4_make_planes<IS_BF16>(code, am);
+        if (!(p.debug & 128)) {  // (experiment switch: hand-shake only, no decode work)
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {  // 4 bytes -> 8 values -> one 16-byte chunk
-          uint32_t outw[4];
-          nf4_lookup4(pl, words[w] & 0xffffu, outw[0], outw[1]);
-          nf4_lookup4(pl, words[w] >> 16, outw[2], outw[3]);
-          const int chunk = khalf * 4 + w;
-          *reinterpret_cast<uint4*>(dst_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+          for (int w = 0; w < 8; ++w) {  // 4 bytes -> 8 values -> one 16-byte chunk
+            uint32_t outw[4];
+            nf4_lookup4(pl, words[w] & 0xffffu, outw[0], outw[1]);
+            nf4_lookup4(pl, words[w] >> 16, outw[2], outw[3]);
+            *reinterpret_cast<uint4*>(dst_row + ((w ^ (row & 7)) << 4)) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+          }
         }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(ready_leader0 + s * 8);
       }
+      it += k_blocks;
     }
   }
 
