@@ -40,7 +40,7 @@ struct GemmParams {
   uint32_t idesc;
   const CUtensorMap* group_maps;  // per-expert tensor maps in workspace ([slot][expert]), or null
   int debug;      // experiment switches (MOE_B200_DEBUG): 1 = no global stores, 2 = no TMEM loads, 4 = no MMA,
-                  // 32 = 512-token pair kernel (tc_gemm_pair2.cuh) instead of the 256-token one,
+                  // 32 = pair forward / dX without per-expert maps (register-store epilogue),
                   // 64 = single-CTA NF4 kernel instead of the pair one
 };
 
@@ -555,7 +555,6 @@ tc_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
 #include "tc_gemm_pair.cuh"
 #include "tc_gemm_dw.cuh"
-#include "tc_gemm_pair2.cuh"
 #include "tc_gemm_nf4.cuh"
 
 namespace moe {
@@ -689,30 +688,20 @@ static int pair_grouped_gemm(int which, const void* a, const void* b, const void
     if (st != MOE_OK) return st;
     if ((st = make_map(&mx, dtype_in, a, (uint64_t)K, (uint64_t)M, 0, 128)) != MOE_OK) return st;
     p.idesc = make_idesc(fmt, which == 1, 0, 256, 0);  // N field is filled per tile
-    {
-      // 512-token tiles on per-expert maps (needs workspace and the larger shared-memory layout)
-      const int bytes2 = P2_STAGES * P2_STAGE_BYTES + 4 * P2_STAGING_BYTES + (int)sizeof(PairControl) + 2 * (E + 1) * 4 + 1024;
-      const bool ws_ok = ws != nullptr && (((uintptr_t)ws & 127) == 0) && ws_bytes >= (size_t)2 * E * sizeof(CUtensorMap);
-      if (ws_ok && bytes2 <= SMEM_LIMIT && (p.debug & 32) && (((uintptr_t)out & 15) == 0 || dtype_out == MOE_F32)) {
-        GroupMapTemplates tm;
-        tm.count = dtype_out == MOE_F32 ? 1 : 2;
-        tm.t[GM_IN] = mx;
-        if (tm.count == 2 && (st = make_map(&tm.t[GM_OUT], dtype_out, out, (uint64_t)N, (uint64_t)M, 0, 64)) != MOE_OK) return st;
-        const int gm_smem = 8 * 128 + 2 * (E + 1) * 4 + 128;
-        build_group_maps_kernel<<<(E + 7) / 8, 256, gm_smem, stream>>>(tm, m_sizes, ms64, E, M, reinterpret_cast<CUtensorMap*>(ws));
-        if ((st = launch_status()) != MOE_OK) return st;
-        p.group_maps = reinterpret_cast<const CUtensorMap*>(ws);
-        if (which == 0) {
-          auto kern = pair_fwd2_kernel<false>;
-          if ((st = set_smem(kern, bytes2)) != MOE_OK) return st;
-          return launch_pair(kern, 2 * resident_pairs(kern, bytes2), bytes2, stream, mw, p);
-        }
-        auto kern = pair_fwd2_kernel<true>;
-        if ((st = set_smem(kern, bytes2)) != MOE_OK) return st;
-        return launch_pair(kern, 2 * resident_pairs(kern, bytes2), bytes2, stream, mw, p);
-      }
+    // Per-expert copies of the token and output maps (row extent = the group's last row): partial
+    // tiles then load no rows of the next expert, and 16-bit outputs can leave through TMA stores.
+    const bool ws_ok = ws != nullptr && (((uintptr_t)ws & 127) == 0) && ws_bytes >= (size_t)2 * E * sizeof(CUtensorMap);
+    if (ws_ok && (((uintptr_t)out & 15) == 0 || dtype_out == MOE_F32) && !(p.debug & 32)) {
+      GroupMapTemplates tm;
+      tm.count = dtype_out == MOE_F32 ? 1 : 2;
+      tm.t[GM_IN] = mx;
+      if (tm.count == 2 && (st = make_map(&tm.t[GM_OUT], dtype_out, out, (uint64_t)N, (uint64_t)M, 0, 32)) != MOE_OK) return st;
+      const int gm_smem = 8 * 128 + 2 * (E + 1) * 4 + 128;
+      build_group_maps_kernel<<<(E + 7) / 8, 256, gm_smem, stream>>>(tm, m_sizes, ms64, E, M, reinterpret_cast<CUtensorMap*>(ws));
+      if ((st = launch_status()) != MOE_OK) return st;
+      p.group_maps = reinterpret_cast<const CUtensorMap*>(ws);
     }
-    const int bytes = PAIR_STAGES * 2 * PAIR_HALF_BYTES + (int)sizeof(PairControl) + 2 * (E + 1) * 4 + 1024;
+    const int bytes = PAIR_STAGES * 2 * PAIR_HALF_BYTES + 4 * PAIR_STAGING_BYTES + (int)sizeof(PairControl) + 2 * (E + 1) * 4 + 1024;
     if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
     if (which == 0) {
       if ((st = set_smem(pair_fwd_kernel<false>, bytes)) != MOE_OK) return st;

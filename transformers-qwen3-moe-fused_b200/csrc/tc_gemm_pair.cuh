@@ -33,6 +33,9 @@ struct PairControl {
   int abort_flag;
 };
 
+enum { GM_IN = 0, GM_OUT = 1 };            // per-expert tensor-map slots of the forward / dX kernels
+constexpr int PAIR_STAGING_BYTES = 32 * 128;  // 32 tokens x 64 weight rows x 16 bit
+
 enum PairWaitCode { PW_EMPTY = 11, PW_FULL = 12, PW_TMEM_EMPTY = 13, PW_TMEM_FULL = 14, PW_PEER = 15 };
 
 template <typename T>
@@ -53,7 +56,8 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  PairControl* ctl = reinterpret_cast<PairControl*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* staging = smem + STAGES * STAGE_BYTES;  // [buffer 0/1][weight-row half 0/1][32 tokens x 128 B]
+  PairControl* ctl = reinterpret_cast<PairControl*>(staging + 4 * PAIR_STAGING_BYTES);
   int* row_start = reinterpret_cast<int*>(ctl + 1);
   int* tt_start = row_start + (p.E + 1);  // token tiles before each expert
   volatile int* abort_flag = &ctl->abort_flag;
@@ -105,11 +109,15 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       const uint32_t full_leader0 = map_to_cta(smem_u32(&ctl->full[0]), 0);
       uint32_t it = 0;
       bool ok = true;
+      int last_e = -1;
       for (int64_t tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
         int e, t0, n_mma, n0;
         decode(tile, e, t0, n_mma, n0);
         const int w_row = n0 + (int)rank * 128;
         const int tok = t0 + (int)rank * (n_mma >> 1);
+        // with per-expert maps the token rows past the group's end are zero-filled, not fetched
+        const CUtensorMap* mx = p.group_maps ? p.group_maps + (size_t)GM_IN * p.E + e : &tmap_x;
+        if (p.group_maps && e != last_e) { tensormap_acquire(mx); last_e = e; }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -124,7 +132,7 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             tma_load_3d_pair(sa, &tmap_w, bar, w_row, kb * BK, e);
             tma_load_3d_pair(sa + BK * 128, &tmap_w, bar, w_row + 64, kb * BK, e);
           }
-          tma_load_2d_pair(sb, &tmap_x, bar, kb * BK, tok);
+          tma_load_2d_pair(sb, mx, bar, kb * BK, tok);
         }
       }
     }
@@ -165,8 +173,13 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   } else {
     // ------------------------------ epilogue (both CTAs) ------------------------------
     const int quarter = warp & 3;
+    const int epi_tid = threadIdx.x - 64;  // 0..127
     const uint32_t tmem_empty_leader0 = map_to_cta(smem_u32(&ctl->tmem_empty[0]), 0);
-    uint32_t acc_it = 0;
+    // 16-bit outputs with per-expert output maps leave through shared memory and TMA stores
+    const bool staged = p.group_maps != nullptr && p.dtype_out != MOE_F32;
+    const bool is_bf16 = p.dtype_out == MOE_BF16;
+    uint32_t acc_it = 0, chunk_it = 0;
+    int last_e = -1;
     bool ok = true;
     for (int64_t tile = pair_id; tile < total_tiles && ok; tile += num_pairs, ++acc_it) {
       int e, t0, n_mma, n0;
@@ -176,9 +189,59 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       const int t_end = row_start[e + 1];
       const uint32_t acc = acc_it & 1;
       const uint32_t acc_ph = (acc_it >> 1) & 1;
+      const CUtensorMap* my = staged ? p.group_maps + (size_t)GM_OUT * p.E + e : nullptr;
+      if (staged && epi_tid == 0 && e != last_e) { tensormap_acquire(my); last_e = e; }
       if (!mbar_wait_cluster(&ctl->tmem_full[acc], acc_ph, abort_flag, PW_TMEM_FULL)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * PAIR_TOKENS + ((uint32_t)(quarter * 32) << 16);
+      if (staged) {
+        // TMEM is read in the accumulator-fragment shape, packed to 16 bit and transposed by
+        // stmatrix into a swizzled [token][weight row] tile: 32 tokens x 2 x 64 weight rows per round
+        const int n_cta = n0 + (int)rank * 128;
+        const int half = quarter >> 1;
+        const int chunk = 4 * (quarter & 1) + (lane >> 3);  // 16-byte chunk of the 128-byte staging row
+#pragma unroll 1
+        for (int c = 0; c < n_mma; c += 32, ++chunk_it) {
+          uint8_t* buf = staging + (chunk_it & 1) * (2 * PAIR_STAGING_BYTES);
+          if (epi_tid == 0) tma_store_wait_read<1>();  // the stores of two rounds ago have read this buffer
+          named_barrier_sync(1, 128);
+          uint32_t lo[16], hi[16];
+          if (!(p.debug & 2)) {
+            tmem_ld_16x256b_x4(taddr + c, lo);
+            tmem_ld_16x256b_x4(taddr + c + (16u << 16), hi);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) { lo[i] = 0; hi[i] = 0; }
+          }
+          uint8_t* tile_buf = buf + half * PAIR_STAGING_BYTES;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t m0, m1, m2, m3;
+            if (is_bf16) {
+              m0 = pack2<__nv_bfloat16>(__uint_as_float(lo[4 * g + 0]), __uint_as_float(lo[4 * g + 1]));
+              m1 = pack2<__nv_bfloat16>(__uint_as_float(lo[4 * g + 2]), __uint_as_float(lo[4 * g + 3]));
+              m2 = pack2<__nv_bfloat16>(__uint_as_float(hi[4 * g + 0]), __uint_as_float(hi[4 * g + 1]));
+              m3 = pack2<__nv_bfloat16>(__uint_as_float(hi[4 * g + 2]), __uint_as_float(hi[4 * g + 3]));
+            } else {
+              m0 = pack2<__half>(__uint_as_float(lo[4 * g + 0]), __uint_as_float(lo[4 * g + 1]));
+              m1 = pack2<__half>(__uint_as_float(lo[4 * g + 2]), __uint_as_float(lo[4 * g + 3]));
+              m2 = pack2<__half>(__uint_as_float(hi[4 * g + 0]), __uint_as_float(hi[4 * g + 1]));
+              m3 = pack2<__half>(__uint_as_float(hi[4 * g + 2]), __uint_as_float(hi[4 * g + 3]));
+            }
+            const int trow = 8 * g + (lane & 7);
+            stmatrix_x4_trans(smem_u32(tile_buf + trow * 128 + ((chunk ^ (trow & 7)) << 4)), m0, m1, m2, m3);
+          }
+          fence_proxy_async_smem();
+          named_barrier_sync(1, 128);
+          if (epi_tid == 0 && !(p.debug & 1)) {
+            // rows past the group's end and columns past N are clipped by the tensor map
+            tma_store_2d(my, buf, n_cta, t0 + c);
+            if (n_cta + 64 < p.N) tma_store_2d(my, buf + PAIR_STAGING_BYTES, n_cta + 64, t0 + c);
+            tma_store_commit();
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < n_mma; c += 32) {
         uint32_t v[32];
@@ -207,10 +270,12 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           }
         }
       }
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tmem_empty_leader0 + acc * 8);
     }
+    if (staged && epi_tid == 0) tma_store_wait_all();
   }
 
   tc_fence_before_sync();
