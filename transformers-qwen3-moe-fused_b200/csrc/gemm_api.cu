@@ -19,7 +19,7 @@ bool tc_nf4_eligible(const void* x, const void* packed, const void* absmax, cons
                      int E, int blocksize, int dtype_in, int dtype_out);
 int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code, const float* absmax, int blocksize,
                         const void* m_sizes, int ms64, void* out, int64_t M, int N, int K, int E,
-                        int dtype_in, int dtype_out, cudaStream_t stream);
+                        int dtype_in, int dtype_out, void* ws, size_t ws_bytes, cudaStream_t stream);
 int tc_read_error(int* flag_out, bool clear);
 const char* tc_last_detail();
 
@@ -122,7 +122,7 @@ MOE_API int moe_grouped_gemm_dw(const void* x, const void* y, const void* m_size
 
 MOE_API int moe_grouped_gemm_fwd_nf4(const void* x, const uint8_t* packed, const float* code, const float* absmax,
                                      int blocksize, const void* m_sizes, int msd, void* y, int64_t M, int N, int K,
-                                     int E, int dtype_in, int dtype_out, void*, size_t, void* stream) {
+                                     int E, int dtype_in, int dtype_out, void* ws, size_t ws_bytes, void* stream) {
   int st = check_common(x, packed, m_sizes, msd, y, M, N, K, E, dtype_in, dtype_out);
   if (st != MOE_OK) return st;
   if (!code || !absmax) return MOE_ERR_NULL;
@@ -136,7 +136,7 @@ MOE_API int moe_grouped_gemm_fwd_nf4(const void* x, const uint8_t* packed, const
   const bool can_tc = tc_nf4_eligible(x, packed, absmax, y, M, N, K, E, blocksize, dtype_in, dtype_out);
   if ((path == MOE_PATH_TC || path == MOE_PATH_TC_SINGLE) && !can_tc) return MOE_ERR_UNSUPPORTED;
   if (can_tc && path != MOE_PATH_SIMT)
-    return tc_grouped_gemm_nf4(x, packed, code, absmax, blocksize, m_sizes, msd == MOE_I64, y, M, N, K, E, dtype_in, dtype_out, (cudaStream_t)stream);
+    return tc_grouped_gemm_nf4(x, packed, code, absmax, blocksize, m_sizes, msd == MOE_I64, y, M, N, K, E, dtype_in, dtype_out, ws, ws_bytes, (cudaStream_t)stream);
   return simt_grouped_gemm_nf4(x, packed, code, absmax, shift, m_sizes, msd == MOE_I64, y, M, N, K, E, dtype_in, dtype_out, (cudaStream_t)stream);
 }
 

@@ -868,7 +868,7 @@ bool tc_nf4_eligible(const void* x, const void* packed, const void* absmax, cons
 
 int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code, const float* absmax, int blocksize,
                         const void* m_sizes, int ms64, void* out, int64_t M, int N, int K, int E,
-                        int dtype_in, int dtype_out, cudaStream_t stream) {
+                        int dtype_in, int dtype_out, void* ws, size_t ws_bytes, cudaStream_t stream) {
   using namespace tc;
   bind_context_once();
   GemmParams p;
@@ -892,8 +892,19 @@ int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code,
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return MOE_ERR_UNSUPPORTED;
     if ((st = make_map(&ma, dtype_in, x, (uint64_t)K, (uint64_t)M, 0, 128)) != MOE_OK) return st;
     p.idesc = make_idesc(dtype_in == MOE_BF16 ? 1 : 0, 0, 0, 256, 0);
-    const int pbytes = NF4P_STAGES * NF4P_STAGE_BYTES + (int)sizeof(Nf4PairControl) + 2 * (E + 1) * 4 + 1024;
+    const int pbytes = NF4P_STAGES * NF4P_STAGE_BYTES + 4 * PAIR_STAGING_BYTES + (int)sizeof(Nf4PairControl) + 2 * (E + 1) * 4 + 1024;
     if (pbytes <= SMEM_LIMIT) {
+      const bool ws_ok = ws != nullptr && (((uintptr_t)ws & 127) == 0) && ws_bytes >= (size_t)2 * E * sizeof(CUtensorMap);
+      if (ws_ok && (((uintptr_t)out & 15) == 0 || dtype_out == MOE_F32) && !(p.debug & 32)) {
+        GroupMapTemplates tm;
+        tm.count = dtype_out == MOE_F32 ? 1 : 2;
+        tm.t[GM_IN] = ma;
+        if (tm.count == 2 && (st = make_map(&tm.t[GM_OUT], dtype_out, out, (uint64_t)N, (uint64_t)M, 0, 32)) != MOE_OK) return st;
+        const int gm_smem = 8 * 128 + 2 * (E + 1) * 4 + 128;
+        build_group_maps_kernel<<<(E + 7) / 8, 256, gm_smem, stream>>>(tm, m_sizes, ms64, E, M, reinterpret_cast<CUtensorMap*>(ws));
+        if ((st = launch_status()) != MOE_OK) return st;
+        p.group_maps = reinterpret_cast<const CUtensorMap*>(ws);
+      }
       if (dtype_in == MOE_BF16) {
         auto kern = pair_fwd_nf4_kernel<true>;
         if ((st = set_smem(kern, pbytes)) != MOE_OK) return st;

@@ -29,7 +29,7 @@ namespace moe {
 namespace tc {
 
 constexpr int NF4P_THREADS = 448;                               // 14 warps: TMA, MMA, 4 epilogue, 8 decode
-constexpr int NF4P_STAGES = 6;
+constexpr int NF4P_STAGES = 5;
 constexpr int NF4P_PACKED_BYTES = 128 * (BK / 2);               // 4 KB
 constexpr int NF4P_STAGE_BYTES = 2 * PAIR_HALF_BYTES + NF4P_PACKED_BYTES;  // 36 KB
 
@@ -96,7 +96,8 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  Nf4PairControl* ctl = reinterpret_cast<Nf4PairControl*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* staging = smem + STAGES * STAGE_BYTES;  // epilogue staging, 4 * PAIR_STAGING_BYTES
+  Nf4PairControl* ctl = reinterpret_cast<Nf4PairControl*>(staging + 4 * PAIR_STAGING_BYTES);
   int* row_start = reinterpret_cast<int*>(ctl + 1);
   int* tt_start = row_start + (p.E + 1);
   volatile int* abort_flag = &ctl->abort_flag;
@@ -152,11 +153,14 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const uint32_t full_leader0 = map_to_cta(smem_u32(&ctl->full[0]), 0);
       uint32_t it = 0;
       bool ok = true;
+      int last_e = -1;
       for (int64_t tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
         int e, t0, n_mma, n0;
         decode(tile, e, t0, n_mma, n0);
         const int w_row = n0 + (int)rank * 128;
         const int tok = t0 + (int)rank * (n_mma >> 1);
+        const CUtensorMap* mx = p.group_maps ? p.group_maps + (size_t)GM_IN * p.E + e : &tmap_x;
+        if (p.group_maps && e != last_e) { tensormap_acquire(mx); last_e = e; }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -165,7 +169,7 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           mbar_expect_tx(&ctl->qfull[s], NF4P_PACKED_BYTES);
           tma_load_3d(st + Q_OFF, &tmap_q, &ctl->qfull[s], kb * (BK / 2), w_row, e);
           if (leader) mbar_expect_tx(&ctl->full[s], 2 * PAIR_HALF_BYTES);
-          tma_load_2d_pair(st + B_OFF, &tmap_x, full_leader0 + s * 8, kb * BK, tok);
+          tma_load_2d_pair(st + B_OFF, mx, full_leader0 + s * 8, kb * BK, tok);
         }
       }
     }
@@ -205,8 +209,11 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   } else if (warp < 6) {
     // ------------------------------ epilogue (both CTAs) ------------------------------
     const int quarter = warp & 3;
+    const int epi_tid = threadIdx.x - 64;
     const uint32_t tmem_empty_leader0 = map_to_cta(smem_u32(&ctl->tmem_empty[0]), 0);
-    uint32_t acc_it = 0;
+    const bool staged = p.group_maps != nullptr && p.dtype_out != MOE_F32;
+    uint32_t acc_it = 0, chunk_it = 0;
+    int last_e = -1;
     bool ok = true;
     for (int64_t tile = pair_id; tile < total_tiles && ok; tile += num_pairs, ++acc_it) {
       int e, t0, n_mma, n0;
@@ -216,9 +223,15 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const int t_end = row_start[e + 1];
       const uint32_t acc = acc_it & 1;
       const uint32_t acc_ph = (acc_it >> 1) & 1;
+      const CUtensorMap* my = staged ? p.group_maps + (size_t)GM_OUT * p.E + e : nullptr;
+      if (staged && epi_tid == 0 && e != last_e) { tensormap_acquire(my); last_e = e; }
       if (!mbar_wait_cluster(&ctl->tmem_full[acc], acc_ph, abort_flag, PW_TMEM_FULL)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * PAIR_TOKENS + ((uint32_t)(quarter * 32) << 16);
+      if (staged) {
+        pair_store_tile_staged(staging, chunk_it, taddr, n_mma, quarter, lane, epi_tid, p.dtype_out == MOE_BF16, my,
+                               n0 + (int)rank * 128, t0, p.N, p.debug);
+      } else {
 #pragma unroll 1
       for (int c = 0; c < n_mma; c += 32) {
         uint32_t v[32];
@@ -242,10 +255,12 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           }
         }
       }
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tmem_empty_leader0 + acc * 8);
     }
+    if (staged && epi_tid == 0) tma_store_wait_all();
   } else {
     // ------------------------------ decode warps (both CTAs) ------------------------------
     // Two groups of four warps take alternate k-blocks, so the decode of one k-block (a few

@@ -43,6 +43,59 @@ __device__ __forceinline__ void store_scalar(void* out, int64_t idx, float v) {
   reinterpret_cast<T*>(out)[idx] = from_f32<T>(v);
 }
 
+// Epilogue of one accumulator (n_mma token columns of this CTA's 128 weight rows) for 16-bit
+// outputs: TMEM is read in the accumulator-fragment shape, packed to 16 bit and transposed by
+// stmatrix into a swizzled [token][weight row] staging tile (32 tokens x 2 x 64 weight rows per
+// round, double buffered), which leaves through TMA stores; `my` is the expert's output map,
+// so rows past the group's end and columns past N are clipped.  Called by the 128 epilogue
+// threads (warps 2..5); `staging` holds 4 * PAIR_STAGING_BYTES.
+__device__ __forceinline__ void pair_store_tile_staged(uint8_t* staging, uint32_t& chunk_it, uint32_t taddr, int n_mma,
+                                                       int quarter, int lane, int epi_tid, bool is_bf16,
+                                                       const CUtensorMap* my, int n_cta, int t0, int N, int debug) {
+  const int half = quarter >> 1;
+  const int chunk = 4 * (quarter & 1) + (lane >> 3);  // 16-byte chunk of the 128-byte staging row
+#pragma unroll 1
+  for (int c = 0; c < n_mma; c += 32, ++chunk_it) {
+    uint8_t* buf = staging + (chunk_it & 1) * (2 * PAIR_STAGING_BYTES);
+    if (epi_tid == 0) tma_store_wait_read<1>();  // the stores of two rounds ago have read this buffer
+    named_barrier_sync(1, 128);
+    uint32_t lo[16], hi[16];
+    if (!(debug & 2)) {
+      tmem_ld_16x256b_x4(taddr + c, lo);
+      tmem_ld_16x256b_x4(taddr + c + (16u << 16), hi);
+      tmem_ld_wait();
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) { lo[i] = 0; hi[i] = 0; }
+    }
+    uint8_t* tile_buf = buf + half * PAIR_STAGING_BYTES;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint32_t m0, m1, m2, m3;
+      if (is_bf16) {
+        m0 = pack2<__nv_bfloat16>(__uint_as_float(lo[4 * g + 0]), __uint_as_float(lo[4 * g + 1]));
+        m1 = pack2<__nv_bfloat16>(__uint_as_float(lo[4 * g + 2]), __uint_as_float(lo[4 * g + 3]));
+        m2 = pack2<__nv_bfloat16>(__uint_as_float(hi[4 * g + 0]), __uint_as_float(hi[4 * g + 1]));
+        m3 = pack2<__nv_bfloat16>(__uint_as_float(hi[4 * g + 2]), __uint_as_float(hi[4 * g + 3]));
+      } else {
+        m0 = pack2<__half>(__uint_as_float(lo[4 * g + 0]), __uint_as_float(lo[4 * g + 1]));
+        m1 = pack2<__half>(__uint_as_float(lo[4 * g + 2]), __uint_as_float(lo[4 * g + 3]));
+        m2 = pack2<__half>(__uint_as_float(hi[4 * g + 0]), __uint_as_float(hi[4 * g + 1]));
+        m3 = pack2<__half>(__uint_as_float(hi[4 * g + 2]), __uint_as_float(hi[4 * g + 3]));
+      }
+      const int trow = 8 * g + (lane & 7);
+      stmatrix_x4_trans(smem_u32(tile_buf + trow * 128 + ((chunk ^ (trow & 7)) << 4)), m0, m1, m2, m3);
+    }
+    fence_proxy_async_smem();
+    named_barrier_sync(1, 128);
+    if (epi_tid == 0 && !(debug & 1)) {
+      tma_store_2d(my, buf, n_cta, t0 + c);
+      if (n_cta + 64 < N) tma_store_2d(my, buf + PAIR_STAGING_BYTES, n_cta + 64, t0 + c);
+      tma_store_commit();
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // forward / dX
 // ---------------------------------------------------------------------------------------
@@ -195,52 +248,8 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * PAIR_TOKENS + ((uint32_t)(quarter * 32) << 16);
       if (staged) {
-        // TMEM is read in the accumulator-fragment shape, packed to 16 bit and transposed by
-        // stmatrix into a swizzled [token][weight row] tile: 32 tokens x 2 x 64 weight rows per round
-        const int n_cta = n0 + (int)rank * 128;
-        const int half = quarter >> 1;
-        const int chunk = 4 * (quarter & 1) + (lane >> 3);  // 16-byte chunk of the 128-byte staging row
-#pragma unroll 1
-        for (int c = 0; c < n_mma; c += 32, ++chunk_it) {
-          uint8_t* buf = staging + (chunk_it & 1) * (2 * PAIR_STAGING_BYTES);
-          if (epi_tid == 0) tma_store_wait_read<1>();  // the stores of two rounds ago have read this buffer
-          named_barrier_sync(1, 128);
-          uint32_t lo[16], hi[16];
-          if (!(p.debug & 2)) {
-            tmem_ld_16x256b_x4(taddr + c, lo);
-            tmem_ld_16x256b_x4(taddr + c + (16u << 16), hi);
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) { lo[i] = 0; hi[i] = 0; }
-          }
-          uint8_t* tile_buf = buf + half * PAIR_STAGING_BYTES;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint32_t m0, m1, m2, m3;
-            if (is_bf16) {
-              m0 = pack2<__nv_bfloat16>(__uint_as_float(lo[4 * g + 0]), __uint_as_float(lo[4 * g + 1]));
-              m1 = pack2<__nv_bfloat16>(__uint_as_float(lo[4 * g + 2]), __uint_as_float(lo[4 * g + 3]));
-              m2 = pack2<__nv_bfloat16>(__uint_as_float(hi[4 * g + 0]), __uint_as_float(hi[4 * g + 1]));
-              m3 = pack2<__nv_bfloat16>(__uint_as_float(hi[4 * g + 2]), __uint_as_float(hi[4 * g + 3]));
-            } else {
-              m0 = pack2<__half>(__uint_as_float(lo[4 * g + 0]), __uint_as_float(lo[4 * g + 1]));
-              m1 = pack2<__half>(__uint_as_float(lo[4 * g + 2]), __uint_as_float(lo[4 * g + 3]));
-              m2 = pack2<__half>(__uint_as_float(hi[4 * g + 0]), __uint_as_float(hi[4 * g + 1]));
-              m3 = pack2<__half>(__uint_as_float(hi[4 * g + 2]), __uint_as_float(hi[4 * g + 3]));
-            }
-            const int trow = 8 * g + (lane & 7);
-            stmatrix_x4_trans(smem_u32(tile_buf + trow * 128 + ((chunk ^ (trow & 7)) << 4)), m0, m1, m2, m3);
-          }
-          fence_proxy_async_smem();
-          named_barrier_sync(1, 128);
-          if (epi_tid == 0 && !(p.debug & 1)) {
-            // rows past the group's end and columns past N are clipped by the tensor map
-            tma_store_2d(my, buf, n_cta, t0 + c);
-            if (n_cta + 64 < p.N) tma_store_2d(my, buf + PAIR_STAGING_BYTES, n_cta + 64, t0 + c);
-            tma_store_commit();
-          }
-        }
+        pair_store_tile_staged(staging, chunk_it, taddr, n_mma, quarter, lane, epi_tid, is_bf16, my,
+                               n0 + (int)rank * 128, t0, p.N, p.debug);
       } else {
 #pragma unroll 1
       for (int c = 0; c < n_mma; c += 32) {
