@@ -63,7 +63,22 @@ __global__ void __launch_bounds__(EW_THREADS)
 silu_fwd_kernel(const T* __restrict__ e, const T* __restrict__ g, T* __restrict__ h, int64_t n) {
   constexpr int V = VEC ? Vec<T>::N : 1;
   const int64_t nv = n / V;
-  for (int64_t i = (int64_t)blockIdx.x * EW_THREADS + threadIdx.x; i < nv; i += (int64_t)gridDim.x * EW_THREADS) {
+  const int64_t stride = (int64_t)gridDim.x * EW_THREADS;
+  int64_t i = (int64_t)blockIdx.x * EW_THREADS + threadIdx.x;
+  if constexpr (VEC) {
+    // two vectors per stream per iteration: four 16-byte loads in flight per thread
+    for (; i + stride < nv; i += 2 * stride) {
+      const int64_t i2 = i + stride;
+      const Vec<T> ve = load_vec(e + i * V), vg = load_vec(g + i * V);
+      const Vec<T> ve2 = load_vec(e + i2 * V), vg2 = load_vec(g + i2 * V);
+      Vec<T> vh, vh2;
+#pragma unroll
+      for (int j = 0; j < V; ++j) { vh.v[j] = silu_fwd_one(ve.v[j], vg.v[j]); vh2.v[j] = silu_fwd_one(ve2.v[j], vg2.v[j]); }
+      store_vec(h + i * V, vh);
+      store_vec(h + i2 * V, vh2);
+    }
+  }
+  for (; i < nv; i += stride) {
     if constexpr (VEC) {
       const Vec<T> ve = load_vec(e + i * V), vg = load_vec(g + i * V);
       Vec<T> vh;
@@ -154,20 +169,30 @@ nf4_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__
   }
 }
 
-// out[j,:] = hidden[sort_idx[j] / k, :].  One CTA walks whole rows.
+// out[j,:] = hidden[sort_idx[j] / k, :].  One CTA walks whole rows, two at a time so that
+// two rows' worth of loads are in flight.
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(EW_THREADS)
 gather_rows_kernel(const T* __restrict__ hidden, const int32_t* __restrict__ sort_idx, int k,
                    T* __restrict__ out, int64_t rows, int H) {
   constexpr int V = VEC ? Vec<T>::N : 1;
   const int hv = H / V;
-  for (int64_t j = blockIdx.x; j < rows; j += gridDim.x) {
-    const int64_t src = (int64_t)(sort_idx[j] / k);
-    const T* s = hidden + src * H;
-    T* d = out + j * H;
+  for (int64_t j = 2 * (int64_t)blockIdx.x; j < rows; j += 2 * (int64_t)gridDim.x) {
+    const bool two = j + 1 < rows;
+    const T* s0 = hidden + (int64_t)(sort_idx[j] / k) * H;
+    const T* s1 = hidden + (int64_t)(sort_idx[two ? j + 1 : j] / k) * H;
+    T* d0 = out + j * H;
+    T* d1 = d0 + H;
     for (int c = threadIdx.x; c < hv; c += EW_THREADS) {
-      if constexpr (VEC) store_vec(d + c * V, load_vec(s + c * V));
-      else d[c] = s[c];
+      if constexpr (VEC) {
+        const Vec<T> a = load_vec(s0 + c * V), b = load_vec(s1 + c * V);
+        store_vec(d0 + c * V, a);
+        if (two) store_vec(d1 + c * V, b);
+      } else {
+        const T a = s0[c], b = s1[c];
+        d0[c] = a;
+        if (two) d1[c] = b;
+      }
     }
   }
 }
@@ -283,7 +308,8 @@ MOE_API int moe_gather_rows(const void* hidden, const int32_t* sort_idx, int k, 
   if (rows < 0 || H < 0 || k <= 0) return MOE_ERR_SHAPE;
   if (rows == 0 || H == 0) return MOE_OK;
   if (!hidden || !sort_idx || !out) return MOE_ERR_NULL;
-  const int64_t g64 = rows < (int64_t)sm_count() * 16 ? rows : (int64_t)sm_count() * 16;
+  const int64_t pairs = (rows + 1) / 2;
+  const int64_t g64 = pairs < (int64_t)sm_count() * 16 ? pairs : (int64_t)sm_count() * 16;
   const int grid = (int)g64;
   MOE_DISPATCH_FLOAT(dtype, T, {
     const bool vec = aligned16(hidden) && aligned16(out) && (H % Vec<T>::N == 0);
