@@ -166,7 +166,9 @@ def config_dict(args, cfg):
     return {"workload": f"Qwen3-30B-A3B {args.workload} grouped GEMM fwd+dX+dW: {cfg['tokens']} tokens x top-{cfg['k']} = "
                         f"{cfg['tokens'] * cfg['k']} rows/GPU, in={cfg['K']}, out={cfg['N']}, experts={cfg['E']}",
             "routing": cfg["routing"], "l2": "inputs larger than L2 (weights alone exceed 400 MB); no flush needed",
-            "parallelism": "single GPU" if args.gpus == 1 else f"expert parallel ep{args.gpus} (all-to-all dispatch/combine)"}
+            "parallelism": "single GPU" if args.gpus == 1 else (
+                f"expert parallel ep{args.gpus}, rows pushed over peer memory, GEMM epilogues store to the source rank"
+                if args.ep_transport == "peer" else f"expert parallel ep{args.gpus} (NCCL all-to-all dispatch/combine)")}
 
 
 def time_cuda(fn, iters: int = 20, warmup: int = 3, flush=None) -> float:
@@ -293,6 +295,22 @@ def run_kernel_suite(args):
         del x, dy
     del packed, state, Gq, Uq, Wq, lor
 
+    # ---- library comparison: torch's own grouped GEMM (a CUTLASS library kernel) on the gate_up forward ----
+    M, N, K = 65536, 1536, 2048
+    x = torch.randn(M, K, device=dev, dtype=bf)
+    wg = mk(E, N, K, sc=0.02)
+    m_sizes = torch.full((E,), M // E, device=dev, dtype=torch.int32)
+    ours = time_cuda(lambda: grouped_gemm_forward(x, wg, m_sizes), iters=20)
+    try:
+        offs = torch.cumsum(m_sizes, 0).to(torch.int32)
+        wt = wg.transpose(1, 2)
+        lib_ms = time_cuda(lambda: torch._grouped_mm(x, wt, offs=offs), iters=20)
+        emit("gate_up forward vs torch._grouped_mm (library)", ours, flops=2.0 * M * N * K, library_ms=lib_ms,
+             library_tflops=2.0 * M * N * K / lib_ms / 1e9, speedup_vs_library=lib_ms / ours)
+    except Exception as exc:  # the library op is optional: report why it is missing
+        emit("gate_up forward vs torch._grouped_mm (library)", ours, flops=2.0 * M * N * K, library="unavailable: " + str(exc)[:120])
+    del x, wg
+
     # ---- one full MoE block forward at the block workload (16384 tokens) ----
     T = 16384
     hidden = torch.randn(1, T, 2048, device=dev, dtype=bf)
@@ -320,6 +338,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (reduced profiling case)")
     ap.add_argument("--experts", type=int, default=None, help="override the expert count (reduced profiling case)")
     ap.add_argument("--only", default=None, choices=["fwd", "dx", "dw"], help="run one of the three GEMMs per step")
+    ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: rows move by peer-memory stores fused with the GEMM epilogue (default) or by NCCL all-to-all")
     ap.add_argument("--gemm-path", default="auto", choices=["auto", "tc", "tc_single", "simt"],
                     help="kernel family for the grouped GEMMs (default: CTA-pair tcgen05 where eligible)")
     args = ap.parse_args()
@@ -395,14 +415,26 @@ def main():
     m_sizes, sort_idx, inv_sort_idx = route_and_sort(logits_d, ids_d)
     x_d = _gather_rows(hidden_d, sort_idx, k)
     plan = None
-    if world > 1:
+    peer = None
+    if world > 1 and args.ep_transport == "nccl":
         plan = ExpertParallelPlan.build(m_sizes, world, rank, dev)
+    elif world > 1:
+        from qwen3_moe_fused.parallel_ep import PeerChannel, PeerPlan, peer_fence, peer_grouped_gemm, peer_push
+
+        # receive buffers hold up to twice the even share of rows; results return into buffers of M rows
+        cap = 2 * M
+        peer = {"plan": PeerPlan.build(m_sizes, world, rank), "x": PeerChannel(cap, K, bf, dev),
+                "dy": PeerChannel(cap, N, bf, dev), "y": PeerChannel(M, N, bf, dev), "dx": PeerChannel(M, K, bf, dev),
+                "token": torch.zeros(1, device=dev)}
+        assert int(peer["plan"].recv_rows) <= cap, "receive buffer too small for this routing"
+        peer_fence(peer["token"])
     torch.cuda.synchronize()
 
     comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
     ev = lambda: torch.cuda.Event(enable_timing=True)
     kernel_ms = {"fwd": [], "dx": [], "dw": []}
-    launches_per_step = 3
+    # GEMMs, plus per step at N > 1: two row pushes (peer) or four row permutations (nccl)
+    launches_per_step = 3 if world == 1 else (5 if args.ep_transport == "peer" else 7)
 
     def step_resident(record: bool):
         if world == 1:
@@ -419,6 +451,36 @@ def main():
                 dw = grouped_gemm_backward_dw(x_d, dy_d, m_sizes, bf)
             marks[3].record()
             return marks if record else None, (y, dx, dw)
+        if peer is not None:
+            # expert parallel over peer memory: rows are pushed to their experts' ranks by a copy
+            # kernel (the second push overlaps the forward GEMM), the forward and dX epilogues store
+            # their results straight into the source ranks' memory; a one-element all-reduce orders
+            # each phase across the ranks.
+            #   comm:    push x | fence | push dy | fence
+            #   compute:                | forward           | dX | dW | fence
+            marks = [ev() for _ in range(4)]
+            main = torch.cuda.current_stream()
+            e_x, e_dy = torch.cuda.Event(), torch.cuda.Event()
+            pl = peer["plan"]
+            comm_stream.wait_stream(main)
+            with torch.cuda.stream(comm_stream):
+                peer_push(pl, x_d, peer["x"])
+                peer_fence(peer["token"])
+                e_x.record()
+                peer_push(pl, dy_d, peer["dy"])
+                peer_fence(peer["token"])
+                e_dy.record()
+            main.wait_event(e_x)
+            marks[0].record()
+            peer_grouped_gemm(pl, peer["x"], w, peer["y"])
+            marks[1].record()
+            main.wait_event(e_dy)
+            peer_grouped_gemm(pl, peer["dy"], w, peer["dx"], transposed=True)
+            marks[2].record()
+            dw = grouped_gemm_backward_dw(peer["x"].local, peer["dy"].local, pl.local_m_sizes, bf)
+            marks[3].record()
+            peer_fence(peer["token"])  # results of every rank have arrived; buffers may be reused
+            return marks if record else None, (peer["y"].local, peer["dx"].local, dw)
         # expert parallel: rows to their experts, compute, results back.  The all-to-alls and
         # their permutation passes run on a second stream so that they overlap the GEMMs:
         #   comm:    dispatch x | dispatch dy |            combine y |           combine dx
@@ -494,6 +556,16 @@ def main():
             y = grouped_gemm_forward(xs, w, ms)
             dx = grouped_gemm_forward_transposed(dyd, w, ms)
             dw = grouped_gemm_backward_dw(xs, dyd, ms, bf)
+        elif peer is not None:
+            pl = PeerPlan.build(ms, world, rank)
+            peer_push(pl, xs, peer["x"])
+            peer_push(pl, dyd, peer["dy"])
+            peer_fence(peer["token"])
+            peer_grouped_gemm(pl, peer["x"], w, peer["y"])
+            peer_grouped_gemm(pl, peer["dy"], w, peer["dx"], transposed=True)
+            dw = grouped_gemm_backward_dw(peer["x"].local, peer["dy"].local, pl.local_m_sizes, bf)
+            peer_fence(peer["token"])
+            y, dx = peer["y"].local, peer["dx"].local
         else:
             pl = ExpertParallelPlan.build(ms, world, rank, dev)
             xl, dyl = pl.dispatch(xs), pl.dispatch(dyd)

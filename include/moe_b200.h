@@ -173,6 +173,41 @@ int moe_gather_rows(const void* hidden, const int32_t* sort_idx, int k, void* ou
 int moe_combine(const void* y, const int32_t* inv_sort_idx, const void* weights, void* out,
                 int64_t T, int k, int H, int dtype, void* stream);
 
+/* ---------------------------------------------------------------------------------
+ * Expert parallelism over peer memory.  The reference has no multi-GPU path
+ * (README.md:26 lists it as open); these entry points have no counterpart there.
+ * A "group" is the run of rows that one source rank sent for one local expert.
+ * ------------------------------------------------------------------------------- */
+
+/* Rows sorted by expert (m_sizes[e] rows each, M in total, row_bytes each) are copied to
+ * one destination per expert: row i of expert e goes to dst_ptrs[e] + i * row_bytes, rows
+ * with i >= dst_limit[e] are dropped (dst_limit may be NULL).  dst_ptrs is a DEVICE array
+ * of E 64-bit addresses, 16-byte aligned, in this GPU's memory or in a peer GPU's memory
+ * mapped into this process; the stores are plain global stores.  The call neither waits
+ * for nor signals the receiver.  max_ctas <= 0 picks a grid from the SM count. */
+int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, const void* m_sizes,
+                     int m_sizes_dtype, int E, const uint64_t* dst_ptrs,
+                     const int32_t* dst_limit, int max_ctas, void* stream);
+
+/* moe_grouped_gemm_fwd / moe_grouped_gemm_dx over G groups where group g multiplies by
+ * weight slice weight_index[g] (NULL: slice g) of n_weights, and its output rows are
+ * written from the address out_ptrs[g] on (DEVICE array of G 64-bit addresses, 16-byte
+ * aligned, local or peer memory) instead of into one contiguous y: the epilogue's TMA
+ * stores go straight to the rank that owns the tokens.  out_template is any 16-byte
+ * aligned buffer of at least one output row (only its address seeds the tensor maps).
+ * Tensor-core CTA-pair kernels only: bf16/fp16 in and out, N >= 192, workspace required;
+ * MOE_ERR_UNSUPPORTED otherwise. */
+int moe_grouped_gemm_fwd_scattered(const void* x, const void* w, const void* group_sizes,
+                                   int group_sizes_dtype, const int32_t* weight_index,
+                                   int n_weights, const uint64_t* out_ptrs, void* out_template,
+                                   int64_t M, int N, int K, int G, int dtype_in, int dtype_out,
+                                   void* ws, size_t ws_bytes, void* stream);
+int moe_grouped_gemm_dx_scattered(const void* x, const void* w, const void* group_sizes,
+                                  int group_sizes_dtype, const int32_t* weight_index,
+                                  int n_weights, const uint64_t* out_ptrs, void* out_template,
+                                  int64_t M, int N, int K, int G, int dtype_in, int dtype_out,
+                                  void* ws, size_t ws_bytes, void* stream);
+
 /* Diagnostics.  Every wait inside the tensor-core kernels is bounded; a wait that gave up
  * records (reason << 16 | CTA index) in a device-side word.  This call copies that word to
  * *flag_out (0 = no wait was ever abandoned) and optionally clears it.  It synchronises

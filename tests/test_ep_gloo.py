@@ -83,3 +83,63 @@ def test_split_sizes_and_row_ids():
     assert split_sizes(m, 4) == [3, 7, 2, 4]
     rc = torch.tensor([[2, 0, 1], [1, 1, 0]])
     assert local_expert_of_received_rows(rc).tolist() == [0, 0, 2, 0, 1]
+
+
+def _peer_worker(rank, world, port, E, rows_per_rank, H, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from qwen3_moe_fused.parallel_ep import PeerPlan
+
+        g = torch.Generator().manual_seed(100 + rank)
+        ids = torch.randint(0, E, (rows_per_rank,), generator=g)
+        if rank == 0:
+            ids[ids == 1] = 0
+        counts, inv_idx, _ = _cpu_sort(ids, E)
+        x = torch.randn(rows_per_rank, H, generator=g)
+        plan = PeerPlan.build(counts, world, rank)
+        torch.save({"xs": x[inv_idx.long()], "ids_sorted": ids[inv_idx.long()], "plan": plan.__dict__},
+                   os.path.join(out_dir, f"p{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_peer_plan_addresses(tmp_path, world):
+    """The peer-memory plan: replaying every rank's pushes on the host fills each owner's buffer
+    in (local expert, source) order, and replaying the scattered GEMM outputs puts every row back
+    at its position on its source rank."""
+    E, rows, H = 8, 300, 5
+    mp.spawn(_peer_worker, args=(world, _free_port(), E, rows, H, str(tmp_path)), nprocs=world, join=True)
+    saved = [torch.load(tmp_path / f"p{r}.pt", weights_only=False) for r in range(world)]
+    e_local = E // world
+    cap = rows * world
+    recv = [torch.full((cap, H), float("nan")) for _ in range(world)]
+    for s in range(world):
+        p, xs = saved[s]["plan"], saved[s]["xs"]
+        begins = torch.cumsum(p["m_sizes"].long(), 0) - p["m_sizes"].long()
+        for e in range(E):
+            n, d = int(p["m_sizes"][e]), int(p["dst_rank"][e])
+            assert d == e // e_local
+            recv[d][int(p["send_row"][e]):int(p["send_row"][e]) + n] = xs[int(begins[e]):int(begins[e]) + n]
+    back = [torch.full((rows, H), float("nan")) for _ in range(world)]
+    for r in range(world):
+        p = saved[r]["plan"]
+        chunks = []
+        for e in range(r * e_local, (r + 1) * e_local):
+            for src in range(world):
+                chunks.append(saved[src]["xs"][saved[src]["ids_sorted"] == e])
+        expect = torch.cat(chunks)
+        assert int(p["recv_rows"]) == expect.shape[0]
+        assert torch.equal(recv[r][:expect.shape[0]], expect)
+        assert p["local_m_sizes"].tolist() == [sum(int((saved[s]["ids_sorted"] == e).sum()) for s in range(world))
+                                               for e in range(r * e_local, (r + 1) * e_local)]
+        assert p["weight_index"].tolist() == [g // world for g in range(E)]
+        # results of group g (here: the rows themselves) go to their source rank
+        start = 0
+        for gi in range(e_local * world):
+            n, s = int(p["group_sizes"][gi]), int(p["group_src"][gi])
+            back[s][int(p["return_row"][gi]):int(p["return_row"][gi]) + n] = recv[r][start:start + n]
+            start += n
+    for s in range(world):
+        assert torch.equal(back[s], saved[s]["xs"])

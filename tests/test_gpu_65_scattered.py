@@ -1,0 +1,101 @@
+"""The peer-memory building blocks on one GPU: the row push to per-expert addresses and the
+scattered forward / dX (several groups per weight slice, one output address per group).  The
+"peer" buffers here are ordinary local buffers; on several GPUs only the addresses differ."""
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import random_m_sizes
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    return torch.device("cuda", 0)
+
+
+@pytest.mark.parametrize("E,M,W", [(8, 1000, 256), (128, 20000, 2048), (5, 7, 8), (16, 513, 776)])
+def test_push_rows(dev, E, M, W):
+    from qwen3_moe_fused.parallel_ep import push_rows
+
+    rng = np.random.default_rng(E * 7 + M)
+    m = random_m_sizes(rng, M, E, empty_frac=0.2)
+    rows = torch.randn(M, W, device=dev).to(torch.bfloat16)
+    # every expert gets a slot of its own in one of two buffers, in a shuffled order, with one
+    # expert's slot shorter than its rows
+    order = rng.permutation(E)
+    limit = m.copy()
+    big = int(np.argmax(m))
+    limit[big] = m[big] // 2
+    bufs = [torch.full((M + 8, W), -1.0, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    ptrs = np.zeros(E, np.int64)
+    slot = {}
+    fill = [0, 0]
+    for e in order:
+        b = int(e) % 2
+        slot[int(e)] = (b, fill[b])
+        ptrs[e] = bufs[b].data_ptr() + fill[b] * W * 2
+        fill[b] += int(limit[e])
+    push_rows(rows, torch.from_numpy(m).to(dev), torch.from_numpy(ptrs).to(dev), torch.from_numpy(limit.astype(np.int32)).to(dev))
+    torch.cuda.synchronize()
+    begins = np.concatenate([[0], np.cumsum(m)])
+    for e in range(E):
+        b, at = slot[e]
+        n = int(limit[e])
+        assert torch.equal(bufs[b][at:at + n], rows[begins[e]:begins[e] + n]), f"expert {e}"
+    for b in range(2):
+        assert bool((bufs[b][fill[b]:] == -1.0).all()), "rows past the limits were written"
+
+
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("E_w,world,M,N,K", [(4, 2, 3000, 384, 256), (8, 4, 9000, 768, 512), (3, 1, 700, 200, 72)])
+def test_scattered_gemm(dev, transposed, dtype, E_w, world, M, N, K):
+    from qwen3_moe_fused.grouped_gemm.forward import grouped_gemm_forward
+    from qwen3_moe_fused.grouped_gemm.forward_transposed import grouped_gemm_forward_transposed
+    from qwen3_moe_fused.parallel_ep import scattered_grouped_gemm
+
+    rng = np.random.default_rng(M + N)
+    G = E_w * world
+    sizes = random_m_sizes(rng, M, G, empty_frac=0.15)
+    x = torch.randn(M, K, device=dev).to(dtype)
+    w = (torch.randn(E_w, N, K, device=dev) * 0.05).to(dtype)
+    if transposed:
+        w = w.transpose(1, 2).contiguous()  # (E_w, K, N): dX reads the weight (E, out=K, in=N)
+    widx = torch.arange(G, device=dev, dtype=torch.int32) // world
+    # reference: the plain grouped GEMM over per-group copies of the weight slices
+    w_rep = w[widx.long()].contiguous()
+    fn = grouped_gemm_forward_transposed if transposed else grouped_gemm_forward
+    ref = fn(x, w_rep, torch.from_numpy(sizes).to(dev))
+    # group g's results go to buffer g % world, groups packed there in reverse order
+    bufs = [torch.full((M + 4, N), 7.0, device=dev, dtype=dtype) for _ in range(world)]
+    ptrs = np.zeros(G, np.int64)
+    where = {}
+    fill = [0] * world
+    for g in reversed(range(G)):
+        b = g % world
+        where[g] = (b, fill[b])
+        ptrs[g] = bufs[b].data_ptr() + fill[b] * N * 2
+        fill[b] += int(sizes[g])
+    scattered_grouped_gemm(x, w, torch.from_numpy(sizes).to(dev), widx, torch.from_numpy(ptrs).to(dev), bufs[0], transposed)
+    torch.cuda.synchronize()
+    begins = np.concatenate([[0], np.cumsum(sizes)])
+    for g in range(G):
+        b, at = where[g]
+        n = int(sizes[g])
+        assert torch.equal(bufs[b][at:at + n], ref[begins[g]:begins[g] + n]), f"group {g}"
+    for b in range(world):
+        assert bool((bufs[b][fill[b]:] == 7.0).all()), "rows outside the groups were written"
+
+
+def test_scattered_rejects_thin(dev):
+    from qwen3_moe_fused import _lib
+    from qwen3_moe_fused.parallel_ep import scattered_grouped_gemm
+
+    x = torch.randn(64, 64, device=dev).to(torch.bfloat16)
+    w = torch.randn(2, 64, 64, device=dev).to(torch.bfloat16)
+    out = torch.empty(64, 64, device=dev, dtype=torch.bfloat16)
+    ptrs = torch.tensor([out.data_ptr(), out.data_ptr() + 32 * 128], device=dev)
+    with pytest.raises(_lib.MoeB200Error):
+        scattered_grouped_gemm(x, w, torch.tensor([32, 32], device=dev, dtype=torch.int32), None, ptrs, out)

@@ -86,3 +86,95 @@ def test_expert_parallel_matches_single_gpu(tmp_path):
             ref = dys[sel].T @ xs[sel]
             got = saved[r]["dw"][le].float().numpy()
             assert O.rel_err(got, ref) < 1e-2 if sel.any() else not got.any(), f"dW of expert {e}"
+
+
+def _peer_worker(rank, world, port, out_dir):
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    for p in (str(root), str(root / "transformers-qwen3-moe-fused_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from qwen3_moe_fused import _lib
+        from qwen3_moe_fused.grouped_gemm.backward_dw import grouped_gemm_backward_dw
+        from qwen3_moe_fused.grouped_gemm.forward import grouped_gemm_forward
+        from qwen3_moe_fused.grouped_gemm.forward_transposed import grouped_gemm_forward_transposed
+        from qwen3_moe_fused.kernels.indexing import get_expert_counts_and_idx
+        from qwen3_moe_fused.parallel_ep import PeerChannel, PeerPlan, peer_fence, peer_grouped_gemm, peer_push
+
+        E, K, N, rows = 16, 256, 384, 3000
+        bf = torch.bfloat16
+        e_local = E // world
+        gw = torch.Generator().manual_seed(7)
+        w_all = (torch.randn(E, N, K, generator=gw) * 0.05).to(bf)
+        g = torch.Generator().manual_seed(100 + rank)
+        ids = torch.randint(0, E, (rows,), generator=g)
+        ids[ids == 3] = 2  # expert 3 receives nothing from anybody
+        x = torch.randn(rows, K, generator=g).to(bf)
+        dy = torch.randn(rows, N, generator=g).to(bf)
+        counts, inv_idx, idx = get_expert_counts_and_idx(ids.to(dev), E)
+        xs = x.to(dev)[inv_idx.long()].contiguous()
+        dys = dy.to(dev)[inv_idx.long()].contiguous()
+        w_local = w_all[rank * e_local:(rank + 1) * e_local].to(dev).contiguous()
+
+        plan = PeerPlan.build(counts, world, rank)
+        cap = rows * world
+        ch_x, ch_dy = PeerChannel(cap, K, bf, dev), PeerChannel(cap, N, bf, dev)
+        ch_y, ch_dx = PeerChannel(rows, N, bf, dev), PeerChannel(rows, K, bf, dev)
+        ch_y.local.fill_(9.0)
+        ch_dx.local.fill_(9.0)
+        token = torch.zeros(1, device=dev)
+        peer_fence(token)                       # every rank's buffers exist and are initialised
+        peer_push(plan, xs, ch_x)
+        peer_push(plan, dys, ch_dy)
+        peer_fence(token)                       # every rank's rows have arrived
+        peer_grouped_gemm(plan, ch_x, w_local, ch_y)
+        peer_grouped_gemm(plan, ch_dy, w_local, ch_dx, transposed=True)
+        dw = grouped_gemm_backward_dw(ch_x.local, ch_dy.local, plan.local_m_sizes, bf)
+        peer_fence(token)                       # every rank's results have arrived
+        torch.cuda.synchronize()
+        assert _lib.read_error_flag() == 0
+        y_ref = grouped_gemm_forward(xs, w_all.to(dev), counts)
+        dx_ref = grouped_gemm_forward_transposed(dys, w_all.to(dev), counts)
+        torch.cuda.synchronize()
+        for name, got, ref in (("y", ch_y.local, y_ref), ("dx", ch_dx.local, dx_ref)):
+            err = float((got.float() - ref.float()).abs().max() / ref.float().abs().max())
+            assert err < 1e-2, f"rank {rank}: {name} mismatch {err}"
+        torch.save({"xs": xs.cpu(), "dys": dys.cpu(), "ids": ids[inv_idx.cpu().long()], "dw": dw.cpu(),
+                    "exact": bool(torch.equal(ch_y.local, y_ref) and torch.equal(ch_dx.local, dx_ref))},
+                   os.path.join(out_dir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_memory_expert_parallel_matches_single_gpu(tmp_path):
+    """Row push over peer memory + forward / dX with TMA stores into the source rank's memory."""
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    from oracle import moe_oracle as O
+
+    mp.spawn(_peer_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    saved = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
+    E, e_local = 16, 8
+    xs = torch.cat([s["xs"] for s in saved]).float().numpy()
+    dys = torch.cat([s["dys"] for s in saved]).float().numpy()
+    ids = torch.cat([s["ids"] for s in saved]).numpy()
+    for r in range(world):
+        for le in range(e_local):
+            e = r * e_local + le
+            sel = ids == e
+            ref = dys[sel].T @ xs[sel]
+            got = saved[r]["dw"][le].float().numpy()
+            assert O.rel_err(got, ref) < 1e-2 if sel.any() else not got.any(), f"dW of expert {e}"

@@ -17,7 +17,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT = HERE / "qwen3_moe_fused" / "libmoe_b200.so"
 OBJ_DIR = HERE / "build"
-SOURCES = ["sort.cu", "simt_gemm.cu", "elementwise.cu", "router.cu", "tc_gemm.cu", "gemm_api.cu"]
+SOURCES = ["sort.cu", "simt_gemm.cu", "elementwise.cu", "router.cu", "ep.cu", "tc_gemm.cu", "gemm_api.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

@@ -1,0 +1,96 @@
+// Expert-parallel row movement over peer memory (NVLink): rows that are sorted by expert are
+// copied, segment by segment, to one destination address per expert.  The destination may be
+// local memory or a peer GPU's memory mapped into this process; the stores are plain 16-byte
+// global stores, posted over NVLink when the address is remote.  The kernel waits on nothing
+// and signals nothing: ordering against the consumer is the caller's (stream order plus a
+// collective or event on both sides).
+#include "common.cuh"
+
+namespace moe {
+
+constexpr int PUSH_THREADS = 256;
+constexpr int PUSH_MAX_E = 1024;
+
+// begins[e] = rows before expert e; computed by warp 0, E / 32 consecutive entries per lane.
+__device__ __forceinline__ void push_build_begins(const void* m_sizes, int ms64, int E, int* begins) {
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    const int per = (E + 31) / 32;
+    const int lo = min(lane * per, E), hi = min(lo + per, E);
+    int sum = 0;
+    for (int e = lo; e < hi; ++e)
+      sum += ms64 ? (int)reinterpret_cast<const int64_t*>(m_sizes)[e] : reinterpret_cast<const int32_t*>(m_sizes)[e];
+    int incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
+    }
+    int run = incl - sum;
+    for (int e = lo; e < hi; ++e) {
+      begins[e] = run;
+      run += ms64 ? (int)reinterpret_cast<const int64_t*>(m_sizes)[e] : reinterpret_cast<const int32_t*>(m_sizes)[e];
+    }
+    if (lane == 31) begins[E] = incl;
+  }
+  __syncthreads();
+}
+
+// One warp per row; each lane keeps up to UNROLL 16-byte vectors in flight.
+template <int UNROLL>
+__global__ void __launch_bounds__(PUSH_THREADS)
+ep_push_rows_kernel(const uint4* __restrict__ rows, int64_t M, int row_vecs, const void* __restrict__ m_sizes, int ms64,
+                    int E, const uint64_t* __restrict__ dst_ptrs, const int32_t* __restrict__ dst_limit) {
+  __shared__ int begins[PUSH_MAX_E + 1];
+  push_build_begins(m_sizes, ms64, E, begins);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warps = PUSH_THREADS / 32;
+  const int64_t total = min(M, (int64_t)begins[E]);
+  for (int64_t r = (int64_t)blockIdx.x * warps + warp; r < total; r += (int64_t)gridDim.x * warps) {
+    // expert of row r: last e with begins[e] <= r
+    int lo = 0, hi = E;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (begins[mid] <= (int)r) lo = mid; else hi = mid;
+    }
+    const int e = lo;
+    const int local = (int)r - begins[e];
+    if (dst_limit != nullptr && local >= dst_limit[e]) continue;  // would overrun the receiver's buffer
+    const uint4* src = rows + r * row_vecs;
+    uint4* dst = reinterpret_cast<uint4*>(dst_ptrs[e]) + (int64_t)local * row_vecs;
+    for (int c0 = 0; c0 < row_vecs; c0 += 32 * UNROLL) {
+      uint4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int c = c0 + u * 32 + lane;
+        if (c < row_vecs) v[u] = __ldg(src + c);
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int c = c0 + u * 32 + lane;
+        if (c < row_vecs) dst[c] = v[u];
+      }
+    }
+  }
+}
+
+}  // namespace moe
+
+using namespace moe;
+
+MOE_API int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, const void* m_sizes, int m_sizes_dtype,
+                             int E, const uint64_t* dst_ptrs, const int32_t* dst_limit, int max_ctas, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!is_int_dtype(m_sizes_dtype)) return MOE_ERR_DTYPE;
+  if (M < 0 || row_bytes < 0 || E <= 0 || E > PUSH_MAX_E || M > 0x7fffffffLL) return MOE_ERR_SHAPE;
+  if (M == 0 || row_bytes == 0) return MOE_OK;
+  if (!rows || !m_sizes || !dst_ptrs) return MOE_ERR_NULL;
+  if ((row_bytes & 15) || ((uintptr_t)rows & 15)) return MOE_ERR_ALIGN;
+  const int warps = PUSH_THREADS / 32;
+  int64_t grid = (M + warps - 1) / warps;
+  const int64_t cap = max_ctas > 0 ? max_ctas : (int64_t)sm_count() * 4;
+  if (grid > cap) grid = cap;
+  ep_push_rows_kernel<8><<<(int)grid, PUSH_THREADS, 0, stream>>>(
+      reinterpret_cast<const uint4*>(rows), M, (int)(row_bytes / 16), m_sizes, m_sizes_dtype == MOE_I64, E, dst_ptrs, dst_limit);
+  return launch_status();
+}

@@ -20,6 +20,10 @@ bool tc_nf4_eligible(const void* x, const void* packed, const void* absmax, cons
 int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code, const float* absmax, int blocksize,
                         const void* m_sizes, int ms64, void* out, int64_t M, int N, int K, int E,
                         int dtype_in, int dtype_out, void* ws, size_t ws_bytes, cudaStream_t stream);
+int tc_grouped_gemm_scattered(int which, const void* a, const void* b, const void* group_sizes, int ms64,
+                              const int* weight_index, int n_weights, const uint64_t* out_ptrs, void* out_template,
+                              int64_t M, int N, int K, int G, int dtype_in, int dtype_out, void* ws, size_t ws_bytes,
+                              cudaStream_t stream);
 int tc_read_error(int* flag_out, bool clear);
 const char* tc_last_detail();
 
@@ -138,6 +142,39 @@ MOE_API int moe_grouped_gemm_fwd_nf4(const void* x, const uint8_t* packed, const
   if (can_tc && path != MOE_PATH_SIMT)
     return tc_grouped_gemm_nf4(x, packed, code, absmax, blocksize, m_sizes, msd == MOE_I64, y, M, N, K, E, dtype_in, dtype_out, ws, ws_bytes, (cudaStream_t)stream);
   return simt_grouped_gemm_nf4(x, packed, code, absmax, shift, m_sizes, msd == MOE_I64, y, M, N, K, E, dtype_in, dtype_out, (cudaStream_t)stream);
+}
+
+static int run_scattered(int which, const void* x, const void* w, const void* group_sizes, int msd,
+                         const int32_t* weight_index, int n_weights, const uint64_t* out_ptrs, void* out_template,
+                         int64_t M, int N, int K, int G, int dtype_in, int dtype_out, void* ws, size_t ws_bytes,
+                         void* stream) {
+  int st = check_common(x, w, group_sizes, msd, out_template, M, N, K, G, dtype_in, dtype_out);
+  if (st != MOE_OK) return st;
+  if (n_weights <= 0 || !out_ptrs) return n_weights <= 0 ? MOE_ERR_SHAPE : MOE_ERR_NULL;
+  if (M == 0 || N == 0) return MOE_OK;
+  if (!device_is_sm100()) return MOE_ERR_DEVICE;
+  // only the CTA-pair tensor-core kernels have per-group output maps
+  if (K == 0 || N < 192 || dtype_out == MOE_F32 || !tc_eligible(which, x, w, out_template, M, N, K, G, dtype_in, dtype_out))
+    return MOE_ERR_UNSUPPORTED;
+  if (!ws || ws_bytes < moe_grouped_gemm_workspace_bytes(which, M, N, K, G)) return MOE_ERR_WORKSPACE;
+  return tc_grouped_gemm_scattered(which, x, w, group_sizes, msd == MOE_I64, weight_index, n_weights, out_ptrs,
+                                   out_template, M, N, K, G, dtype_in, dtype_out, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+MOE_API int moe_grouped_gemm_fwd_scattered(const void* x, const void* w, const void* group_sizes, int msd,
+                                           const int32_t* weight_index, int n_weights, const uint64_t* out_ptrs,
+                                           void* out_template, int64_t M, int N, int K, int G, int dtype_in,
+                                           int dtype_out, void* ws, size_t ws_bytes, void* stream) {
+  return run_scattered(0, x, w, group_sizes, msd, weight_index, n_weights, out_ptrs, out_template, M, N, K, G, dtype_in,
+                       dtype_out, ws, ws_bytes, stream);
+}
+
+MOE_API int moe_grouped_gemm_dx_scattered(const void* x, const void* w, const void* group_sizes, int msd,
+                                          const int32_t* weight_index, int n_weights, const uint64_t* out_ptrs,
+                                          void* out_template, int64_t M, int N, int K, int G, int dtype_in,
+                                          int dtype_out, void* ws, size_t ws_bytes, void* stream) {
+  return run_scattered(1, x, w, group_sizes, msd, weight_index, n_weights, out_ptrs, out_template, M, N, K, G, dtype_in,
+                       dtype_out, ws, ws_bytes, stream);
 }
 
 MOE_API int moe_debug_read_error(int* flag_out, int clear) {

@@ -144,6 +144,10 @@ __device__ __forceinline__ void tensormap_replace_dim(void* smem_map, uint32_t e
   asm volatile("tensormap.replace.tile.global_dim.shared::cta.b1024.b32 [%0], %1, %2;"
                ::"l"((uint64_t)smem_u32(smem_map)), "n"(ORD), "r"(extent) : "memory");
 }
+__device__ __forceinline__ void tensormap_replace_address(void* smem_map, uint64_t global_address) {
+  asm volatile("tensormap.replace.tile.global_address.shared::cta.b1024.b64 [%0], %1;"
+               ::"l"((uint64_t)smem_u32(smem_map)), "l"(global_address) : "memory");
+}
 // Whole warp: copies the 128-byte map from shared to global memory with release semantics.
 __device__ __forceinline__ void tensormap_publish(void* gmem_dst, void* smem_src) {
   asm volatile("tensormap.cp_fenceproxy.global.shared::cta.tensormap::generic.release.gpu.sync.aligned [%0], [%1], 128;"

@@ -39,6 +39,7 @@ struct GemmParams {
   int dtype_out;  // MOE_F32 / MOE_BF16 / MOE_F16
   uint32_t idesc;
   const CUtensorMap* group_maps;  // per-expert tensor maps in workspace ([slot][expert]), or null
+  const int* weight_index = nullptr;  // weight slice of each group (null: group e uses slice e)
   int debug;      // experiment switches (MOE_B200_DEBUG): 1 = no global stores, 2 = no TMEM loads, 4 = no MMA,
                   // 32 = pair forward / dX without per-expert maps (register-store epilogue),
                   // 64 = single-CTA NF4 kernel instead of the pair one
@@ -670,11 +671,17 @@ static int launch_pair(void (*kernel)(KArgs...), int grid, int smem_bytes, cudaS
 template <typename... KArgs, typename... Args>
 static int launch_pair_threads(void (*kernel)(KArgs...), int grid, int threads, int smem_bytes, cudaStream_t stream, Args... args);
 
+// `weight_index` / `n_weights` / `out_ptrs` (all optional) describe the scattered form: group e
+// multiplies by weight slice weight_index[e] of n_weights, and its output rows start at the
+// address out_ptrs[e] instead of row row_start[e] of `out`.
 static int pair_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes, int ms64, void* out,
                              int64_t M, int N, int K, int E, int dtype_in, int dtype_out, void* ws, size_t ws_bytes,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, const int* weight_index = nullptr, int n_weights = 0,
+                             const uint64_t* out_ptrs = nullptr) {
   using namespace tc;
+  if (n_weights <= 0) n_weights = E;
   GemmParams p;
+  p.weight_index = weight_index;
   p.a = a; p.b = b;
   p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags();
   const int fmt = dtype_in == MOE_BF16 ? 1 : 0;
@@ -683,8 +690,8 @@ static int pair_grouped_gemm(int which, const void* a, const void* b, const void
   int st;
   if (which == 0 || which == 1) {
     // A = weight (accumulator rows), B = activations (accumulator columns = tokens)
-    if (which == 0) st = make_map(&mw, dtype_in, b, (uint64_t)K, (uint64_t)N, (uint64_t)E, 128);
-    else st = make_map(&mw, dtype_in, b, (uint64_t)N, (uint64_t)K, (uint64_t)E, BK);
+    if (which == 0) st = make_map(&mw, dtype_in, b, (uint64_t)K, (uint64_t)N, (uint64_t)n_weights, 128);
+    else st = make_map(&mw, dtype_in, b, (uint64_t)N, (uint64_t)K, (uint64_t)n_weights, BK);
     if (st != MOE_OK) return st;
     if ((st = make_map(&mx, dtype_in, a, (uint64_t)K, (uint64_t)M, 0, 128)) != MOE_OK) return st;
     p.idesc = make_idesc(fmt, which == 1, 0, 256, 0);  // N field is filled per tile
@@ -697,10 +704,13 @@ static int pair_grouped_gemm(int which, const void* a, const void* b, const void
       tm.t[GM_IN] = mx;
       if (tm.count == 2 && (st = make_map(&tm.t[GM_OUT], dtype_out, out, (uint64_t)N, (uint64_t)M, 0, 32)) != MOE_OK) return st;
       const int gm_smem = 8 * 128 + 2 * (E + 1) * 4 + 128;
-      build_group_maps_kernel<<<(E + 7) / 8, 256, gm_smem, stream>>>(tm, m_sizes, ms64, E, M, reinterpret_cast<CUtensorMap*>(ws));
+      build_group_maps_kernel<<<(E + 7) / 8, 256, gm_smem, stream>>>(tm, m_sizes, ms64, E, M, reinterpret_cast<CUtensorMap*>(ws),
+                                                                     out_ptrs, GM_OUT, (int64_t)N * 2);
       if ((st = launch_status()) != MOE_OK) return st;
       p.group_maps = reinterpret_cast<const CUtensorMap*>(ws);
     }
+    // scattered outputs exist only as per-group output maps
+    if (out_ptrs != nullptr && (p.group_maps == nullptr || dtype_out == MOE_F32)) return MOE_ERR_UNSUPPORTED;
     const int bytes = PAIR_STAGES * 2 * PAIR_HALF_BYTES + 4 * PAIR_STAGING_BYTES + (int)sizeof(PairControl) + 2 * (E + 1) * 4 + 1024;
     if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
     if (which == 0) {
@@ -856,6 +866,17 @@ int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes
     return launch_status();
   }
   return MOE_ERR_UNSUPPORTED;
+}
+
+// Scattered forward (which = 0) / dX (which = 1) on the CTA-pair kernels: see pair_grouped_gemm.
+int tc_grouped_gemm_scattered(int which, const void* a, const void* b, const void* group_sizes, int ms64,
+                              const int* weight_index, int n_weights, const uint64_t* out_ptrs, void* out_template,
+                              int64_t M, int N, int K, int G, int dtype_in, int dtype_out, void* ws, size_t ws_bytes,
+                              cudaStream_t stream) {
+  bind_context_once();
+  if (which != 0 && which != 1) return MOE_ERR_UNSUPPORTED;
+  return pair_grouped_gemm(which, a, b, group_sizes, ms64, out_template, M, N, K, G, dtype_in, dtype_out, ws, ws_bytes,
+                           stream, weight_index, n_weights, out_ptrs);
 }
 
 bool tc_nf4_eligible(const void* x, const void* packed, const void* absmax, const void* out, int64_t M, int N, int K,

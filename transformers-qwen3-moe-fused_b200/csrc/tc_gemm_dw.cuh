@@ -28,9 +28,14 @@ struct GroupMapTemplates {
 
 // out[t * E + e] = templates.t[t] with the extent of dimension 1 (rows) set to the last row
 // of expert e (exclusive).  One warp per expert.
+// With `out_ptrs`, slot `ptr_slot` of group e is additionally re-based so that row row_start[e]
+// of the map is the address out_ptrs[e]: each group's rows then land in a buffer of their own
+// (possibly in a peer GPU's memory) while the kernels keep addressing rows by their position in
+// the concatenated input.  `row_bytes` is the pitch of that slot's rows.
 __global__ void __launch_bounds__(256)
 build_group_maps_kernel(const __grid_constant__ GroupMapTemplates tm, const void* __restrict__ m_sizes, int ms64,
-                        int E, int64_t M, CUtensorMap* __restrict__ out) {
+                        int E, int64_t M, CUtensorMap* __restrict__ out,
+                        const uint64_t* __restrict__ out_ptrs = nullptr, int ptr_slot = -1, int64_t row_bytes = 0) {
   extern __shared__ uint8_t gm_smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gm_smem_raw) + 127) & ~(uintptr_t)127);
   CUtensorMap* slots = reinterpret_cast<CUtensorMap*>(base);  // 8 slots, one per warp
@@ -44,7 +49,17 @@ build_group_maps_kernel(const __grid_constant__ GroupMapTemplates tm, const void
   for (int t = 0; t < tm.count; ++t) {
     reinterpret_cast<uint32_t*>(&slots[warp])[lane] = reinterpret_cast<const uint32_t*>(&tm.t[t])[lane];
     __syncwarp();
-    if (lane == 0) tensormap_replace_dim<1>(&slots[warp], row_end);
+    if (lane == 0) {
+      tensormap_replace_dim<1>(&slots[warp], row_end);
+      if (out_ptrs != nullptr && t == ptr_slot) {
+        uint64_t addr = out_ptrs[e];
+        if (addr & 15) {  // a tensor map needs a 16-byte aligned base: record it and keep the store legal
+          atomicCAS(&g_tc_error, 0, (16 << 16) | (e & 0xffff));
+          addr &= ~(uint64_t)15;
+        }
+        tensormap_replace_address(&slots[warp], addr - (uint64_t)row_start[e] * (uint64_t)row_bytes);
+      }
+    }
     __syncwarp();
     tensormap_publish(&out[(size_t)t * E + e], &slots[warp]);
     __syncwarp();

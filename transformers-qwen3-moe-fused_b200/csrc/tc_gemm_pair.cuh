@@ -166,6 +166,7 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       for (int64_t tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
         int e, t0, n_mma, n0;
         decode(tile, e, t0, n_mma, n0);
+        const int we = p.weight_index ? __ldg(p.weight_index + e) : e;  // several groups may share a weight slice
         const int w_row = n0 + (int)rank * 128;
         const int tok = t0 + (int)rank * (n_mma >> 1);
         // with per-expert maps the token rows past the group's end are zero-filled, not fetched
@@ -180,10 +181,10 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           const uint32_t bar = full_leader0 + s * 8;
           if (leader) mbar_expect_tx(&ctl->full[s], 2 * STAGE_BYTES);  // both CTAs' bytes
           if constexpr (!W_MN) {
-            tma_load_3d_pair(sa, &tmap_w, bar, kb * BK, w_row, e);
+            tma_load_3d_pair(sa, &tmap_w, bar, kb * BK, w_row, we);
           } else {
-            tma_load_3d_pair(sa, &tmap_w, bar, w_row, kb * BK, e);
-            tma_load_3d_pair(sa + BK * 128, &tmap_w, bar, w_row + 64, kb * BK, e);
+            tma_load_3d_pair(sa, &tmap_w, bar, w_row, kb * BK, we);
+            tma_load_3d_pair(sa + BK * 128, &tmap_w, bar, w_row + 64, kb * BK, we);
           }
           tma_load_2d_pair(sb, mx, bar, kb * BK, tok);
         }

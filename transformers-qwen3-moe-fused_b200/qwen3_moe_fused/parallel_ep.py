@@ -95,3 +95,154 @@ class ExpertParallelPlan:
 
     def grouped_dw(self, fn: Callable, x: torch.Tensor, dy: torch.Tensor, dtype, e_local: int) -> torch.Tensor:
         return fn(x, dy, self.local_group_sizes, dtype)
+
+
+# ------------------------------------------------------------------------------------------
+# Expert parallelism over peer memory: no all-to-all.  Every rank maps every other rank's
+# receive buffers (symmetric memory over NVLink); rows are pushed by a copy kernel straight to
+# their expert-major position on the owner of their expert, and the forward / dX GEMMs write
+# each (local expert, source rank) group of results with TMA stores straight into the source
+# rank's memory, at the position the rows had there.  One small count all-gather per routing
+# decision and one fence per phase are the only collectives.
+# ------------------------------------------------------------------------------------------
+@dataclass
+class PeerPlan:
+    """Row bookkeeping of one routing decision, all tensors on the device, no host sync.
+
+    Groups on a rank are ordered (local expert, source rank): g = el * world + s.
+    """
+
+    world: int
+    rank: int
+    e_local: int
+    m_sizes: torch.Tensor          # (E,) int32: this rank's rows per global expert
+    dst_rank: torch.Tensor         # (E,) int64: owner of each global expert
+    send_row: torch.Tensor         # (E,) int64: first row, in the owner's receive buffer, of my rows of expert e
+    group_sizes: torch.Tensor      # (G,) int32: rows of each (local expert, source) group received here
+    weight_index: torch.Tensor     # (G,) int32: local expert of each group
+    group_src: torch.Tensor        # (G,) int64: source rank of each group
+    return_row: torch.Tensor       # (G,) int64: first row of the group in its source rank's sorted order
+    local_m_sizes: torch.Tensor    # (E_local,) int32: rows per local expert after dispatch
+    recv_rows: torch.Tensor        # () int64: rows this rank receives in total
+
+    @staticmethod
+    def build(m_sizes: torch.Tensor, world: int, rank: int, group=None) -> "PeerPlan":
+        E = m_sizes.numel()
+        assert E % world == 0, "experts must divide evenly over the ranks"
+        e_local = E // world
+        mine = m_sizes.to(torch.int32).contiguous()
+        counts = torch.empty(world * E, dtype=torch.int32, device=mine.device)
+        dist.all_gather_into_tensor(counts, mine, group=group)
+        return PeerPlan.from_counts(counts.view(world, E), world, rank)
+
+    @staticmethod
+    def from_counts(counts: torch.Tensor, world: int, rank: int) -> "PeerPlan":
+        """counts (world, E): rows of every rank per global expert."""
+        E = counts.shape[1]
+        e_local = E // world
+        dev = counts.device
+        c = counts.view(world, world, e_local).long()              # [source, owner, local expert]
+        per_owner = c.permute(1, 2, 0).contiguous()                # [owner, local expert, source]
+        flat = per_owner.view(world, e_local * world)
+        first = flat.cumsum(dim=1) - flat                          # exclusive: first row of each group on its owner
+        send_row = first.view(world, e_local, world)[:, :, rank].reshape(E)
+        begins = counts.long().cumsum(dim=1) - counts.long()       # [source, global expert]: first row in the source's order
+        mine = per_owner[rank]                                     # [local expert, source]
+        return_row = begins[:, rank * e_local:(rank + 1) * e_local].t().contiguous().view(-1)
+        g = torch.arange(e_local * world, device=dev)
+        return PeerPlan(
+            world=world, rank=rank, e_local=e_local, m_sizes=counts[rank].contiguous(),
+            dst_rank=torch.arange(E, device=dev) // e_local, send_row=send_row.contiguous(),
+            group_sizes=mine.reshape(-1).to(torch.int32).contiguous(), weight_index=(g // world).to(torch.int32),
+            group_src=g % world, return_row=return_row,
+            local_m_sizes=mine.sum(dim=1).to(torch.int32).contiguous(), recv_rows=mine.sum())
+
+
+class PeerChannel:
+    """A (capacity, width) buffer on every rank that every rank can address."""
+
+    def __init__(self, capacity_rows: int, width: int, dtype: torch.dtype, device, group=None):
+        import os
+
+        # this module never uses multicast addresses: keep the allocation off NVLink multicast objects
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group if group is not None else dist.group.WORLD
+        self.local = symm_mem.empty((capacity_rows, width), dtype=dtype, device=device)
+        handle = symm_mem.rendezvous(self.local, group)
+        self.handle = handle
+        self.capacity_rows = capacity_rows
+        self.row_bytes = width * self.local.element_size()
+        self.ptrs = torch.tensor([int(p) for p in handle.buffer_ptrs], dtype=torch.int64, device=device)
+        assert int(self.ptrs[dist.get_rank(group)]) == self.local.data_ptr()
+
+
+def peer_fence(token: torch.Tensor, group=None) -> None:
+    """Orders this rank's earlier work on the current stream (peer stores included) before every
+    rank's later work on theirs: a one-element all-reduce."""
+    dist.all_reduce(token, group=group)
+
+
+def push_rows(rows: torch.Tensor, m_sizes: torch.Tensor, dst_ptrs: torch.Tensor,
+              dst_limit: Optional[torch.Tensor] = None, max_ctas: int = 0) -> None:
+    """rows (M, W) sorted by expert, m_sizes (E,): row i of expert e is copied to the address
+    dst_ptrs[e] + i * row_bytes (int64 device tensor of addresses, local or peer memory); rows
+    with i >= dst_limit[e] are dropped."""
+    from . import _lib
+
+    assert rows.is_cuda and rows.is_contiguous() and rows.dim() == 2
+    assert dst_ptrs.dtype == torch.int64 and dst_ptrs.is_contiguous() and dst_ptrs.numel() == m_sizes.numel()
+    m_sizes = _lib.as_index_tensor(m_sizes).contiguous()
+    if dst_limit is not None:
+        assert dst_limit.dtype == torch.int32 and dst_limit.is_contiguous() and dst_limit.numel() == m_sizes.numel()
+    _lib.check(_lib.load().moe_ep_push_rows(
+        _lib.ptr(rows), rows.shape[0], rows.shape[1] * rows.element_size(), _lib.ptr(m_sizes), _lib.int_code(m_sizes.dtype),
+        m_sizes.numel(), _lib.ptr(dst_ptrs), _lib.ptr(dst_limit), max_ctas, _lib.stream_ptr(rows.device)), "moe_ep_push_rows")
+
+
+def scattered_grouped_gemm(x: torch.Tensor, weight: torch.Tensor, group_sizes: torch.Tensor,
+                           weight_index: Optional[torch.Tensor], out_ptrs: torch.Tensor, out_template: torch.Tensor,
+                           transposed: bool = False) -> None:
+    """Forward (weight (E_w, N, K)) or dX (`transposed`: weight (E_w, K, N)) over G groups of the
+    rows of x; group g uses weight slice weight_index[g] and its results start at the address
+    out_ptrs[g] (int64 device tensor, local or peer memory) with row pitch N."""
+    from . import _lib
+
+    assert x.is_cuda and x.is_contiguous() and weight.is_contiguous() and x.dim() == 2 and weight.dim() == 3
+    M, K = x.shape
+    e_w, N, kw = weight.shape if not transposed else (weight.shape[0], weight.shape[2], weight.shape[1])
+    assert kw == K and weight.dtype == x.dtype
+    G = group_sizes.numel()
+    group_sizes = _lib.as_index_tensor(group_sizes).contiguous()
+    assert out_ptrs.dtype == torch.int64 and out_ptrs.is_contiguous() and out_ptrs.numel() == G
+    if weight_index is not None:
+        assert weight_index.dtype == torch.int32 and weight_index.is_contiguous() and weight_index.numel() == G
+    lib = _lib.load()
+    ws_bytes = lib.moe_grouped_gemm_workspace_bytes(0, M, N, K, G)
+    ws = torch.empty(ws_bytes + 128, dtype=torch.uint8, device=x.device)
+    ws_ptr = (ws.data_ptr() + 127) & ~127
+    name = "moe_grouped_gemm_dx_scattered" if transposed else "moe_grouped_gemm_fwd_scattered"
+    dt = _lib.float_code(x.dtype)
+    _lib.check(getattr(lib, name)(
+        _lib.ptr(x), _lib.ptr(weight), _lib.ptr(group_sizes), _lib.int_code(group_sizes.dtype), _lib.ptr(weight_index), e_w,
+        _lib.ptr(out_ptrs), _lib.ptr(out_template), M, N, K, G, dt, dt, ws_ptr, ws_bytes, _lib.stream_ptr(x.device)), name)
+
+
+def peer_push(plan: PeerPlan, rows: torch.Tensor, channel: PeerChannel, max_ctas: int = 0) -> None:
+    """Rows sorted by global expert -> expert-major (local expert, source) order in the owners' `channel`."""
+    row_bytes = rows.shape[1] * rows.element_size()
+    assert row_bytes == channel.row_bytes
+    dst = (channel.ptrs[plan.dst_rank] + plan.send_row * row_bytes).contiguous()
+    # rows that would not fit into the owner's buffer are dropped, never written past its end
+    limit = (channel.capacity_rows - plan.send_row).clamp(min=0, max=2**31 - 1).to(torch.int32).contiguous()
+    push_rows(rows, plan.m_sizes, dst, limit, max_ctas)
+
+
+def peer_grouped_gemm(plan: PeerPlan, rows_in: PeerChannel, weight: torch.Tensor, rows_out: PeerChannel,
+                      transposed: bool = False) -> None:
+    """Forward or dX over the rows received in `rows_in`; each (local expert, source) group's
+    results are stored into the source rank's `rows_out` at the rows' position in that rank's order."""
+    assert weight.shape[0] == plan.e_local
+    out_ptrs = (rows_out.ptrs[plan.group_src] + plan.return_row * rows_out.row_bytes).contiguous()
+    scattered_grouped_gemm(rows_in.local, weight, plan.group_sizes, plan.weight_index, out_ptrs, rows_out.local, transposed)
