@@ -357,6 +357,7 @@ def main():
 
     import __graft_entry__ as entry
 
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # peer buffers are addressed directly, never through multicast
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -589,12 +590,35 @@ def main():
         e2e_ms = e0.elapsed_time(e1) / args.steps
     clocks = sampler.stop() if rank == 0 else None
 
+    # ---- the row exchange alone (N > 1): one dispatch of x, timed on the device ----
+    xchg_ms, remote_bytes = float("nan"), 0
+    if world > 1:
+        own = int(m_sizes.view(world, E_local)[rank].sum())
+        remote_bytes = (M - own) * K * 2
+        if peer is not None:
+            def exchange():
+                peer_push(peer["plan"], x_d, peer["x"])
+                peer_fence(peer["token"])
+        else:
+            def exchange():
+                plan.dispatch(x_d)
+        for _ in range(3):
+            exchange()
+        barrier()
+        x0, x1 = ev(), ev()
+        x0.record()
+        for _ in range(10):
+            exchange()
+        x1.record()
+        barrier()
+        xchg_ms = x0.elapsed_time(x1) / 10
+
     # max over ranks
     times = torch.tensor([resident_ms, e2e_ms, float(np.mean(kernel_ms["fwd"])), float(np.mean(kernel_ms["dx"])),
-                          float(np.mean(kernel_ms["dw"]))], device=dev, dtype=torch.float64)
+                          float(np.mean(kernel_ms["dw"])), xchg_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    resident_ms, e2e_ms, fwd_ms, dx_ms, dw_ms = times.tolist()
+    resident_ms, e2e_ms, fwd_ms, dx_ms, dw_ms, xchg_ms = times.tolist()
     err_flag = _lib.read_error_flag()
 
     if rank == 0:
@@ -632,6 +656,10 @@ def main():
             "tokens_per_s": T * world / (resident_ms * 1e-3),
             "clocks": clocks, "kernel_wait_errors": err_flag,
         }
+        if world > 1:
+            line["exchange"] = {"what": "dispatch of x alone (rows to their experts' ranks), rank 0's remote bytes",
+                                "transport": args.ep_transport, "ms": xchg_ms, "remote_bytes": remote_bytes,
+                                "gbs_out": remote_bytes / (xchg_ms * 1e-3) / 1e9, "nvlink_peak_gbs_per_direction": 900.0}
         if world == 1 and not args.no_cpu_baseline:
             tf, dt, cores = cpu_reference_arm(cfg, 1, 0, args.cpu_rows)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",

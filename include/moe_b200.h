@@ -184,10 +184,12 @@ int moe_combine(const void* y, const int32_t* inv_sort_idx, const void* weights,
  * with i >= dst_limit[e] are dropped (dst_limit may be NULL).  dst_ptrs is a DEVICE array
  * of E 64-bit addresses, 16-byte aligned, in this GPU's memory or in a peer GPU's memory
  * mapped into this process; the stores are plain global stores.  The call neither waits
- * for nor signals the receiver.  max_ctas <= 0 picks a grid from the SM count. */
+ * for nor signals the receiver.  Rows are visited starting with expert first_expert and
+ * wrapping around (ranks that start at different experts do not all write to the same
+ * destination at once).  max_ctas <= 0 picks a grid from the SM count. */
 int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, const void* m_sizes,
                      int m_sizes_dtype, int E, const uint64_t* dst_ptrs,
-                     const int32_t* dst_limit, int max_ctas, void* stream);
+                     const int32_t* dst_limit, int first_expert, int max_ctas, void* stream);
 
 /* moe_grouped_gemm_fwd / moe_grouped_gemm_dx over G groups where group g multiplies by
  * weight slice weight_index[g] (NULL: slice g) of n_weights, and its output rows are

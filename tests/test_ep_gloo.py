@@ -107,7 +107,7 @@ def _peer_worker(rank, world, port, E, rows_per_rank, H, out_dir):
 @pytest.mark.parametrize("world", [2, 4])
 def test_peer_plan_addresses(tmp_path, world):
     """The peer-memory plan: replaying every rank's pushes on the host fills each owner's buffer
-    in (local expert, source) order, and replaying the scattered GEMM outputs puts every row back
+    in (local expert, source rotated to start after the owner) order, and replaying the scattered GEMM outputs puts every row back
     at its position on its source rank."""
     E, rows, H = 8, 300, 5
     mp.spawn(_peer_worker, args=(world, _free_port(), E, rows, H, str(tmp_path)), nprocs=world, join=True)
@@ -127,7 +127,8 @@ def test_peer_plan_addresses(tmp_path, world):
         p = saved[r]["plan"]
         chunks = []
         for e in range(r * e_local, (r + 1) * e_local):
-            for src in range(world):
+            for j in range(world):
+                src = (r + 1 + j) % world
                 chunks.append(saved[src]["xs"][saved[src]["ids_sorted"] == e])
         expect = torch.cat(chunks)
         assert int(p["recv_rows"]) == expect.shape[0]

@@ -37,7 +37,8 @@ def test_push_rows(dev, E, M, W):
         slot[int(e)] = (b, fill[b])
         ptrs[e] = bufs[b].data_ptr() + fill[b] * W * 2
         fill[b] += int(limit[e])
-    push_rows(rows, torch.from_numpy(m).to(dev), torch.from_numpy(ptrs).to(dev), torch.from_numpy(limit.astype(np.int32)).to(dev))
+    push_rows(rows, torch.from_numpy(m).to(dev), torch.from_numpy(ptrs).to(dev), torch.from_numpy(limit.astype(np.int32)).to(dev),
+              first_expert=(E * 2) // 3)
     torch.cuda.synchronize()
     begins = np.concatenate([[0], np.cumsum(m)])
     for e in range(E):

@@ -40,13 +40,17 @@ __device__ __forceinline__ void push_build_begins(const void* m_sizes, int ms64,
 template <int UNROLL>
 __global__ void __launch_bounds__(PUSH_THREADS)
 ep_push_rows_kernel(const uint4* __restrict__ rows, int64_t M, int row_vecs, const void* __restrict__ m_sizes, int ms64,
-                    int E, const uint64_t* __restrict__ dst_ptrs, const int32_t* __restrict__ dst_limit) {
+                    int E, const uint64_t* __restrict__ dst_ptrs, const int32_t* __restrict__ dst_limit, int first_expert) {
   __shared__ int begins[PUSH_MAX_E + 1];
   push_build_begins(m_sizes, ms64, E, begins);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps = PUSH_THREADS / 32;
   const int64_t total = min(M, (int64_t)begins[E]);
-  for (int64_t r = (int64_t)blockIdx.x * warps + warp; r < total; r += (int64_t)gridDim.x * warps) {
+  // rows are visited starting at `first_expert` (wrapping around): ranks that start at different
+  // experts write to different destinations at any one time instead of all to the same one
+  const int64_t start = min((int64_t)begins[first_expert], total);
+  for (int64_t i = (int64_t)blockIdx.x * warps + warp; i < total; i += (int64_t)gridDim.x * warps) {
+    const int64_t r = i + start < total ? i + start : i + start - total;
     // expert of row r: last e with begins[e] <= r
     int lo = 0, hi = E;
     while (hi - lo > 1) {
@@ -79,10 +83,12 @@ ep_push_rows_kernel(const uint4* __restrict__ rows, int64_t M, int row_vecs, con
 using namespace moe;
 
 MOE_API int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, const void* m_sizes, int m_sizes_dtype,
-                             int E, const uint64_t* dst_ptrs, const int32_t* dst_limit, int max_ctas, void* stream_) {
+                             int E, const uint64_t* dst_ptrs, const int32_t* dst_limit, int first_expert,
+                             int max_ctas, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (!is_int_dtype(m_sizes_dtype)) return MOE_ERR_DTYPE;
   if (M < 0 || row_bytes < 0 || E <= 0 || E > PUSH_MAX_E || M > 0x7fffffffLL) return MOE_ERR_SHAPE;
+  if (first_expert < 0 || first_expert >= E) return MOE_ERR_SHAPE;
   if (M == 0 || row_bytes == 0) return MOE_OK;
   if (!rows || !m_sizes || !dst_ptrs) return MOE_ERR_NULL;
   if ((row_bytes & 15) || ((uintptr_t)rows & 15)) return MOE_ERR_ALIGN;
@@ -91,6 +97,6 @@ MOE_API int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, con
   const int64_t cap = max_ctas > 0 ? max_ctas : (int64_t)sm_count() * 4;
   if (grid > cap) grid = cap;
   ep_push_rows_kernel<8><<<(int)grid, PUSH_THREADS, 0, stream>>>(
-      reinterpret_cast<const uint4*>(rows), M, (int)(row_bytes / 16), m_sizes, m_sizes_dtype == MOE_I64, E, dst_ptrs, dst_limit);
+      reinterpret_cast<const uint4*>(rows), M, (int)(row_bytes / 16), m_sizes, m_sizes_dtype == MOE_I64, E, dst_ptrs, dst_limit, first_expert);
   return launch_status();
 }

@@ -109,7 +109,8 @@ class ExpertParallelPlan:
 class PeerPlan:
     """Row bookkeeping of one routing decision, all tensors on the device, no host sync.
 
-    Groups on a rank are ordered (local expert, source rank): g = el * world + s.
+    Groups on rank d are ordered (local expert, slot): g = el * world + j, holding the rows of
+    source rank (d + 1 + j) % world.
     """
 
     world: int
@@ -142,19 +143,28 @@ class PeerPlan:
         e_local = E // world
         dev = counts.device
         c = counts.view(world, world, e_local).long()              # [source, owner, local expert]
-        per_owner = c.permute(1, 2, 0).contiguous()                # [owner, local expert, source]
+        # On owner d the sources of an expert are laid out d+1, d+2, ..., d (mod world): when every
+        # rank walks its groups in order, the ranks' result stores go to distinct ranks at any one time.
+        owners = torch.arange(world, device=dev)
+        src_of = (owners.view(world, 1) + 1 + torch.arange(world, device=dev).view(1, world)) % world   # [owner, slot] -> source
+        per_owner = c.permute(1, 2, 0)                             # [owner, local expert, source]
+        per_owner = torch.gather(per_owner, 2, src_of.view(world, 1, world).expand(world, e_local, world)).contiguous()  # [owner, el, slot]
         flat = per_owner.view(world, e_local * world)
         first = flat.cumsum(dim=1) - flat                          # exclusive: first row of each group on its owner
-        send_row = first.view(world, e_local, world)[:, :, rank].reshape(E)
+        my_slot = (rank - owners - 1) % world                      # slot of this rank's rows on each owner
+        send_row = torch.gather(first.view(world, e_local, world), 2,
+                                my_slot.view(world, 1, 1).expand(world, e_local, 1)).reshape(E)
         begins = counts.long().cumsum(dim=1) - counts.long()       # [source, global expert]: first row in the source's order
-        mine = per_owner[rank]                                     # [local expert, source]
-        return_row = begins[:, rank * e_local:(rank + 1) * e_local].t().contiguous().view(-1)
+        mine = per_owner[rank]                                     # [local expert, slot]
         g = torch.arange(e_local * world, device=dev)
+        group_src = (rank + 1 + g % world) % world
+        group_expert = rank * e_local + g // world
+        return_row = begins[group_src, group_expert]
         return PeerPlan(
             world=world, rank=rank, e_local=e_local, m_sizes=counts[rank].contiguous(),
             dst_rank=torch.arange(E, device=dev) // e_local, send_row=send_row.contiguous(),
             group_sizes=mine.reshape(-1).to(torch.int32).contiguous(), weight_index=(g // world).to(torch.int32),
-            group_src=g % world, return_row=return_row,
+            group_src=group_src, return_row=return_row.contiguous(),
             local_m_sizes=mine.sum(dim=1).to(torch.int32).contiguous(), recv_rows=mine.sum())
 
 
@@ -185,10 +195,10 @@ def peer_fence(token: torch.Tensor, group=None) -> None:
 
 
 def push_rows(rows: torch.Tensor, m_sizes: torch.Tensor, dst_ptrs: torch.Tensor,
-              dst_limit: Optional[torch.Tensor] = None, max_ctas: int = 0) -> None:
+              dst_limit: Optional[torch.Tensor] = None, max_ctas: int = 0, first_expert: int = 0) -> None:
     """rows (M, W) sorted by expert, m_sizes (E,): row i of expert e is copied to the address
     dst_ptrs[e] + i * row_bytes (int64 device tensor of addresses, local or peer memory); rows
-    with i >= dst_limit[e] are dropped."""
+    with i >= dst_limit[e] are dropped.  The copy starts with the rows of `first_expert`."""
     from . import _lib
 
     assert rows.is_cuda and rows.is_contiguous() and rows.dim() == 2
@@ -198,7 +208,8 @@ def push_rows(rows: torch.Tensor, m_sizes: torch.Tensor, dst_ptrs: torch.Tensor,
         assert dst_limit.dtype == torch.int32 and dst_limit.is_contiguous() and dst_limit.numel() == m_sizes.numel()
     _lib.check(_lib.load().moe_ep_push_rows(
         _lib.ptr(rows), rows.shape[0], rows.shape[1] * rows.element_size(), _lib.ptr(m_sizes), _lib.int_code(m_sizes.dtype),
-        m_sizes.numel(), _lib.ptr(dst_ptrs), _lib.ptr(dst_limit), max_ctas, _lib.stream_ptr(rows.device)), "moe_ep_push_rows")
+        m_sizes.numel(), _lib.ptr(dst_ptrs), _lib.ptr(dst_limit), first_expert, max_ctas, _lib.stream_ptr(rows.device)),
+        "moe_ep_push_rows")
 
 
 def scattered_grouped_gemm(x: torch.Tensor, weight: torch.Tensor, group_sizes: torch.Tensor,
@@ -236,7 +247,9 @@ def peer_push(plan: PeerPlan, rows: torch.Tensor, channel: PeerChannel, max_ctas
     dst = (channel.ptrs[plan.dst_rank] + plan.send_row * row_bytes).contiguous()
     # rows that would not fit into the owner's buffer are dropped, never written past its end
     limit = (channel.capacity_rows - plan.send_row).clamp(min=0, max=2**31 - 1).to(torch.int32).contiguous()
-    push_rows(rows, plan.m_sizes, dst, limit, max_ctas)
+    # every rank starts with the rows of the next rank's experts, so the ranks' writes fan out
+    # over distinct destinations instead of converging on one receiver at a time
+    push_rows(rows, plan.m_sizes, dst, limit, max_ctas, first_expert=((plan.rank + 1) % plan.world) * plan.e_local)
 
 
 def peer_grouped_gemm(plan: PeerPlan, rows_in: PeerChannel, weight: torch.Tensor, rows_out: PeerChannel,
