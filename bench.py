@@ -171,16 +171,25 @@ def config_dict(args, cfg):
                 if args.ep_transport == "peer" else f"expert parallel ep{args.gpus} (NCCL all-to-all dispatch/combine)")}
 
 
+_TIME_OVERRIDE = {}  # {"iters": n, "warmup": m} for profiling runs (few launches per kernel)
+
+
 def time_cuda(fn, iters: int = 20, warmup: int = 3, flush=None) -> float:
     """Median device time of fn() in ms (CUDA events around every call; an optional buffer larger
-    than L2 is rewritten between calls so that small inputs are not served from cache)."""
+    than L2 is rewritten between calls so that small inputs are not served from cache).  Some
+    device work is always queued ahead of the first event (the flush, else a short spin), so the
+    host's launch latency of fn() is not counted as kernel time."""
+    iters = _TIME_OVERRIDE.get("iters", iters)
+    warmup = _TIME_OVERRIDE.get("warmup", warmup)
     for _ in range(warmup):
         fn()
     times = []
     for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         if flush is not None:
             flush.add_(1)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        else:
+            torch.cuda._sleep(200_000)  # ~0.1 ms of device time for the host to get ahead
         a.record()
         fn()
         b.record()
@@ -212,6 +221,8 @@ def run_kernel_suite(args):
     bf = torch.bfloat16
     flush = torch.zeros(64 * 1024 * 1024, device=dev, dtype=torch.float32)  # 256 MB
     torch.manual_seed(0)
+    if args.kernel_iters:
+        _TIME_OVERRIDE.update(iters=args.kernel_iters, warmup=1)
 
     def emit(name, ms, nbytes=None, flops=None, **extra):
         line = {"suite": "kernels", "kernel": name, "ms": ms}
@@ -262,6 +273,9 @@ def run_kernel_suite(args):
     del wfull
     nel = E * N * K
     emit("nf4_dequant 128x1536x2048 -> bf16", time_cuda(lambda: dequantize_4bit(packed, state, bf)), nel // 2 + nel // 64 * 4 + nel * 2)
+    if args.hbm_only:
+        assert _lib.read_error_flag() == 0
+        return
     for tokens in (512, 4096, 32768):
         M = tokens * 8
         x = torch.randn(M, K, device=dev, dtype=bf)
@@ -334,6 +348,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--suite", default="hotpath", choices=["hotpath", "kernels"],
                     help="hotpath: the contract line (default); kernels: roofline lines of the surrounding kernels")
+    ap.add_argument("--hbm-only", action="store_true", help="kernel suite: only the HBM-bound kernels (profiling runs)")
+    ap.add_argument("--kernel-iters", type=int, default=None, help="kernel suite: timed launches per kernel (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (reduced profiling case)")
     ap.add_argument("--experts", type=int, default=None, help="override the expert count (reduced profiling case)")

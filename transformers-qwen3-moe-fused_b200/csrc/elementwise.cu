@@ -31,7 +31,13 @@ __device__ __forceinline__ void store_vec(T* p, const Vec<T>& r) {
   *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(r.v);
 }
 
-__device__ __forceinline__ float sigmoid_f32(float x) { return 1.f / (1.f + __expf(-x)); }
+// Sigmoid in fp32.  fp32 tensors take the IEEE division; 16-bit tensors take the hardware
+// reciprocal (1 ulp in fp32, far below the storage rounding), which keeps the 16-bit kernels
+// bound by memory rather than by instruction issue.
+template <typename T>
+__device__ __forceinline__ float sigmoid_for(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+template <>
+__device__ __forceinline__ float sigmoid_for<float>(float x) { return 1.f / (1.f + __expf(-x)); }
 
 // Rounding points follow qwen3_moe_fused/kernels/silu_mul.py:34-39 (forward) and
 // :66-73 / :101-111 (backward): f = T(e*sigmoid(e)) with e in fp32; h = f*g, df = dh*g,
@@ -42,20 +48,85 @@ __device__ __forceinline__ T mul_t(T a, T b) { return from_f32<T>(to_f32(a) * to
 template <typename T>
 __device__ __forceinline__ T silu_fwd_one(T e, T g) {
   const float e32 = to_f32(e);
-  const T f = from_f32<T>(e32 * sigmoid_f32(e32));
+  const T f = from_f32<T>(e32 * sigmoid_for<T>(e32));
   return mul_t(f, g);
 }
 
 template <typename T>
 __device__ __forceinline__ void silu_bwd_one(T dh, T e, T g, T& h, T& de, T& dg) {
   const float e32 = to_f32(e);
-  const float se = sigmoid_f32(e32);
+  const float se = sigmoid_for<T>(e32);
   const float ese = e32 * se;
   const T f = from_f32<T>(ese);
   h = mul_t(f, g);
   const T df = mul_t(dh, g);
   dg = mul_t(f, dh);
   de = from_f32<T>(to_f32(df) * se * (1.f + e32 - ese));
+}
+
+// Packed forms for the 16-bit types: two elements per conversion and per multiply.  A packed
+// 16-bit multiply rounds the exact product once, which is what mul_t computes.
+template <typename T> struct Packed;
+template <> struct Packed<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+  static __device__ __forceinline__ float2 unpack(type v) { return __bfloat1622float2(v); }
+  static __device__ __forceinline__ type pack(float a, float b) { return __floats2bfloat162_rn(a, b); }
+};
+template <> struct Packed<__half> {
+  using type = __half2;
+  static __device__ __forceinline__ float2 unpack(type v) { return __half22float2(v); }
+  static __device__ __forceinline__ type pack(float a, float b) { return __floats2half2_rn(a, b); }
+};
+
+template <typename T>
+__device__ __forceinline__ Vec<T> silu_fwd_vec(const Vec<T>& ve, const Vec<T>& vg) {
+  Vec<T> vh;
+  if constexpr (sizeof(T) == 2) {
+    using P = Packed<T>;
+    using P2 = typename P::type;
+    const P2* e2 = reinterpret_cast<const P2*>(ve.v);
+    const P2* g2 = reinterpret_cast<const P2*>(vg.v);
+    P2* h2 = reinterpret_cast<P2*>(vh.v);
+#pragma unroll
+    for (int j = 0; j < Vec<T>::N / 2; ++j) {
+      const float2 e = P::unpack(e2[j]);
+      const P2 f = P::pack(e.x * sigmoid_for<T>(e.x), e.y * sigmoid_for<T>(e.y));
+      h2[j] = __hmul2(f, g2[j]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < Vec<T>::N; ++j) vh.v[j] = silu_fwd_one(ve.v[j], vg.v[j]);
+  }
+  return vh;
+}
+
+template <typename T>
+__device__ __forceinline__ void silu_bwd_vec(const Vec<T>& vdh, const Vec<T>& ve, const Vec<T>& vg,
+                                             Vec<T>& vh, Vec<T>& vde, Vec<T>& vdg) {
+  if constexpr (sizeof(T) == 2) {
+    using P = Packed<T>;
+    using P2 = typename P::type;
+    const P2* dh2 = reinterpret_cast<const P2*>(vdh.v);
+    const P2* e2 = reinterpret_cast<const P2*>(ve.v);
+    const P2* g2 = reinterpret_cast<const P2*>(vg.v);
+    P2* h2 = reinterpret_cast<P2*>(vh.v);
+    P2* de2 = reinterpret_cast<P2*>(vde.v);
+    P2* dg2 = reinterpret_cast<P2*>(vdg.v);
+#pragma unroll
+    for (int j = 0; j < Vec<T>::N / 2; ++j) {
+      const float2 e = P::unpack(e2[j]);
+      const float s0 = sigmoid_for<T>(e.x), s1 = sigmoid_for<T>(e.y);
+      const float es0 = e.x * s0, es1 = e.y * s1;
+      const P2 f = P::pack(es0, es1);
+      h2[j] = __hmul2(f, g2[j]);
+      const float2 df = P::unpack(__hmul2(dh2[j], g2[j]));
+      dg2[j] = __hmul2(f, dh2[j]);
+      de2[j] = P::pack(df.x * s0 * (1.f + e.x - es0), df.y * s1 * (1.f + e.y - es1));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < Vec<T>::N; ++j) silu_bwd_one(vdh.v[j], ve.v[j], vg.v[j], vh.v[j], vde.v[j], vdg.v[j]);
+  }
 }
 
 template <typename T, bool VEC>
@@ -71,20 +142,13 @@ silu_fwd_kernel(const T* __restrict__ e, const T* __restrict__ g, T* __restrict_
       const int64_t i2 = i + stride;
       const Vec<T> ve = load_vec(e + i * V), vg = load_vec(g + i * V);
       const Vec<T> ve2 = load_vec(e + i2 * V), vg2 = load_vec(g + i2 * V);
-      Vec<T> vh, vh2;
-#pragma unroll
-      for (int j = 0; j < V; ++j) { vh.v[j] = silu_fwd_one(ve.v[j], vg.v[j]); vh2.v[j] = silu_fwd_one(ve2.v[j], vg2.v[j]); }
-      store_vec(h + i * V, vh);
-      store_vec(h + i2 * V, vh2);
+      store_vec(h + i * V, silu_fwd_vec(ve, vg));
+      store_vec(h + i2 * V, silu_fwd_vec(ve2, vg2));
     }
   }
   for (; i < nv; i += stride) {
     if constexpr (VEC) {
-      const Vec<T> ve = load_vec(e + i * V), vg = load_vec(g + i * V);
-      Vec<T> vh;
-#pragma unroll
-      for (int j = 0; j < V; ++j) vh.v[j] = silu_fwd_one(ve.v[j], vg.v[j]);
-      store_vec(h + i * V, vh);
+      store_vec(h + i * V, silu_fwd_vec(load_vec(e + i * V), load_vec(g + i * V)));
     } else {
       h[i] = silu_fwd_one(e[i], g[i]);
     }
@@ -105,8 +169,7 @@ silu_bwd_kernel(const T* dh, const T* e, const T* g, T* h, T* de, T* dg, int64_t
     if constexpr (VEC) {
       const Vec<T> vdh = load_vec(dh + i * V), ve = load_vec(e + i * V), vg = load_vec(g + i * V);
       Vec<T> vh, vde, vdg;
-#pragma unroll
-      for (int j = 0; j < V; ++j) silu_bwd_one(vdh.v[j], ve.v[j], vg.v[j], vh.v[j], vde.v[j], vdg.v[j]);
+      silu_bwd_vec(vdh, ve, vg, vh, vde, vdg);
       if constexpr (WRITE_H) store_vec(h + i * V, vh);
       store_vec(de + i * V, vde);
       store_vec(dg + i * V, vdg);
@@ -130,7 +193,8 @@ silu_bwd_kernel(const T* dh, const T* e, const T* g, T* h, T* de, T* dg, int64_t
   }
 }
 
-// NF4 decode, 16 weights (8 packed bytes) per thread iteration.
+// NF4 decode, 8 weights (4 packed bytes) per thread iteration: a warp reads 128 contiguous
+// bytes and, for 16-bit outputs, writes 512 contiguous bytes per store instruction.
 // Element 2j is the high nibble of byte j, element 2j+1 the low nibble
 // (qwen3_moe_fused/grouped_gemm/forward_4bit.py:99-104).
 template <typename T>
@@ -141,27 +205,29 @@ nf4_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__
   __shared__ float tbl[16];
   if (threadIdx.x < 16) tbl[threadIdx.x] = code[threadIdx.x];
   __syncthreads();
-  const int64_t ngroups = vec_ok ? n_elems / 16 : 0;
+  const int64_t ngroups = vec_ok ? n_elems / 8 : 0;
+  const bool one_scale = bs_shift >= 3;  // the 8 elements of a group share one absmax block
+#pragma unroll 2
   for (int64_t gi = (int64_t)blockIdx.x * EW_THREADS + threadIdx.x; gi < ngroups; gi += (int64_t)gridDim.x * EW_THREADS) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(packed + gi * 8);
-    const int64_t base = gi * 16;
-    const uint32_t words[2] = {raw.x, raw.y};
-    T vals[16];
+    const uint32_t raw = __ldg(reinterpret_cast<const uint32_t*>(packed) + gi);
+    const int64_t base = gi * 8;
+    const float a_all = __ldg(absmax + (base >> bs_shift));
+    T vals[8];
 #pragma unroll
-    for (int b = 0; b < 8; ++b) {
-      const uint32_t byte = (words[b >> 2] >> ((b & 3) * 8)) & 0xffu;
-      const float a0 = absmax[(base + 2 * b) >> bs_shift];
-      const float a1 = absmax[(base + 2 * b + 1) >> bs_shift];
+    for (int b = 0; b < 4; ++b) {
+      const uint32_t byte = (raw >> (b * 8)) & 0xffu;
+      const float a0 = one_scale ? a_all : absmax[(base + 2 * b) >> bs_shift];
+      const float a1 = one_scale ? a_all : absmax[(base + 2 * b + 1) >> bs_shift];
       vals[2 * b] = from_f32<T>(tbl[byte >> 4] * a0);
       vals[2 * b + 1] = from_f32<T>(tbl[byte & 15] * a1);
     }
-    constexpr int NV = 16 * sizeof(T) / 16;
+    constexpr int NV = 8 * sizeof(T) / 16;
 #pragma unroll
     for (int v = 0; v < NV; ++v)
-      reinterpret_cast<uint4*>(out + base)[v] = reinterpret_cast<const uint4*>(vals)[v];
+      __stcs(reinterpret_cast<uint4*>(out + base) + v, reinterpret_cast<const uint4*>(vals)[v]);
   }
   // scalar remainder (or everything when the buffers are not 16-byte aligned)
-  const int64_t start = ngroups * 16;
+  const int64_t start = ngroups * 8;
   for (int64_t i = start + (int64_t)blockIdx.x * EW_THREADS + threadIdx.x; i < n_elems; i += (int64_t)gridDim.x * EW_THREADS) {
     const uint8_t byte = packed[i >> 1];
     const int nib = (i & 1) ? (byte & 15) : (byte >> 4);
@@ -169,42 +235,83 @@ nf4_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__
   }
 }
 
-// out[j,:] = hidden[sort_idx[j] / k, :].  One CTA walks whole rows, two at a time so that
-// two rows' worth of loads are in flight.
+// out[j,:] = hidden[sort_idx[j] / k, :].  Vector form: one warp per output row, up to eight
+// 16-byte loads in flight per lane, and the index of the warp's next row is fetched before the
+// current row is copied (the index -> row -> store chain is what bounds this kernel otherwise).
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(EW_THREADS)
 gather_rows_kernel(const T* __restrict__ hidden, const int32_t* __restrict__ sort_idx, int k,
                    T* __restrict__ out, int64_t rows, int H) {
-  constexpr int V = VEC ? Vec<T>::N : 1;
-  const int hv = H / V;
-  for (int64_t j = 2 * (int64_t)blockIdx.x; j < rows; j += 2 * (int64_t)gridDim.x) {
-    const bool two = j + 1 < rows;
-    const T* s0 = hidden + (int64_t)(sort_idx[j] / k) * H;
-    const T* s1 = hidden + (int64_t)(sort_idx[two ? j + 1 : j] / k) * H;
-    T* d0 = out + j * H;
-    T* d1 = d0 + H;
-    for (int c = threadIdx.x; c < hv; c += EW_THREADS) {
-      if constexpr (VEC) {
-        const Vec<T> a = load_vec(s0 + c * V), b = load_vec(s1 + c * V);
-        store_vec(d0 + c * V, a);
-        if (two) store_vec(d1 + c * V, b);
-      } else {
-        const T a = s0[c], b = s1[c];
-        d0[c] = a;
-        if (two) d1[c] = b;
+  if constexpr (VEC) {
+    constexpr int UNROLL = 8;
+    const int row_vecs = H / Vec<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * (EW_THREADS / 32);
+    int64_t j = (int64_t)blockIdx.x * (EW_THREADS / 32) + (threadIdx.x >> 5);
+    int idx = j < rows ? sort_idx[j] : 0;
+    for (; j < rows; j += warps) {
+      const int64_t jn = j + warps;
+      const int idx_next = jn < rows ? sort_idx[jn] : 0;
+      const uint4* src = reinterpret_cast<const uint4*>(hidden + (int64_t)(idx / k) * H);
+      uint4* dst = reinterpret_cast<uint4*>(out + j * H);
+      for (int c0 = 0; c0 < row_vecs; c0 += 32 * UNROLL) {
+        uint4 v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int c = c0 + u * 32 + lane;
+          if (c < row_vecs) v[u] = __ldg(src + c);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int c = c0 + u * 32 + lane;
+          if (c < row_vecs) __stcs(dst + c, v[u]);  // streaming: keep the re-read token rows in L2, not the output
+        }
       }
+      idx = idx_next;
+    }
+  } else {
+    for (int64_t j = blockIdx.x; j < rows; j += gridDim.x) {
+      const T* src = hidden + (int64_t)(sort_idx[j] / k) * H;
+      T* dst = out + j * H;
+      for (int c = threadIdx.x; c < H; c += EW_THREADS) dst[c] = src[c];
     }
   }
 }
 
 // out[t,:] = T( sum_j f32(weights[t,j]) * f32(y[inv_sort_idx[t*k+j],:]) )
-template <typename T, bool VEC>
+// KFIX > 0 fixes k at compile time so that the k row loads of a thread are all in flight.
+template <typename T, bool VEC, int KFIX>
 __global__ void __launch_bounds__(EW_THREADS)
 combine_kernel(const T* __restrict__ y, const int32_t* __restrict__ inv_sort_idx,
-               const T* __restrict__ weights, T* __restrict__ out, int64_t tokens, int k, int H) {
+               const T* __restrict__ weights, T* __restrict__ out, int64_t tokens, int k_rt, int H) {
   constexpr int V = VEC ? Vec<T>::N : 1;
+  const int k = KFIX > 0 ? KFIX : k_rt;
   const int hv = H / V;
   for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+    if constexpr (KFIX > 0 && VEC) {
+      int64_t src[KFIX];
+      float wj[KFIX];
+#pragma unroll
+      for (int j = 0; j < KFIX; ++j) {
+        src[j] = inv_sort_idx[t * KFIX + j];
+        wj[j] = to_f32(weights[t * KFIX + j]);
+      }
+      for (int c = threadIdx.x; c < hv; c += EW_THREADS) {
+        Vec<T> v[KFIX];
+#pragma unroll
+        for (int j = 0; j < KFIX; ++j) v[j] = load_vec(y + src[j] * H + c * V);
+        Vec<T> o;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          float acc = 0.f;
+#pragma unroll
+          for (int j = 0; j < KFIX; ++j) acc = fmaf(wj[j], to_f32(v[j].v[i]), acc);  // same order as the generic loop
+          o.v[i] = from_f32<T>(acc);
+        }
+        store_vec(out + t * H + c * V, o);
+      }
+      continue;
+    }
     for (int c = threadIdx.x; c < hv; c += EW_THREADS) {
       float acc[V];
 #pragma unroll
@@ -294,9 +401,9 @@ MOE_API int moe_nf4_dequant(const uint8_t* packed, const float* code, const floa
   if (shift < 0 || n_elems < 0 || (n_elems & 1)) return MOE_ERR_SHAPE;
   if (n_elems == 0) return MOE_OK;
   if (!packed || !code || !absmax || !out) return MOE_ERR_NULL;
-  const bool vec_ok = (((uintptr_t)packed & 7) == 0) && aligned16(out);
+  const bool vec_ok = (((uintptr_t)packed & 3) == 0) && aligned16(out);
   MOE_DISPATCH_FLOAT(dtype_out, T, {
-    nf4_dequant_kernel<T><<<ew_grid((n_elems + 15) / 16), EW_THREADS, 0, stream>>>(
+    nf4_dequant_kernel<T><<<ew_grid((n_elems + 7) / 8), EW_THREADS, 0, stream>>>(
         packed, code, absmax, shift, (T*)out, n_elems, vec_ok);
   });
   return launch_status();
@@ -308,11 +415,12 @@ MOE_API int moe_gather_rows(const void* hidden, const int32_t* sort_idx, int k, 
   if (rows < 0 || H < 0 || k <= 0) return MOE_ERR_SHAPE;
   if (rows == 0 || H == 0) return MOE_OK;
   if (!hidden || !sort_idx || !out) return MOE_ERR_NULL;
-  const int64_t pairs = (rows + 1) / 2;
-  const int64_t g64 = pairs < (int64_t)sm_count() * 16 ? pairs : (int64_t)sm_count() * 16;
-  const int grid = (int)g64;
   MOE_DISPATCH_FLOAT(dtype, T, {
     const bool vec = aligned16(hidden) && aligned16(out) && (H % Vec<T>::N == 0);
+    // vector form: a warp per row (8 rows per CTA per pass); scalar form: a CTA per row
+    const int64_t want = vec ? (rows + EW_THREADS / 32 - 1) / (EW_THREADS / 32) : rows;
+    const int64_t cap = (int64_t)sm_count() * (vec ? 8 : 16);
+    const int grid = (int)(want < cap ? want : cap);
     if (vec) gather_rows_kernel<T, true><<<grid, EW_THREADS, 0, stream>>>((const T*)hidden, sort_idx, k, (T*)out, rows, H);
     else gather_rows_kernel<T, false><<<grid, EW_THREADS, 0, stream>>>((const T*)hidden, sort_idx, k, (T*)out, rows, H);
   });
@@ -329,8 +437,9 @@ MOE_API int moe_combine(const void* y, const int32_t* inv_sort_idx, const void* 
   const int grid = (int)g64;
   MOE_DISPATCH_FLOAT(dtype, T, {
     const bool vec = aligned16(y) && aligned16(out) && (H % Vec<T>::N == 0);
-    if (vec) combine_kernel<T, true><<<grid, EW_THREADS, 0, stream>>>((const T*)y, inv_sort_idx, (const T*)weights, (T*)out, T_, k, H);
-    else combine_kernel<T, false><<<grid, EW_THREADS, 0, stream>>>((const T*)y, inv_sort_idx, (const T*)weights, (T*)out, T_, k, H);
+    if (vec && k == 8) combine_kernel<T, true, 8><<<grid, EW_THREADS, 0, stream>>>((const T*)y, inv_sort_idx, (const T*)weights, (T*)out, T_, k, H);
+    else if (vec) combine_kernel<T, true, 0><<<grid, EW_THREADS, 0, stream>>>((const T*)y, inv_sort_idx, (const T*)weights, (T*)out, T_, k, H);
+    else combine_kernel<T, false, 0><<<grid, EW_THREADS, 0, stream>>>((const T*)y, inv_sort_idx, (const T*)weights, (T*)out, T_, k, H);
   });
   return launch_status();
 }

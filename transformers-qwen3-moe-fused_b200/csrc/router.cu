@@ -85,57 +85,106 @@ router_kernel(const TL* __restrict__ logits, int64_t T, int E, int k, int norm,
 // Faster form for k <= 8: eight lanes per token (four tokens per warp), E/8 logits per lane.
 // The winners are chosen on the logits (the same order as on the probabilities, without the
 // rounding of exp in between); only the softmax denominator needs every exponential.
-template <typename TL, typename TW, int NV>
+//
+// Logits are mapped to unsigned keys that sort like the floats, so that a lane's maximum is a
+// tree of integer max instructions (no serial compare-select chain) and the maximum over the
+// token's eight lanes is three shuffle steps; the winner's expert id (lowest id among equal
+// keys) is a second three-step minimum.  (redux.sync with one mask per group of eight lanes
+// was measured slower than the shuffles.)
+// VLOAD: every lane reads four consecutive logits per access (needs E % 32 == 0 and 16-byte
+// aligned rows); expert ids are ascending in v inside a lane under both mappings.
+__device__ __forceinline__ uint32_t router_key(float x) {
+  const uint32_t u = __float_as_uint(x + 0.0f);  // -0 and +0 share a key, as they compare equal
+  return u ^ ((uint32_t)((int32_t)u >> 31) | 0x80000000u);
+}
+__device__ __forceinline__ float router_unkey(uint32_t key) {
+  return __uint_as_float(key ^ ((uint32_t)((int32_t)~key >> 31) | 0x80000000u));
+}
+
+template <typename TL, int NV, bool VLOAD>
+__device__ __forceinline__ void router_load(const TL* __restrict__ row, int sub, int E, bool live, float (&x)[NV]) {
+  if constexpr (VLOAD) {
+#pragma unroll
+    for (int q = 0; q < NV / 4; ++q) {
+      const TL* p = row + 32 * q + 4 * sub;
+      if constexpr (sizeof(TL) == 4) {
+        const float4 v = live ? *reinterpret_cast<const float4*>(p) : make_float4(0.f, 0.f, 0.f, 0.f);
+        x[4 * q] = v.x; x[4 * q + 1] = v.y; x[4 * q + 2] = v.z; x[4 * q + 3] = v.w;
+      } else {
+        TL t[4];
+        *reinterpret_cast<uint2*>(t) = live ? *reinterpret_cast<const uint2*>(p) : make_uint2(0u, 0u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[4 * q + j] = to_f32(t[j]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int e = sub + 8 * v;
+      x[v] = (live && e < E) ? to_f32(row[e]) : 0.f;
+    }
+  }
+}
+
+template <typename TL, typename TW, int NV, bool VLOAD>
 __global__ void __launch_bounds__(RT_WARPS * 32)
 router8_kernel(const TL* __restrict__ logits, int64_t T, int E, int k, int norm,
                TW* __restrict__ weights, int64_t* __restrict__ experts) {
   const int lane = threadIdx.x & 31;
   const int sub = lane & 7;                 // lane inside the token's group of 8
-  const unsigned gmask = 0xffu << (lane & 24);
   const int64_t group_global = ((int64_t)blockIdx.x * (RT_WARPS * 32) + threadIdx.x) >> 3;
   const int64_t group_stride = ((int64_t)gridDim.x * (RT_WARPS * 32)) >> 3;
+  auto expert_of = [&](int v) { return VLOAD ? 32 * (v >> 2) + 4 * sub + (v & 3) : sub + 8 * v; };
   for (int64_t t0 = group_global - (lane >> 3); t0 < T; t0 += group_stride) {
     // t0 is the first token of this warp's four; all lanes of the warp loop together
     const int64_t t = t0 + (lane >> 3);
     const bool live = t < T;
-    const TL* row = logits + (live ? t : 0) * E;
     float x[NV];
-    float mx = -CUDART_INF_F;
+    router_load<TL, NV, VLOAD>(logits + (live ? t : 0) * E, sub, E, live, x);
+    uint32_t key[NV];  // 0 = absent (padding past E, or already taken); every real logit has a key > 0
 #pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      const int e = sub + 8 * v;
-      x[v] = (live && e < E) ? to_f32(row[e]) : -CUDART_INF_F;
-      mx = fmaxf(mx, x[v]);
-    }
+    for (int v = 0; v < NV; ++v) key[v] = expert_of(v) < E ? router_key(x[v]) : 0u;
+    auto lane_max = [&]() {
+      uint32_t m[NV];
 #pragma unroll
-    for (int d = 4; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+      for (int v = 0; v < NV; ++v) m[v] = key[v];
+#pragma unroll
+      for (int w = NV / 2; w > 0; w >>= 1)
+#pragma unroll
+        for (int v = 0; v < w; ++v) m[v] = max(m[v], m[v + w]);
+      return m[0];
+    };
+    auto group_max = [&](uint32_t v) {
+#pragma unroll
+      for (int d = 4; d > 0; d >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, d));
+      return v;
+    };
+    auto group_min = [&](uint32_t v) {
+#pragma unroll
+      for (int d = 4; d > 0; d >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, d));
+      return v;
+    };
+    const float mx = router_unkey(group_max(lane_max()));
     float sum = 0.f;
 #pragma unroll
-    for (int v = 0; v < NV; ++v) sum += (sub + 8 * v < E) ? __expf(x[v] - mx) : 0.f;
+    for (int v = 0; v < NV; ++v) sum += key[v] != 0u ? __expf(x[v] - mx) : 0.f;
 #pragma unroll
     for (int d = 4; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
     float top_sum = 0.f, my_p = 0.f;
     int my_e = 0;
     for (int r = 0; r < k; ++r) {
-      float bv = -CUDART_INF_F;
-      int be = 0x7fffffff;
+      const uint32_t best = group_max(lane_max());
+      // lowest expert id among the keys equal to the best one: scan down so the lowest v stays
+      uint32_t cand = 0x7fffffffu;
 #pragma unroll
-      for (int v = 0; v < NV; ++v)
-        if (x[v] > bv) { bv = x[v]; be = sub + 8 * v; }  // ascending e inside a lane: first hit wins
+      for (int v = NV - 1; v >= 0; --v) cand = key[v] == best ? (uint32_t)expert_of(v) : cand;
+      const int be = (int)group_min(cand);
 #pragma unroll
-      for (int d = 4; d > 0; d >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
-        const int oe = __shfl_xor_sync(0xffffffffu, be, d);
-        if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
-      }
-#pragma unroll
-      for (int v = 0; v < NV; ++v)
-        if (sub + 8 * v == be) x[v] = -CUDART_INF_F;
-      const float pr = __expf(bv - mx) / sum;  // softmax probability of the winner
+      for (int v = 0; v < NV; ++v) key[v] = expert_of(v) == be ? 0u : key[v];
+      const float pr = __expf(router_unkey(best) - mx) / sum;  // softmax probability of the winner
       top_sum += pr;
       if (r == sub) { my_p = pr; my_e = be; }
     }
-    (void)gmask;
     if (live && sub < k) {
       experts[t * k + sub] = (int64_t)my_e;
       weights[t * k + sub] = from_f32<TW>(norm ? my_p / top_sum : my_p);
@@ -153,9 +202,16 @@ static int launch_router(const void* logits, int64_t T, int E, int k, int norm, 
     const int64_t want8 = (T + 31) / 32;  // 32 tokens per CTA
     const int grid8 = (int)(want8 < cap ? want8 : cap);
     const int nv = (E + 7) / 8;
-#define MOE_RT8_CASE(NV)                                                                             \
-  router8_kernel<TL, TW, NV><<<grid8, RT_WARPS * 32, 0, stream>>>((const TL*)logits, T, E, k, norm, \
-                                                                  (TW*)weights, experts)
+    const bool vload = (E % 32) == 0 && (((uintptr_t)logits) & 15) == 0;
+#define MOE_RT8_CASE(NV)                                                                                         \
+  do {                                                                                                           \
+    if (vload && (NV) % 4 == 0 && (NV) * 8 == E)                                                                 \
+      router8_kernel<TL, TW, NV, true><<<grid8, RT_WARPS * 32, 0, stream>>>((const TL*)logits, T, E, k, norm,    \
+                                                                            (TW*)weights, experts);              \
+    else                                                                                                         \
+      router8_kernel<TL, TW, NV, false><<<grid8, RT_WARPS * 32, 0, stream>>>((const TL*)logits, T, E, k, norm,   \
+                                                                             (TW*)weights, experts);             \
+  } while (0)
     if (nv <= 2) MOE_RT8_CASE(2);
     else if (nv <= 4) MOE_RT8_CASE(4);
     else if (nv <= 8) MOE_RT8_CASE(8);
