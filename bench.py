@@ -174,13 +174,16 @@ def config_dict(args, cfg):
 _TIME_OVERRIDE = {}  # {"iters": n, "warmup": m} for profiling runs (few launches per kernel)
 
 
-def time_cuda(fn, iters: int = 20, warmup: int = 3, flush=None) -> float:
+def time_cuda(fn, iters: int = 20, warmup: int = 3, flush=None, inner: int = 1) -> float:
     """Median device time of fn() in ms (CUDA events around every call; an optional buffer larger
     than L2 is rewritten between calls so that small inputs are not served from cache).  Some
     device work is always queued ahead of the first event (the flush, else a short spin), so the
-    host's launch latency of fn() is not counted as kernel time."""
+    host's launch latency of fn() is not counted as kernel time.  `inner` > 1 times that many
+    back-to-back calls per sample (for kernels whose working set is several times L2), which
+    amortises the event overhead of a few microseconds."""
     iters = _TIME_OVERRIDE.get("iters", iters)
     warmup = _TIME_OVERRIDE.get("warmup", warmup)
+    inner = _TIME_OVERRIDE.get("inner", inner)
     for _ in range(warmup):
         fn()
     times = []
@@ -191,10 +194,11 @@ def time_cuda(fn, iters: int = 20, warmup: int = 3, flush=None) -> float:
         else:
             torch.cuda._sleep(200_000)  # ~0.1 ms of device time for the host to get ahead
         a.record()
-        fn()
+        for _ in range(inner):
+            fn()
         b.record()
         b.synchronize()
-        times.append(a.elapsed_time(b))
+        times.append(a.elapsed_time(b) / inner)
     return float(np.median(times))
 
 
@@ -209,7 +213,7 @@ def run_kernel_suite(args):
     from qwen3_moe_fused.grouped_gemm.forward_4bit import grouped_gemm_forward_4bit
     from qwen3_moe_fused.kernels.fast_lora import fast_lora
     from qwen3_moe_fused.kernels.indexing import get_expert_counts_and_idx
-    from qwen3_moe_fused.kernels.routing import _combine, _gather_rows, softmax_topk
+    from qwen3_moe_fused.kernels.routing import _combine, _expand_rows, _gather_rows, softmax_topk
     from qwen3_moe_fused.kernels.silu_mul import silu_mul_backward_inplace, silu_mul_forward
     from qwen3_moe_fused.moe_block import moe_block_forward
     from qwen3_moe_fused.quantize.nf4 import dequantize_4bit, quantize_nf4
@@ -222,7 +226,7 @@ def run_kernel_suite(args):
     flush = torch.zeros(64 * 1024 * 1024, device=dev, dtype=torch.float32)  # 256 MB
     torch.manual_seed(0)
     if args.kernel_iters:
-        _TIME_OVERRIDE.update(iters=args.kernel_iters, warmup=1)
+        _TIME_OVERRIDE.update(iters=args.kernel_iters, warmup=1, inner=1)
 
     def emit(name, ms, nbytes=None, flops=None, **extra):
         line = {"suite": "kernels", "kernel": name, "ms": ms}
@@ -236,8 +240,8 @@ def run_kernel_suite(args):
     # ---- SiLU-mul at the down-projection input size ----
     n = 65536 * 768
     e, g, dh = (torch.randn(n, device=dev, dtype=bf) for _ in range(3))
-    emit("silu_mul_fwd bf16 65536x768", time_cuda(lambda: silu_mul_forward(e, g)), 3 * 2 * n)
-    emit("silu_mul_bwd_inplace bf16 65536x768", time_cuda(lambda: silu_mul_backward_inplace(dh, e, g)), 6 * 2 * n)
+    emit("silu_mul_fwd bf16 65536x768", time_cuda(lambda: silu_mul_forward(e, g), inner=5), 3 * 2 * n)
+    emit("silu_mul_bwd_inplace bf16 65536x768", time_cuda(lambda: silu_mul_backward_inplace(dh, e, g), inner=5), 6 * 2 * n)
     del e, g, dh
 
     # ---- router ----
@@ -261,9 +265,11 @@ def run_kernel_suite(args):
     sel = torch.randint(0, 128, (T * k,), device=dev)
     _, sort_idx, inv_sort_idx = get_expert_counts_and_idx(sel, 128)
     w = torch.rand(T, k, device=dev, dtype=bf)
-    emit("gather_rows bf16 16384 tokens x8 x2048", time_cuda(lambda: _gather_rows(hidden, sort_idx, k)), 2 * (T * H + T * k * H) + 4 * T * k)
+    emit("gather_rows bf16 16384 tokens x8 x2048", time_cuda(lambda: _gather_rows(hidden, sort_idx, k), flush=flush), 2 * (T * H + T * k * H) + 4 * T * k)
+    emit("expand_rows (same rows, token-major) bf16 16384 tokens x8 x2048", time_cuda(lambda: _expand_rows(hidden, inv_sort_idx, k), flush=flush),
+         2 * (T * H + T * k * H) + 4 * T * k)
     y = torch.randn(T * k, H, device=dev, dtype=bf)
-    emit("combine bf16 16384 tokens x8 x2048", time_cuda(lambda: _combine(y, inv_sort_idx, w)), 2 * (T * k * H + T * H) + 6 * T * k)
+    emit("combine bf16 16384 tokens x8 x2048", time_cuda(lambda: _combine(y, inv_sort_idx, w), inner=5), 2 * (T * k * H + T * H) + 6 * T * k)
     del hidden, y
 
     # ---- NF4: decode alone, fused forward vs decode + GEMM (BASELINE config 4) ----
@@ -272,7 +278,7 @@ def run_kernel_suite(args):
     packed, state = quantize_nf4(wfull, 64)
     del wfull
     nel = E * N * K
-    emit("nf4_dequant 128x1536x2048 -> bf16", time_cuda(lambda: dequantize_4bit(packed, state, bf)), nel // 2 + nel // 64 * 4 + nel * 2)
+    emit("nf4_dequant 128x1536x2048 -> bf16", time_cuda(lambda: dequantize_4bit(packed, state, bf), inner=5), nel // 2 + nel // 64 * 4 + nel * 2)
     if args.hbm_only:
         assert _lib.read_error_flag() == 0
         return

@@ -167,6 +167,12 @@ int moe_router_softmax_topk(const void* logits, int dtype_logits, int64_t T, int
 int moe_gather_rows(const void* hidden, const int32_t* sort_idx, int k, void* out,
                     int64_t rows, int H, int dtype, void* stream);
 
+/* The same rows as moe_gather_rows, written token by token through the inverse index:
+ * out[inv_sort_idx[t*k + j], :] = hidden[t, :] for j < k.  Every token row is read once.
+ * Replaces qwen3_moe_fused/modular_qwen3_moe_fused.py:95-103. */
+int moe_expand_rows(const void* hidden, const int32_t* inv_sort_idx, int k, void* out,
+                    int64_t tokens, int H, int dtype, void* stream);
+
 /* out[t,:] = sum_j weights[t,j] * y[inv_sort_idx[t*k+j], :]  with the reference's
  * rounding (product and sum in fp32, one rounding to dtype).
  * Replaces qwen3_moe_fused/modular_qwen3_moe_fused.py:112-115. */

@@ -92,7 +92,7 @@ def test_router_ties_pick_lowest_expert(cuda):
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 @pytest.mark.parametrize("T,k,H", [(64, 8, 2048), (33, 3, 16), (5, 2, 7)])
 def test_gather_and_combine(cuda, dtype, T, k, H):
-    from qwen3_moe_fused.kernels.routing import _combine, _gather_rows
+    from qwen3_moe_fused.kernels.routing import _combine, _expand_rows, _gather_rows
 
     rng = np.random.default_rng(T * k + H)
     E = 9
@@ -102,6 +102,9 @@ def test_gather_and_combine(cuda, dtype, T, k, H):
     weights = rounded(rng.random((T, k)), dtype)
     got = _gather_rows(to_dev(hidden, dtype, cuda), torch.from_numpy(sort_idx).to(cuda), k)
     np.testing.assert_array_equal(to_np(got), O.gather_rows(hidden, sort_idx, k))
+    # the token-major form writes the same rows through the inverse index
+    got2 = _expand_rows(to_dev(hidden, dtype, cuda), torch.from_numpy(inv_sort_idx).to(cuda), k)
+    assert torch.equal(got2, got)
     y = rounded(rng.standard_normal((T * k, H)), dtype)
     out = _combine(to_dev(y, dtype, cuda), torch.from_numpy(inv_sort_idx).to(cuda), to_dev(weights, dtype, cuda))
     assert_close(to_np(out), O.combine(y, inv_sort_idx, weights, dtype), dtype, "combine")

@@ -235,6 +235,20 @@ nf4_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__
   }
 }
 
+// 16-byte load that asks L2 to keep the line (token rows are read k times each, while the
+// output streams through the cache).
+__device__ __forceinline__ uint64_t l2_keep_policy() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint4 ld_keep(const uint4* ptr, uint64_t policy) {
+  uint4 v;
+  asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr), "l"(policy));
+  return v;
+}
+
 // out[j,:] = hidden[sort_idx[j] / k, :].  Vector form: one warp per output row, up to eight
 // 16-byte loads in flight per lane, and the index of the warp's next row is fetched before the
 // current row is copied (the index -> row -> store chain is what bounds this kernel otherwise).
@@ -248,6 +262,7 @@ gather_rows_kernel(const T* __restrict__ hidden, const int32_t* __restrict__ sor
     const int lane = threadIdx.x & 31;
     const int64_t warps = (int64_t)gridDim.x * (EW_THREADS / 32);
     int64_t j = (int64_t)blockIdx.x * (EW_THREADS / 32) + (threadIdx.x >> 5);
+    const uint64_t keep = l2_keep_policy();
     int idx = j < rows ? sort_idx[j] : 0;
     for (; j < rows; j += warps) {
       const int64_t jn = j + warps;
@@ -259,7 +274,7 @@ gather_rows_kernel(const T* __restrict__ hidden, const int32_t* __restrict__ sor
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
           const int c = c0 + u * 32 + lane;
-          if (c < row_vecs) v[u] = __ldg(src + c);
+          if (c < row_vecs) v[u] = ld_keep(src + c, keep);
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -274,6 +289,49 @@ gather_rows_kernel(const T* __restrict__ hidden, const int32_t* __restrict__ sor
       const T* src = hidden + (int64_t)(sort_idx[j] / k) * H;
       T* dst = out + j * H;
       for (int c = threadIdx.x; c < H; c += EW_THREADS) dst[c] = src[c];
+    }
+  }
+}
+
+// out[inv_sort_idx[t*k + j], :] = hidden[t, :]: the same result as gather_rows, produced token by
+// token, so every token row is read from memory exactly once (the gather form re-reads each row
+// k times, and the output stream pushes the rows out of L2 in between).  One warp per token.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(EW_THREADS)
+expand_rows_kernel(const T* __restrict__ hidden, const int32_t* __restrict__ inv_sort_idx, int k,
+                   T* __restrict__ out, int64_t tokens, int H) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (EW_THREADS / 32);
+  for (int64_t t = (int64_t)blockIdx.x * (EW_THREADS / 32) + (threadIdx.x >> 5); t < tokens; t += warps) {
+    if constexpr (VEC) {
+      constexpr int UNROLL = 8;
+      const int row_vecs = H / Vec<T>::N;
+      const uint4* src = reinterpret_cast<const uint4*>(hidden + t * H);
+      for (int c0 = 0; c0 < row_vecs; c0 += 32 * UNROLL) {
+        uint4 v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int c = c0 + u * 32 + lane;
+          if (c < row_vecs) v[u] = __ldcs(src + c);
+        }
+        for (int j0 = 0; j0 < k; j0 += 32) {
+          const int mine = j0 + lane < k ? inv_sort_idx[t * k + j0 + lane] : 0;
+          const int nj = min(32, k - j0);
+          for (int j = 0; j < nj; ++j) {
+            uint4* dst = reinterpret_cast<uint4*>(out + (int64_t)__shfl_sync(0xffffffffu, mine, j) * H);
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+              const int c = c0 + u * 32 + lane;
+              if (c < row_vecs) __stcs(dst + c, v[u]);
+            }
+          }
+        }
+      }
+    } else {
+      for (int j = 0; j < k; ++j) {
+        T* dst = out + (int64_t)inv_sort_idx[t * k + j] * H;
+        for (int c = lane; c < H; c += 32) dst[c] = hidden[t * H + c];
+      }
     }
   }
 }
@@ -423,6 +481,23 @@ MOE_API int moe_gather_rows(const void* hidden, const int32_t* sort_idx, int k, 
     const int grid = (int)(want < cap ? want : cap);
     if (vec) gather_rows_kernel<T, true><<<grid, EW_THREADS, 0, stream>>>((const T*)hidden, sort_idx, k, (T*)out, rows, H);
     else gather_rows_kernel<T, false><<<grid, EW_THREADS, 0, stream>>>((const T*)hidden, sort_idx, k, (T*)out, rows, H);
+  });
+  return launch_status();
+}
+
+MOE_API int moe_expand_rows(const void* hidden, const int32_t* inv_sort_idx, int k, void* out,
+                            int64_t tokens, int H, int dtype, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (tokens < 0 || H < 0 || k <= 0) return MOE_ERR_SHAPE;
+  if (tokens == 0 || H == 0) return MOE_OK;
+  if (!hidden || !inv_sort_idx || !out) return MOE_ERR_NULL;
+  const int64_t want = (tokens + EW_THREADS / 32 - 1) / (EW_THREADS / 32);
+  const int64_t cap = (int64_t)sm_count() * 8;
+  const int grid = (int)(want < cap ? want : cap);
+  MOE_DISPATCH_FLOAT(dtype, T, {
+    const bool vec = aligned16(hidden) && aligned16(out) && (H % Vec<T>::N == 0);
+    if (vec) expand_rows_kernel<T, true><<<grid, EW_THREADS, 0, stream>>>((const T*)hidden, inv_sort_idx, k, (T*)out, tokens, H);
+    else expand_rows_kernel<T, false><<<grid, EW_THREADS, 0, stream>>>((const T*)hidden, inv_sort_idx, k, (T*)out, tokens, H);
   });
   return launch_status();
 }

@@ -70,6 +70,23 @@ def _gather_rows(hidden: torch.Tensor, sort_idx: torch.Tensor, k: int) -> torch.
     return out
 
 
+def _expand_rows(hidden: torch.Tensor, inv_sort_idx: torch.Tensor, k: int) -> torch.Tensor:
+    """The result of _gather_rows computed through the inverse index (out[inv_sort_idx[t*k+j]] =
+    hidden[t]): every token row is read once instead of k times."""
+    assert hidden.is_cuda and hidden.ndim == 2 and hidden.is_contiguous()
+    assert inv_sort_idx.dtype == torch.int32 and inv_sort_idx.is_contiguous()
+    tokens = hidden.shape[0]
+    assert inv_sort_idx.numel() == tokens * k
+    out = torch.empty((tokens * k, hidden.shape[1]), device=hidden.device, dtype=hidden.dtype)
+    with torch.cuda.device(hidden.device):
+        status = _lib.load().moe_expand_rows(
+            _lib.ptr(hidden), _lib.ptr(inv_sort_idx), k, _lib.ptr(out), tokens, hidden.shape[1],
+            _lib.float_code(hidden.dtype), _lib.stream_ptr(hidden.device),
+        )
+    _lib.check(status, "moe_expand_rows")
+    return out
+
+
 def _combine(y: torch.Tensor, inv_sort_idx: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
     assert y.is_cuda and y.ndim == 2 and y.is_contiguous()
     assert inv_sort_idx.dtype == torch.int32 and inv_sort_idx.is_contiguous()
@@ -92,6 +109,8 @@ class GatherRows(torch.autograd.Function):
     def forward(ctx, hidden, sort_idx, inv_sort_idx, k):
         ctx.save_for_backward(inv_sort_idx)
         ctx.k = k
+        if inv_sort_idx.numel() == hidden.shape[0] * k:
+            return _expand_rows(hidden, inv_sort_idx, k)  # same rows, each token read once
         return _gather_rows(hidden, sort_idx, k)
 
     @staticmethod
