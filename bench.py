@@ -612,6 +612,14 @@ def main():
         e2e_ms = e0.elapsed_time(e1) / args.steps
     clocks = sampler.stop() if rank == 0 else None
 
+    # ---- each GEMM alone (N = 1): isolated launches with idle time between them, i.e. at burst
+    # clocks, to set beside the burst cuBLAS figure; the timed loop above runs under the power cap ----
+    burst_ms = {}
+    if world == 1 and not args.only:
+        burst_ms["fwd"] = time_cuda(lambda: grouped_gemm_forward(x_d, w, m_sizes), iters=20)
+        burst_ms["dx"] = time_cuda(lambda: grouped_gemm_forward_transposed(dy_d, w, m_sizes), iters=20)
+        burst_ms["dw"] = time_cuda(lambda: grouped_gemm_backward_dw(x_d, dy_d, m_sizes, bf), iters=20)
+
     # ---- the row exchange alone (N > 1): one dispatch of x, timed on the device ----
     xchg_ms, remote_bytes = float("nan"), 0
     if world > 1:
@@ -678,6 +686,9 @@ def main():
             "tokens_per_s": T * world / (resident_ms * 1e-3),
             "clocks": clocks, "kernel_wait_errors": err_flag,
         }
+        for name, ms in burst_ms.items():
+            line["kernels"][name].update(isolated_ms=ms, isolated_tflops=flops_one / (ms * 1e-3) / 1e12,
+                                         isolated_frac_of_burst_peak=flops_one / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"])
         if world > 1:
             line["exchange"] = {"what": "dispatch of x alone (rows to their experts' ranks), rank 0's remote bytes",
                                 "transport": args.ep_transport, "ms": xchg_ms, "remote_bytes": remote_bytes,

@@ -135,6 +135,20 @@ int moe_grouped_gemm_fwd_nf4(const void* x, const uint8_t* packed, const float* 
                              int64_t M, int N, int K, int E, int dtype_in, int dtype_out,
                              void* ws, size_t ws_bytes, void* stream);
 
+/* dX through an NF4 weight decoded inside the kernel:
+ *   y[m,n] = sum_k w[e(m),k,n] * x[m,k],  w = the NF4 tensor of logical shape (E,K,N)
+ *   (K = the layer's out_features, N = its in_features), decoded as in
+ *   moe_grouped_gemm_fwd_nf4.  x (M,K), y (M,N).
+ * The reference has no fused form: its backward decodes the whole weight first
+ * (qwen3_moe_fused/kernels/fast_lora.py:57-63,128; quantize/layer.py:17-22).
+ * Tensor-core CTA-pair kernel only: bf16/fp16, blocksize >= 64, N % 64 == 0, K % 64 == 0,
+ * N >= 192; MOE_ERR_UNSUPPORTED otherwise (decode with moe_nf4_dequant and call
+ * moe_grouped_gemm_dx instead). */
+int moe_grouped_gemm_dx_nf4(const void* x, const uint8_t* packed, const float* code,
+                            const float* absmax, int blocksize, const void* m_sizes,
+                            int m_sizes_dtype, void* y, int64_t M, int N, int K, int E,
+                            int dtype_in, int dtype_out, void* ws, size_t ws_bytes, void* stream);
+
 /* Stand-alone NF4 decode of n_elems weights (same format as above) to dtype_out.
  * Stands in for the bitsandbytes dequantize_4bit call at
  * qwen3_moe_fused/quantize/layer.py:21 and qwen3_moe_fused/kernels/fast_lora.py:62. */

@@ -67,3 +67,51 @@ def test_fused_equals_decode_then_gemm(cuda):
     b = moe_fused_linear_4bit(tx, packed, state, tm, fused=False)
     assert_close(to_np(a), to_np(b), "bf16", "fused vs unfused")
     assert_close(to_np(a), ref, "bf16", "fused vs oracle")
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("M,K,N,E,bs,empty", [
+    (1024, 2048, 768, 16, 64, 0.0),     # gate-projection shape (E, out=768, in=2048)
+    (512, 256, 320, 8, 64, 0.2),
+    (4096, 2048, 1536, 4, 64, 0.0),
+    (700, 512, 192, 3, 128, 0.0),       # block size 128: two 64-feature halves share an absmax
+    (300, 128, 64, 5, 64, 0.0),         # input width below the pair kernel: decode + dX route
+])
+def test_fused_dx(cuda, dtype, M, K, N, E, bs, empty):
+    """dX through the NF4 weight: the weight is the (E, out=N_w, in=K_w) tensor of `make`, dy has
+    N_w columns and the result K_w columns."""
+    from qwen3_moe_fused import _lib
+    from qwen3_moe_fused.grouped_gemm.forward_4bit import grouped_gemm_forward_transposed_4bit
+
+    rng = np.random.default_rng(M + K + N + E + bs + 1)
+    from qwen3_moe_fused.quantize.nf4 import Nf4State
+
+    code = O.nf4_code()
+    w = (rng.standard_normal((E, N, K)) / np.sqrt(N)).astype(np.float32)
+    packed, absmax = O.nf4_quantize(w, bs, code)
+    w_deq = O.nf4_dequantize(packed, absmax, code, bs, w.shape, dtype)
+    dy = rounded(rng.standard_normal((M, N)), dtype)
+    m_sizes = random_m_sizes(rng, M, E, empty)
+    state = Nf4State(absmax=torch.from_numpy(absmax).to(cuda), code=torch.from_numpy(code).to(cuda), blocksize=bs,
+                     shape=torch.Size(w.shape), dtype=DT[dtype])
+    ref = O.grouped_gemm_dx(dy, w_deq, m_sizes, dtype)
+    dx = grouped_gemm_forward_transposed_4bit(to_dev(dy, dtype, cuda), torch.from_numpy(packed).to(cuda), state,
+                                              torch.from_numpy(m_sizes).to(cuda))
+    torch.cuda.synchronize()
+    assert _lib.read_error_flag() == 0
+    assert dx.shape == (M, K)
+    assert_close(to_np(dx), ref, dtype, "nf4 dx")
+
+
+def test_linear4bit_backward_is_fused_dx(cuda):
+    from qwen3_moe_fused.quantize.linear4bit import moe_fused_linear_4bit
+
+    rng = np.random.default_rng(5)
+    x, packed, state, m_sizes, _ = make(cuda, rng, 1024, 512, 512, 8, 64, "bf16", 0.1)
+    tm = torch.from_numpy(m_sizes).to(cuda)
+    xa = to_dev(x, "bf16", cuda).requires_grad_()
+    xb = xa.detach().clone().requires_grad_()
+    dy = torch.randn(1024, 512, device=cuda).to(torch.bfloat16)
+    moe_fused_linear_4bit(xa, packed, state, tm, fused=True).backward(dy)
+    moe_fused_linear_4bit(xb, packed, state, tm, fused=False).backward(dy)
+    assert_close(to_np(xa.grad), to_np(xb.grad), "bf16", "fused dX vs decode + dX")

@@ -19,7 +19,7 @@ bool tc_nf4_eligible(const void* x, const void* packed, const void* absmax, cons
                      int E, int blocksize, int dtype_in, int dtype_out);
 int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code, const float* absmax, int blocksize,
                         const void* m_sizes, int ms64, void* out, int64_t M, int N, int K, int E,
-                        int dtype_in, int dtype_out, void* ws, size_t ws_bytes, cudaStream_t stream);
+                        int dtype_in, int dtype_out, void* ws, size_t ws_bytes, cudaStream_t stream, bool transposed);
 int tc_grouped_gemm_scattered(int which, const void* a, const void* b, const void* group_sizes, int ms64,
                               const int* weight_index, int n_weights, const uint64_t* out_ptrs, void* out_template,
                               int64_t M, int N, int K, int G, int dtype_in, int dtype_out, void* ws, size_t ws_bytes,
@@ -140,8 +140,29 @@ MOE_API int moe_grouped_gemm_fwd_nf4(const void* x, const uint8_t* packed, const
   const bool can_tc = tc_nf4_eligible(x, packed, absmax, y, M, N, K, E, blocksize, dtype_in, dtype_out);
   if ((path == MOE_PATH_TC || path == MOE_PATH_TC_SINGLE) && !can_tc) return MOE_ERR_UNSUPPORTED;
   if (can_tc && path != MOE_PATH_SIMT)
-    return tc_grouped_gemm_nf4(x, packed, code, absmax, blocksize, m_sizes, msd == MOE_I64, y, M, N, K, E, dtype_in, dtype_out, ws, ws_bytes, (cudaStream_t)stream);
+    return tc_grouped_gemm_nf4(x, packed, code, absmax, blocksize, m_sizes, msd == MOE_I64, y, M, N, K, E, dtype_in, dtype_out, ws, ws_bytes, (cudaStream_t)stream, false);
   return simt_grouped_gemm_nf4(x, packed, code, absmax, shift, m_sizes, msd == MOE_I64, y, M, N, K, E, dtype_in, dtype_out, (cudaStream_t)stream);
+}
+
+MOE_API int moe_grouped_gemm_dx_nf4(const void* x, const uint8_t* packed, const float* code, const float* absmax,
+                                    int blocksize, const void* m_sizes, int msd, void* y, int64_t M, int N, int K,
+                                    int E, int dtype_in, int dtype_out, void* ws, size_t ws_bytes, void* stream) {
+  int st = check_common(x, packed, m_sizes, msd, y, M, N, K, E, dtype_in, dtype_out);
+  if (st != MOE_OK) return st;
+  if (!code || !absmax) return MOE_ERR_NULL;
+  int shift = -1;
+  for (int s = 0; s < 31; ++s) if ((1 << s) == blocksize) shift = s;
+  if (shift < 0 || (N & 1) || (((int64_t)E * N * K) % blocksize) != 0) return MOE_ERR_SHAPE;
+  if (M == 0 || N == 0) return MOE_OK;
+  if (K == 0) return cuda_status(cudaMemsetAsync(y, 0, (size_t)M * N * dtype_size(dtype_out), (cudaStream_t)stream));
+  if (!device_is_sm100()) return MOE_ERR_DEVICE;
+  // Tensor-core CTA-pair kernel only: 16-bit activations, an absmax block = 64 (or a multiple)
+  // consecutive output features of one contraction row, whole 64-row contraction blocks.
+  if (!tc_eligible(1, x, packed, y, M, N, K, E, dtype_in, dtype_out) || blocksize < 64 || (N % 64) != 0 ||
+      (K % 64) != 0 || N < 192 || ((uintptr_t)absmax & 3))
+    return MOE_ERR_UNSUPPORTED;
+  return tc_grouped_gemm_nf4(x, packed, code, absmax, blocksize, m_sizes, msd == MOE_I64, y, M, N, K, E, dtype_in,
+                             dtype_out, ws, ws_bytes, (cudaStream_t)stream, true);
 }
 
 static int run_scattered(int which, const void* x, const void* w, const void* group_sizes, int msd,

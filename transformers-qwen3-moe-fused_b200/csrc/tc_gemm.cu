@@ -889,30 +889,38 @@ bool tc_nf4_eligible(const void* x, const void* packed, const void* absmax, cons
 
 int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code, const float* absmax, int blocksize,
                         const void* m_sizes, int ms64, void* out, int64_t M, int N, int K, int E,
-                        int dtype_in, int dtype_out, void* ws, size_t ws_bytes, cudaStream_t stream) {
+                        int dtype_in, int dtype_out, void* ws, size_t ws_bytes, cudaStream_t stream, bool transposed) {
+  // transposed: y[m,n] = sum_k w[e,k,n] x[m,k] with the NF4 tensor of logical shape (E, K, N)
   using namespace tc;
   bind_context_once();
   GemmParams p;
   p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags(); p.group_maps = nullptr;
   p.idesc = make_idesc(dtype_in == MOE_BF16 ? 1 : 0, 0, 0, BM, NF4_BN);
+  if (transposed && N < 192) return MOE_ERR_UNSUPPORTED;  // only the CTA-pair kernel has the transposed decode
   Nf4Params q;
   q.code = code; q.absmax = absmax; q.shift = 0;
   while ((1 << q.shift) < blocksize) ++q.shift;
   CUtensorMap ma, mq;
   int st;
-  if (N >= 192 && !(p.debug & 64)) {
-    // CTA-pair form: 128 weight rows of packed codes per CTA and stage
+  if (N >= 192 && (transposed || !(p.debug & 64))) {
+    // CTA-pair form: 128 weight rows of packed codes per CTA and stage (transposed: 64
+    // contraction rows x 128 output features)
     EncodeTiledFn fn = encode_fn();
     if (!fn) return MOE_ERR_DEVICE;
     cuuint64_t dims[3] = {(cuuint64_t)K / 2, (cuuint64_t)N, (cuuint64_t)E};
     cuuint64_t strides[2] = {(cuuint64_t)K / 2, (cuuint64_t)K / 2 * (cuuint64_t)N};
     cuuint32_t box[3] = {BK / 2, 128, 1};
     cuuint32_t estr[3] = {1, 1, 1};
+    if (transposed) {
+      dims[0] = (cuuint64_t)N / 2; dims[1] = (cuuint64_t)K;
+      strides[0] = (cuuint64_t)N / 2; strides[1] = (cuuint64_t)N / 2 * (cuuint64_t)K;
+      box[0] = 64; box[1] = BK;
+    }
     if (fn(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(packed), dims, strides, box, estr,
            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return MOE_ERR_UNSUPPORTED;
     if ((st = make_map(&ma, dtype_in, x, (uint64_t)K, (uint64_t)M, 0, 128)) != MOE_OK) return st;
-    p.idesc = make_idesc(dtype_in == MOE_BF16 ? 1 : 0, 0, 0, 256, 0);
+    p.idesc = make_idesc(dtype_in == MOE_BF16 ? 1 : 0, transposed ? 1 : 0, 0, 256, 0);
     const int pbytes = NF4P_STAGES * NF4P_STAGE_BYTES + 4 * PAIR_STAGING_BYTES + (int)sizeof(Nf4PairControl) + 2 * (E + 1) * 4 + 1024;
     if (pbytes <= SMEM_LIMIT) {
       const bool ws_ok = ws != nullptr && (((uintptr_t)ws & 127) == 0) && ws_bytes >= (size_t)2 * E * sizeof(CUtensorMap);
@@ -926,16 +934,23 @@ int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code,
         if ((st = launch_status()) != MOE_OK) return st;
         p.group_maps = reinterpret_cast<const CUtensorMap*>(ws);
       }
+#define MOE_NF4P_LAUNCH(BF, WT)                                                                          \
+  do {                                                                                                   \
+    auto kern = pair_fwd_nf4_kernel<BF, WT>;                                                             \
+    if ((st = set_smem(kern, pbytes)) != MOE_OK) return st;                                              \
+    return launch_pair_threads(kern, 2 * resident_pairs(kern, pbytes, NF4P_THREADS), NF4P_THREADS, pbytes, \
+                               stream, mq, ma, p, q);                                                    \
+  } while (0)
       if (dtype_in == MOE_BF16) {
-        auto kern = pair_fwd_nf4_kernel<true>;
-        if ((st = set_smem(kern, pbytes)) != MOE_OK) return st;
-        return launch_pair_threads(kern, 2 * resident_pairs(kern, pbytes, NF4P_THREADS), NF4P_THREADS, pbytes, stream, mq, ma, p, q);
+        if (transposed) MOE_NF4P_LAUNCH(true, true);
+        MOE_NF4P_LAUNCH(true, false);
       }
-      auto kern = pair_fwd_nf4_kernel<false>;
-      if ((st = set_smem(kern, pbytes)) != MOE_OK) return st;
-      return launch_pair_threads(kern, 2 * resident_pairs(kern, pbytes, NF4P_THREADS), NF4P_THREADS, pbytes, stream, mq, ma, p, q);
+      if (transposed) MOE_NF4P_LAUNCH(false, true);
+      MOE_NF4P_LAUNCH(false, false);
+#undef MOE_NF4P_LAUNCH
     }
   }
+  if (transposed) return MOE_ERR_UNSUPPORTED;
   if ((st = make_map(&ma, dtype_in, x, (uint64_t)K, (uint64_t)M, 0, BM)) != MOE_OK) return st;
   {
     EncodeTiledFn fn = encode_fn();

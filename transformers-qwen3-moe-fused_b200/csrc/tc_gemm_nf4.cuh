@@ -16,6 +16,13 @@
 // The decode warps publish their shared-memory writes to the async proxy
 // (fence.proxy.async) before arriving on the leader's barrier.
 //
+// pair_fwd_nf4_kernel<IS_BF16, true> is the transposed form (dX through an NF4 weight):
+//   y[t, n] = sum_k w[e, k, n] x[t, k],  w = the (E, K, N) NF4 tensor, n contiguous in a block
+// A stage then holds 64 contraction rows x 128 output features per CTA: the codes arrive as a
+// 64 x 64-byte box, a decode thread owns (contraction row, 64-feature half) = one absmax block,
+// and the 16-bit tile is written in the MN-major form pair_fwd_kernel<true> loads by TMA
+// (two chunks of 64 rows x 128 bytes).
+//
 // Decode without table reads from shared memory (shared-memory bandwidth is what bounds
 // these kernels): a thread owns 32 consecutive weights of one row, which share one absmax.
 // It first forms the 16 possible values round16(code[n] * absmax) in registers, splits
@@ -84,7 +91,7 @@ __device__ __forceinline__ void nf4_lookup4(const Nf4Planes& pl, uint32_t two_by
   out23 = prmt(lo, hi, 0x6273);  // (e2, e3)
 }
 
-template <bool IS_BF16>
+template <bool IS_BF16, bool W_T = false>
 __global__ void __launch_bounds__(NF4P_THREADS, 1)
 pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_x,
                     const GemmParams p, const Nf4Params q) {
@@ -167,7 +174,8 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, PW_EMPTY)) { ok = false; break; }
           uint8_t* st = smem + s * STAGE_BYTES;
           mbar_expect_tx(&ctl->qfull[s], NF4P_PACKED_BYTES);
-          tma_load_3d(st + Q_OFF, &tmap_q, &ctl->qfull[s], kb * (BK / 2), w_row, e);
+          if constexpr (!W_T) tma_load_3d(st + Q_OFF, &tmap_q, &ctl->qfull[s], kb * (BK / 2), w_row, e);
+          else tma_load_3d(st + Q_OFF, &tmap_q, &ctl->qfull[s], w_row / 2, kb * BK, e);
           if (leader) mbar_expect_tx(&ctl->full[s], 2 * PAIR_HALF_BYTES);
           tma_load_2d_pair(st + B_OFF, mx, full_leader0 + s * 8, kb * BK, tok);
         }
@@ -194,12 +202,13 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (!mbar_wait_cluster(&ctl->ready[s], ph, abort_flag, PW_PEER)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-          const uint64_t da = make_smem_desc(sa, 16, 1024);
+          const uint64_t da = W_T ? make_smem_desc(sa, BK * 128, 1024) : make_smem_desc(sa, 16, 1024);
           const uint64_t db = make_smem_desc(sa + B_OFF, 16, 1024);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t adv = (uint64_t)((k * UMMA_K * 2) >> 4);
-            if (!(p.debug & 4)) umma_f16_pair(d_tmem, da + adv, db + adv, idesc, (kb | k) != 0);
+            const uint64_t a_adv = W_T ? (uint64_t)((k * UMMA_K * 128) >> 4) : adv;
+            if (!(p.debug & 4)) umma_f16_pair(d_tmem, da + a_adv, db + adv, idesc, (kb | k) != 0);
           }
           umma_commit_pair(&ctl->empty[s], 3);
         }
@@ -279,9 +288,14 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     for (int64_t tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
       int e, t0, n_mma, n0;
       decode(tile, e, t0, n_mma, n0);
-      const int n = n0 + (int)rank * 128 + row;
+      // forward: the thread's weight row n, its k-block kb covers columns kb*64..; flat index of
+      // (e, n, kb*64).  transposed: contraction row kb*64 + (row & 63), output features
+      // n0 + rank*128 + (row >> 6)*64 ..+63; flat index of (e, that row, that first feature).
+      const int n = W_T ? n0 + (int)rank * 128 + (row >> 6) * 64 : n0 + (int)rank * 128 + row;
       const bool n_ok = n < p.N;
-      const int64_t row_flat = ((int64_t)e * p.N + (n_ok ? n : 0)) * p.K;
+      const int64_t row_flat = W_T ? ((int64_t)e * p.K + (row & 63)) * p.N + (n_ok ? n : 0)
+                                   : ((int64_t)e * p.N + (n_ok ? n : 0)) * p.K;
+      const int64_t kb_stride = W_T ? (int64_t)BK * p.N : (int64_t)BK;  // flat elements from one k-block to the next
       // k-blocks of this tile that belong to this group: kb0, kb0 + 2, ...
       const int kb0 = (int)((group - (int)(it & 1)) & 1);
       // absmax of the next AM_AHEAD own k-blocks is kept in flight: one L2 round trip per
@@ -291,7 +305,7 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 #pragma unroll
       for (int i = 0; i < AM_AHEAD; ++i) {
         const int kbi = kb0 + 2 * i;
-        am_ring[i] = (n_ok && kbi < k_blocks) ? __ldg(q.absmax + ((row_flat + (int64_t)kbi * BK) >> q.shift)) : 0.f;
+        am_ring[i] = (n_ok && kbi < k_blocks) ? __ldg(q.absmax + ((row_flat + (int64_t)kbi * kb_stride) >> q.shift)) : 0.f;
       }
       for (int kb = kb0; kb < k_blocks; kb += 2) {
         const uint32_t my_it = it + kb;
@@ -302,11 +316,12 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         for (int i = 0; i + 1 < AM_AHEAD; ++i) am_ring[i] = am_ring[i + 1];
         {
           const int kbn = kb + 2 * AM_AHEAD;
-          am_ring[AM_AHEAD - 1] = (n_ok && kbn < k_blocks) ? __ldg(q.absmax + ((row_flat + (int64_t)kbn * BK) >> q.shift)) : 0.f;
+          am_ring[AM_AHEAD - 1] = (n_ok && kbn < k_blocks) ? __ldg(q.absmax + ((row_flat + (int64_t)kbn * kb_stride) >> q.shift)) : 0.f;
         }
         if (!mbar_wait(&ctl->qfull[s], ph, abort_flag, PW_FULL)) { ok = false; break; }
         uint8_t* st = smem + s * STAGE_BYTES;
-        const uint4* src = reinterpret_cast<const uint4*>(st + Q_OFF + row * (BK / 2));
+        // forward: 128 rows x 32 bytes; transposed: 64 rows x 64 bytes, this thread's half of its row
+        const uint4* src = reinterpret_cast<const uint4*>(st + Q_OFF + (W_T ? (row & 63) * 64 + (row >> 6) * 32 : row * (BK / 2)));
         const uint4 raw0 = src[0], raw1 = src[1];
         const uint32_t words[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
         uint8_t* dst_row = st + row * 128;

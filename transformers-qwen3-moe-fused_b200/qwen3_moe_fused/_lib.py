@@ -13,6 +13,7 @@ from pathlib import Path
 import torch
 
 F32, BF16, F16, I32, I64 = 0, 1, 2, 3, 4
+ERR_UNSUPPORTED = -5  # MOE_ERR_UNSUPPORTED: the selected kernel family does not cover the request
 PATH_AUTO, PATH_SIMT, PATH_TC, PATH_TC_SINGLE = 0, 1, 2, 3
 
 _FLOAT_CODES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
@@ -37,6 +38,7 @@ SIGNATURES = {
     "moe_grouped_gemm_dx": (_I, [_P, _P, _P, _I, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_grouped_gemm_dw": (_I, [_P, _P, _P, _I, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_grouped_gemm_fwd_nf4": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
+    "moe_grouped_gemm_dx_nf4": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_nf4_dequant": (_I, [_P, _P, _P, _I, _P, _L, _I, _P]),
     "moe_silu_mul_fwd": (_I, [_P, _P, _P, _L, _I, _P]),
     "moe_silu_mul_bwd": (_I, [_P, _P, _P, _P, _P, _L, _I, _P]),

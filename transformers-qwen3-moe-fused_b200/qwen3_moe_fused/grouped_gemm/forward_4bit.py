@@ -86,3 +86,49 @@ def grouped_gemm_forward_4bit(
         )
     _lib.check(status, "moe_grouped_gemm_fwd_nf4")
     return y
+
+
+def grouped_gemm_forward_transposed_4bit(
+    x: torch.Tensor,
+    w_quant: torch.Tensor,
+    w_quant_state,
+    m_sizes: torch.Tensor,
+    dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """dX through an NF4 weight: y[m, i] = sum_o w[e(m), o, i] * x[m, o] with the NF4 tensor of
+    logical shape (E, out, in) decoded inside the kernel; x (M, out), y (M, in).
+
+    The reference has no such kernel (its backward decodes the whole weight first,
+    qwen3_moe_fused/kernels/fast_lora.py:57-63,128); shapes the fused kernel does not cover
+    take that route here too: decode, then `grouped_gemm_forward_transposed`."""
+    assert w_quant_state.quant_type == "nf4"
+    blocksize = int(w_quant_state.blocksize)
+    w_code = w_quant_state.code
+    w_absmax = _unnest_absmax(w_quant_state)
+    assert x.is_cuda and x.is_contiguous() and x.ndim == 2
+    assert w_quant.is_contiguous() and w_code.is_contiguous() and w_absmax.is_contiguous() and m_sizes.is_contiguous()
+    assert is_int_tensor(w_quant) and is_int_tensor(m_sizes)
+    M, K = x.shape
+    E, k_w, N = w_quant_state.shape
+    assert k_w == K and m_sizes.numel() == E
+    assert w_quant.numel() * w_quant.element_size() == E * N * K // 2
+    if dtype is None:
+        dtype = x.dtype
+    y = torch.empty((M, N), device=x.device, dtype=dtype)
+    lib = _lib.load()
+    m_sizes = _lib.as_index_tensor(m_sizes)
+    ws_bytes = lib.moe_grouped_gemm_workspace_bytes(1, M, N, K, E)
+    ws = torch.empty(ws_bytes, device=x.device, dtype=torch.uint8) if ws_bytes else None
+    with torch.cuda.device(x.device):
+        status = lib.moe_grouped_gemm_dx_nf4(
+            _lib.ptr(x), _lib.ptr(w_quant), _lib.ptr(w_code), _lib.ptr(w_absmax), blocksize,
+            _lib.ptr(m_sizes), _lib.int_code(m_sizes.dtype), _lib.ptr(y), M, N, K, E,
+            _lib.float_code(x.dtype), _lib.float_code(dtype), _lib.ptr(ws), ws_bytes, _lib.stream_ptr(x.device),
+        )
+    if status == _lib.ERR_UNSUPPORTED:
+        from ..quantize.nf4 import dequantize_4bit
+        from .forward_transposed import grouped_gemm_forward_transposed
+
+        return grouped_gemm_forward_transposed(x, dequantize_4bit(w_quant, w_quant_state, x.dtype), m_sizes, dtype)
+    _lib.check(status, "moe_grouped_gemm_dx_nf4")
+    return y

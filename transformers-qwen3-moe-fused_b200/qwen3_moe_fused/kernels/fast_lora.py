@@ -18,7 +18,7 @@ import torch
 
 from ..grouped_gemm.backward_dw import grouped_gemm_backward_dw
 from ..grouped_gemm.forward import grouped_gemm_forward
-from ..grouped_gemm.forward_4bit import grouped_gemm_forward_4bit
+from ..grouped_gemm.forward_4bit import grouped_gemm_forward_4bit, grouped_gemm_forward_transposed_4bit
 from ..grouped_gemm.forward_transposed import grouped_gemm_forward_transposed
 from ..quantize.nf4 import dequantize_4bit
 from .silu_mul import silu_mul_backward_inplace, silu_mul_forward
@@ -72,6 +72,11 @@ class FastLora(torch.autograd.Function):
         def vm(_x, _w):  # rows times (E, k, n) weight read transposed
             return grouped_gemm_forward_transposed(_x, _w, m_sizes, dt)
 
+        def vm_base(_x, _wq, _wqs):  # the same through a base weight that may be NF4 (decoded inside the kernel)
+            if _wqs is None:
+                return vm(_x, _wq)
+            return grouped_gemm_forward_transposed_4bit(_x, _wq, _wqs, m_sizes, dt)
+
         def mv(_x, _w):
             return grouped_gemm_forward(_x, _w, m_sizes, dt)
 
@@ -80,7 +85,7 @@ class FastLora(torch.autograd.Function):
 
         # down projection
         dyB = vm(dy, Bw)  # (rows, r)
-        dh = vm(dy, _dense(Wq, Wqs, dt))
+        dh = vm_base(dy, Wq, Wqs)
         dh += vm(dyB, Aw) * Sw
         # dh, e, g become h, de, dg
         silu_mul_backward_inplace(dh, e, g)
@@ -100,9 +105,9 @@ class FastLora(torch.autograd.Function):
 
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = vm(de, _dense(Gq, Gqs, dt))
+            dx = vm_base(de, Gq, Gqs)
             dx += vm(deB, Ag) * Sg
-            dx += vm(dg, _dense(Uq, Uqs, dt))
+            dx += vm_base(dg, Uq, Uqs)
             dx += vm(dgB, Au) * Su
 
         return (dx, None, None, dAg, dBg, None, None, None, dAu, dBu, None, None, None, dAw, dBw, None, None)
