@@ -41,7 +41,7 @@ WORKLOADS = {
 # dram__bytes_read + dram__bytes_write over algorithmic bytes, from one ncu capture per kernel on the
 # reduced case (16384 rows, 32 experts; profiles/pair_kernels_gate_up_16k_rows.md).  Traffic grows in
 # proportion to rows and experts, so the ratio carries over to the full workload.
-NCU_TRAFFIC_RATIO = {"fwd": 0.95, "dx": 0.95, "dw": 0.85}
+NCU_TRAFFIC_RATIO = {"fwd": 0.95, "dx": 0.94, "dw": 0.83}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -456,8 +456,9 @@ def main():
     comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
     ev = lambda: torch.cuda.Event(enable_timing=True)
     kernel_ms = {"fwd": [], "dx": [], "dw": []}
-    # GEMMs, plus per step at N > 1: two row pushes (peer) or four row permutations (nccl)
-    launches_per_step = 3 if world == 1 else (5 if args.ep_transport == "peer" else 7)
+    # three GEMMs, each preceded by the kernel that builds its per-expert tensor maps; per step at
+    # N > 1 also two row pushes (peer) or four row permutations (nccl)
+    launches_per_step = 6 if world == 1 else (8 if args.ep_transport == "peer" else 10)
 
     def step_resident(record: bool):
         if world == 1:
@@ -682,7 +683,7 @@ def main():
             "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "tokens_per_s": T * world / (e2e_ms * 1e-3)},
-            "gpu_launches": args.steps * (1 if args.only else launches_per_step),
+            "gpu_launches": args.steps * (2 if args.only else launches_per_step),
             "tokens_per_s": T * world / (resident_ms * 1e-3),
             "clocks": clocks, "kernel_wait_errors": err_flag,
         }
