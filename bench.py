@@ -362,6 +362,10 @@ def main():
     ap.add_argument("--only", default=None, choices=["fwd", "dx", "dw"], help="run one of the three GEMMs per step")
     ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
                     help="N > 1: rows move by peer-memory stores fused with the GEMM epilogue (default) or by NCCL all-to-all")
+    ap.add_argument("--push-ctas", type=int, default=0,
+                    help="N > 1, peer transport: CTAs of the row push that overlaps a GEMM (0: four per SM)")
+    ap.add_argument("--ep-chunks", type=int, default=1,
+                    help="N > 1, peer transport: chunks of local experts whose exchange and GEMMs are pipelined")
     ap.add_argument("--gemm-path", default="auto", choices=["auto", "tc", "tc_single", "simt"],
                     help="kernel family for the grouped GEMMs (default: CTA-pair tcgen05 where eligible)")
     args = ap.parse_args()
@@ -444,12 +448,22 @@ def main():
     elif world > 1:
         from qwen3_moe_fused.parallel_ep import PeerChannel, PeerPlan, peer_fence, peer_grouped_gemm, peer_push
 
-        # receive buffers hold up to twice the even share of rows; results return into buffers of M rows
+        # The local experts are split into chunks with a plan and a buffer region each, so that the
+        # exchange of one chunk overlaps the GEMMs of another.  Receive buffers hold up to twice the
+        # even share of rows; results return into buffers of M rows.
+        n_chunks = max(1, min(args.ep_chunks, E_local))
+        bounds = [E_local * i // n_chunks for i in range(n_chunks + 1)]
+        counts_all = PeerPlan.gather_counts(m_sizes, world)
         cap = 2 * M
-        peer = {"plan": PeerPlan.build(m_sizes, world, rank), "x": PeerChannel(cap, K, bf, dev),
-                "dy": PeerChannel(cap, N, bf, dev), "y": PeerChannel(M, N, bf, dev), "dx": PeerChannel(M, K, bf, dev),
-                "token": torch.zeros(1, device=dev)}
-        assert int(peer["plan"].recv_rows) <= cap, "receive buffer too small for this routing"
+        region = cap // n_chunks // 8 * 8
+        ch_x, ch_dy = PeerChannel(cap, K, bf, dev), PeerChannel(cap, N, bf, dev)
+        peer = {"plans": [PeerPlan.from_counts(counts_all, world, rank, (bounds[i], bounds[i + 1])) for i in range(n_chunks)],
+                "x": [ch_x.rows(i * region, region) for i in range(n_chunks)],
+                "dy": [ch_dy.rows(i * region, region) for i in range(n_chunks)],
+                "w": [w[bounds[i]:bounds[i + 1]] for i in range(n_chunks)],
+                "y": PeerChannel(M, N, bf, dev), "dx": PeerChannel(M, K, bf, dev),
+                "x_all": ch_x, "dy_all": ch_dy, "token": torch.zeros(1, device=dev), "n": n_chunks}
+        assert all(int(pl.recv_rows) <= region for pl in peer["plans"]), "receive buffer too small for this routing"
         peer_fence(peer["token"])
     torch.cuda.synchronize()
 
@@ -458,7 +472,8 @@ def main():
     kernel_ms = {"fwd": [], "dx": [], "dw": []}
     # three GEMMs, each preceded by the kernel that builds its per-expert tensor maps; per step at
     # N > 1 also two row pushes (peer) or four row permutations (nccl)
-    launches_per_step = 6 if world == 1 else (8 if args.ep_transport == "peer" else 10)
+    nck = max(1, min(args.ep_chunks, E_local))
+    launches_per_step = 6 if world == 1 else (8 * nck if args.ep_transport == "peer" else 10)
 
     def step_resident(record: bool):
         if world == 1:
@@ -480,31 +495,37 @@ def main():
             # kernel (the second push overlaps the forward GEMM), the forward and dX epilogues store
             # their results straight into the source ranks' memory; a one-element all-reduce orders
             # each phase across the ranks.
-            #   comm:    push x | fence | push dy | fence
-            #   compute:                | forward           | dX | dW | fence
+            #   comm:    push dy | fence | push x | fence
+            #   compute:                 | dX              | forward | dW | fence
+            # (per chunk of local experts when --ep-chunks > 1; one chunk measured fastest)
             marks = [ev() for _ in range(4)]
             main = torch.cuda.current_stream()
-            e_x, e_dy = torch.cuda.Event(), torch.cuda.Event()
-            pl = peer["plan"]
+            nc = peer["n"]
+            e_x = [torch.cuda.Event() for _ in range(nc)]
+            e_dy = [torch.cuda.Event() for _ in range(nc)]
+            # dY (the smaller operand) goes first and dX runs first: the exposed first push is shorter
             comm_stream.wait_stream(main)
             with torch.cuda.stream(comm_stream):
-                peer_push(pl, x_d, peer["x"])
-                peer_fence(peer["token"])
-                e_x.record()
-                peer_push(pl, dy_d, peer["dy"])
-                peer_fence(peer["token"])
-                e_dy.record()
-            main.wait_event(e_x)
-            marks[0].record()
-            peer_grouped_gemm(pl, peer["x"], w, peer["y"])
-            marks[1].record()
-            main.wait_event(e_dy)
-            peer_grouped_gemm(pl, peer["dy"], w, peer["dx"], transposed=True)
+                for rows, chans, events, ctas in ((dy_d, peer["dy"], e_dy, 0), (x_d, peer["x"], e_x, args.push_ctas)):
+                    for i in range(nc):
+                        peer_push(peer["plans"][i], rows, chans[i], ctas)  # the second push runs beside a GEMM
+                        peer_fence(peer["token"])
+                        events[i].record()
+            for i in range(nc):
+                main.wait_event(e_dy[i])
+                if i == 0:
+                    marks[0].record()
+                peer_grouped_gemm(peer["plans"][i], peer["dy"][i], peer["w"][i], peer["dx"], transposed=True)
+            marks[1].record()  # marks 0-1: dX, 1-2: forward (including its wait for x), 2-3: dW
+            for i in range(nc):
+                main.wait_event(e_x[i])
+                peer_grouped_gemm(peer["plans"][i], peer["x"][i], peer["w"][i], peer["y"])
             marks[2].record()
-            dw = grouped_gemm_backward_dw(peer["x"].local, peer["dy"].local, pl.local_m_sizes, bf)
+            dw = [grouped_gemm_backward_dw(peer["x"][i].local, peer["dy"][i].local, peer["plans"][i].local_m_sizes, bf)
+                  for i in range(nc)]
             marks[3].record()
             peer_fence(peer["token"])  # results of every rank have arrived; buffers may be reused
-            return marks if record else None, (peer["y"].local, peer["dx"].local, dw)
+            return marks if record else None, (peer["y"].local, peer["dx"].local, dw[0])
         # expert parallel: rows to their experts, compute, results back.  The all-to-alls and
         # their permutation passes run on a second stream so that they overlap the GEMMs:
         #   comm:    dispatch x | dispatch dy |            combine y |           combine dx
@@ -560,20 +581,42 @@ def main():
     t_end.record()
     barrier()
     resident_ms = t_start.elapsed_time(t_end) / args.steps
+    first, second = ("dx", "fwd") if peer is not None else ("fwd", "dx")  # the peer schedule runs dX first
     for marks in all_marks:
-        kernel_ms["fwd"].append(marks[0].elapsed_time(marks[1]))
-        kernel_ms["dx"].append(marks[1].elapsed_time(marks[2]))
+        kernel_ms[first].append(marks[0].elapsed_time(marks[1]))
+        kernel_ms[second].append(marks[1].elapsed_time(marks[2]))
         kernel_ms["dw"].append(marks[2].elapsed_time(marks[3]))
 
     # ---- end to end through the public API, inputs in pinned host memory ----
     h2d = hidden_h.numel() * 2 + dy_h.numel() * 2 + (logits_h.numel() * 4 if logits_h is not None else ids_h.numel() * 8)
     d2h = 3 * 4 + E * 4
 
-    def step_e2e():
-        hd = hidden_h.to(dev, non_blocking=True)
-        dyd = dy_h.to(dev, non_blocking=True)
-        lg = logits_h.to(dev, non_blocking=True) if logits_h is not None else None
-        idd = ids_h.to(dev, non_blocking=True) if ids_h is not None else None
+    # Inputs are double-buffered on the device: the upload of step i+1 (copy stream) runs beside the
+    # compute of step i.  Every step's inputs still cross PCIe inside the timed region.
+    copy_stream = torch.cuda.Stream(device=dev)
+    slots = [{"hd": torch.empty_like(hidden_d), "dyd": torch.empty_like(dy_d),
+              "lg": torch.empty_like(logits_d) if logits_d is not None else None,
+              "idd": torch.empty_like(ids_d) if ids_d is not None else None,
+              "ready": torch.cuda.Event(), "free": torch.cuda.Event()} for _ in range(2)]
+
+    def upload(slot):
+        sl = slots[slot]
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(sl["free"])  # the step that last read this slot has finished
+            sl["hd"].copy_(hidden_h, non_blocking=True)
+            sl["dyd"].copy_(dy_h, non_blocking=True)
+            if sl["lg"] is not None:
+                sl["lg"].copy_(logits_h, non_blocking=True)
+            else:
+                sl["idd"].copy_(ids_h, non_blocking=True)
+            sl["ready"].record()
+
+    def step_e2e(i, last):
+        sl = slots[i % 2]
+        torch.cuda.current_stream().wait_event(sl["ready"])
+        if not last:
+            upload((i + 1) % 2)
+        hd, dyd, lg, idd = sl["hd"], sl["dyd"], sl["lg"], sl["idd"]
         ms, si, _ = route_and_sort(lg, idd)
         xs = _gather_rows(hd, si, k)
         if world == 1:
@@ -582,12 +625,13 @@ def main():
             dw = grouped_gemm_backward_dw(xs, dyd, ms, bf)
         elif peer is not None:
             pl = PeerPlan.build(ms, world, rank)
-            peer_push(pl, xs, peer["x"])
-            peer_push(pl, dyd, peer["dy"])
+            cx, cdy = peer["x_all"], peer["dy_all"]
+            peer_push(pl, xs, cx)
+            peer_push(pl, dyd, cdy)
             peer_fence(peer["token"])
-            peer_grouped_gemm(pl, peer["x"], w, peer["y"])
-            peer_grouped_gemm(pl, peer["dy"], w, peer["dx"], transposed=True)
-            dw = grouped_gemm_backward_dw(peer["x"].local, peer["dy"].local, pl.local_m_sizes, bf)
+            peer_grouped_gemm(pl, cx, w, peer["y"])
+            peer_grouped_gemm(pl, cdy, w, peer["dx"], transposed=True)
+            dw = grouped_gemm_backward_dw(cx.local, cdy.local, pl.local_m_sizes, bf)
             peer_fence(peer["token"])
             y, dx = peer["y"].local, peer["dx"].local
         else:
@@ -597,17 +641,20 @@ def main():
             dx = pl.combine(pl.grouped(grouped_gemm_forward_transposed, dyl, w))
             dw = pl.grouped_dw(grouped_gemm_backward_dw, xl, dyl, bf, E_local)
         stats = torch.stack([y[0].float().sum(), dx[0].float().sum(), dw[0, 0].float().sum()])
+        sl["free"].record()
         return stats.cpu(), ms.cpu()  # device -> host read of the step's result
 
     e2e_ms = float("nan")
     if not args.no_e2e:
-        for _ in range(3):
-            step_e2e()
+        upload(0)
+        for i in range(3):
+            step_e2e(i, i == 2)
         barrier()
         e0, e1 = ev(), ev()
         e0.record()
-        for _ in range(args.steps):
-            step_e2e()
+        upload(0)  # the first step's upload is inside the timed region too
+        for i in range(args.steps):
+            step_e2e(i, i == args.steps - 1)
         e1.record()
         barrier()
         e2e_ms = e0.elapsed_time(e1) / args.steps
@@ -628,7 +675,8 @@ def main():
         remote_bytes = (M - own) * K * 2
         if peer is not None:
             def exchange():
-                peer_push(peer["plan"], x_d, peer["x"])
+                for i in range(peer["n"]):
+                    peer_push(peer["plans"][i], x_d, peer["x"][i])
                 peer_fence(peer["token"])
         else:
             def exchange():
@@ -682,6 +730,7 @@ def main():
                          "algorithmic_bytes": alg_bytes},
             "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "note": "inputs double-buffered: the upload of step i+1 runs beside the compute of step i",
                     "tokens_per_s": T * world / (e2e_ms * 1e-3)},
             "gpu_launches": args.steps * (2 if args.only else launches_per_step),
             "tokens_per_s": T * world / (resident_ms * 1e-3),

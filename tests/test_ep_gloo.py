@@ -98,7 +98,12 @@ def _peer_worker(rank, world, port, E, rows_per_rank, H, out_dir):
         counts, inv_idx, _ = _cpu_sort(ids, E)
         x = torch.randn(rows_per_rank, H, generator=g)
         plan = PeerPlan.build(counts, world, rank)
-        torch.save({"xs": x[inv_idx.long()], "ids_sorted": ids[inv_idx.long()], "plan": plan.__dict__},
+        # the same exchange as two independent plans over halves of every rank's experts
+        all_counts = PeerPlan.gather_counts(counts, world)
+        half = E // world // 2
+        halves = [PeerPlan.from_counts(all_counts, world, rank, (0, half)).__dict__,
+                  PeerPlan.from_counts(all_counts, world, rank, (half, E // world)).__dict__] if half > 0 else []
+        torch.save({"xs": x[inv_idx.long()], "ids_sorted": ids[inv_idx.long()], "plan": plan.__dict__, "halves": halves},
                    os.path.join(out_dir, f"p{rank}.pt"))
     finally:
         dist.destroy_process_group()
@@ -142,5 +147,43 @@ def test_peer_plan_addresses(tmp_path, world):
             n, s = int(p["group_sizes"][gi]), int(p["group_src"][gi])
             back[s][int(p["return_row"][gi]):int(p["return_row"][gi]) + n] = recv[r][start:start + n]
             start += n
+    for s in range(world):
+        assert torch.equal(back[s], saved[s]["xs"])
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_peer_plan_sub_ranges(tmp_path, world):
+    """Two plans over disjoint halves of the local experts: each fills its own buffer from row 0
+    with its experts' rows only, and together they return every row to its place."""
+    E, rows, H = 16, 300, 3
+    mp.spawn(_peer_worker, args=(world, _free_port(), E, rows, H, str(tmp_path)), nprocs=world, join=True)
+    saved = [torch.load(tmp_path / f"p{r}.pt", weights_only=False) for r in range(world)]
+    e_local = E // world
+    half = e_local // 2
+    back = [torch.full((rows, H), float("nan")) for _ in range(world)]
+    for hi_, (lo, hi) in enumerate(((0, half), (half, e_local))):
+        recv = [torch.full((rows * world, H), float("nan")) for _ in range(world)]
+        for s in range(world):
+            p, xs = saved[s]["halves"][hi_], saved[s]["xs"]
+            begins = torch.cumsum(p["m_sizes"].long(), 0) - p["m_sizes"].long()
+            for e in range(E):
+                if not bool(p["send_mask"][e]):
+                    assert not (lo <= e % e_local < hi)
+                    continue
+                n, d = int(p["m_sizes"][e]), int(p["dst_rank"][e])
+                recv[d][int(p["send_row"][e]):int(p["send_row"][e]) + n] = xs[int(begins[e]):int(begins[e]) + n]
+        for r in range(world):
+            p = saved[r]["halves"][hi_]
+            chunks = [saved[(r + 1 + j) % world]["xs"][saved[(r + 1 + j) % world]["ids_sorted"] == e]
+                      for e in range(r * e_local + lo, r * e_local + hi) for j in range(world)]
+            expect = torch.cat(chunks)
+            assert int(p["recv_rows"]) == expect.shape[0] and p["expert_lo"] == lo
+            assert torch.equal(recv[r][:expect.shape[0]], expect)
+            assert p["weight_index"].tolist() == [g // world for g in range((hi - lo) * world)]
+            start = 0
+            for gi in range((hi - lo) * world):
+                n, s = int(p["group_sizes"][gi]), int(p["group_src"][gi])
+                back[s][int(p["return_row"][gi]):int(p["return_row"][gi]) + n] = recv[r][start:start + n]
+                start += n
     for s in range(world):
         assert torch.equal(back[s], saved[s]["xs"])

@@ -67,12 +67,12 @@ ep_push_rows_kernel(const uint4* __restrict__ rows, int64_t M, int row_vecs, con
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const int c = c0 + u * 32 + lane;
-        if (c < row_vecs) v[u] = __ldg(src + c);
+        if (c < row_vecs) v[u] = __ldcs(src + c);  // streaming: a GEMM running beside this kernel keeps its tiles in L2
       }
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const int c = c0 + u * 32 + lane;
-        if (c < row_vecs) dst[c] = v[u];
+        if (c < row_vecs) __stcs(dst + c, v[u]);
       }
     }
   }

@@ -14,7 +14,7 @@ weight lives on exactly one rank.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Callable, Optional
 
 import torch
@@ -125,24 +125,39 @@ class PeerPlan:
     return_row: torch.Tensor       # (G,) int64: first row of the group in its source rank's sorted order
     local_m_sizes: torch.Tensor    # (E_local,) int32: rows per local expert after dispatch
     recv_rows: torch.Tensor        # () int64: rows this rank receives in total
+    send_mask: Optional[torch.Tensor] = None  # (E,) bool: experts this plan moves (None: all)
+    expert_lo: int = 0             # first local expert of this plan (plans over a sub-range of the local experts)
+    cache: dict = field(default_factory=dict, repr=False)  # address tables per channel, built on first use
 
     @staticmethod
-    def build(m_sizes: torch.Tensor, world: int, rank: int, group=None) -> "PeerPlan":
+    def gather_counts(m_sizes: torch.Tensor, world: int, group=None) -> torch.Tensor:
+        """(world, E) int32: rows of every rank per global expert (one all-gather)."""
         E = m_sizes.numel()
         assert E % world == 0, "experts must divide evenly over the ranks"
-        e_local = E // world
         mine = m_sizes.to(torch.int32).contiguous()
         counts = torch.empty(world * E, dtype=torch.int32, device=mine.device)
         dist.all_gather_into_tensor(counts, mine, group=group)
-        return PeerPlan.from_counts(counts.view(world, E), world, rank)
+        return counts.view(world, E)
 
     @staticmethod
-    def from_counts(counts: torch.Tensor, world: int, rank: int) -> "PeerPlan":
-        """counts (world, E): rows of every rank per global expert."""
+    def build(m_sizes: torch.Tensor, world: int, rank: int, group=None) -> "PeerPlan":
+        return PeerPlan.from_counts(PeerPlan.gather_counts(m_sizes, world, group), world, rank)
+
+    @staticmethod
+    def from_counts(counts: torch.Tensor, world: int, rank: int, local_range: Optional[tuple] = None) -> "PeerPlan":
+        """counts (world, E): rows of every rank per global expert.
+
+        `local_range` = (lo, hi) restricts the plan to local experts lo..hi-1 of every rank: their
+        rows are laid out from row 0 of the (sub-)buffer they are pushed into, the groups are
+        those experts' only, and `weight_index` counts from expert lo.  Plans over disjoint ranges
+        are independent, so the exchange of one range can overlap the GEMMs of another."""
         E = counts.shape[1]
-        e_local = E // world
+        e_all = E // world
         dev = counts.device
-        c = counts.view(world, world, e_local).long()              # [source, owner, local expert]
+        lo, hi = local_range if local_range is not None else (0, e_all)
+        assert 0 <= lo < hi <= e_all
+        e_local = hi - lo
+        c = counts.view(world, world, e_all).long()[:, :, lo:hi]   # [source, owner, local expert of the range]
         # On owner d the sources of an expert are laid out d+1, d+2, ..., d (mod world): when every
         # rank walks its groups in order, the ranks' result stores go to distinct ranks at any one time.
         owners = torch.arange(world, device=dev)
@@ -152,20 +167,25 @@ class PeerPlan:
         flat = per_owner.view(world, e_local * world)
         first = flat.cumsum(dim=1) - flat                          # exclusive: first row of each group on its owner
         my_slot = (rank - owners - 1) % world                      # slot of this rank's rows on each owner
-        send_row = torch.gather(first.view(world, e_local, world), 2,
-                                my_slot.view(world, 1, 1).expand(world, e_local, 1)).reshape(E)
+        send_sub = torch.gather(first.view(world, e_local, world), 2,
+                                my_slot.view(world, 1, 1).expand(world, e_local, 1)).view(world, e_local)
+        send_row = torch.zeros((world, e_all), dtype=torch.int64, device=dev)
+        send_row[:, lo:hi] = send_sub
+        send_mask = torch.zeros((world, e_all), dtype=torch.bool, device=dev)
+        send_mask[:, lo:hi] = True
         begins = counts.long().cumsum(dim=1) - counts.long()       # [source, global expert]: first row in the source's order
         mine = per_owner[rank]                                     # [local expert, slot]
         g = torch.arange(e_local * world, device=dev)
         group_src = (rank + 1 + g % world) % world
-        group_expert = rank * e_local + g // world
+        group_expert = rank * e_all + lo + g // world
         return_row = begins[group_src, group_expert]
         return PeerPlan(
             world=world, rank=rank, e_local=e_local, m_sizes=counts[rank].contiguous(),
-            dst_rank=torch.arange(E, device=dev) // e_local, send_row=send_row.contiguous(),
+            dst_rank=torch.arange(E, device=dev) // e_all, send_row=send_row.reshape(E).contiguous(),
             group_sizes=mine.reshape(-1).to(torch.int32).contiguous(), weight_index=(g // world).to(torch.int32),
             group_src=group_src, return_row=return_row.contiguous(),
-            local_m_sizes=mine.sum(dim=1).to(torch.int32).contiguous(), recv_rows=mine.sum())
+            local_m_sizes=mine.sum(dim=1).to(torch.int32).contiguous(), recv_rows=mine.sum(),
+            send_mask=None if local_range is None else send_mask.reshape(E), expert_lo=lo)
 
 
 class PeerChannel:
@@ -186,6 +206,20 @@ class PeerChannel:
         self.row_bytes = width * self.local.element_size()
         self.ptrs = torch.tensor([int(p) for p in handle.buffer_ptrs], dtype=torch.int64, device=device)
         assert int(self.ptrs[dist.get_rank(group)]) == self.local.data_ptr()
+
+    def rows(self, first_row: int, n_rows: int) -> "PeerChannelRows":
+        """Rows first_row .. first_row + n_rows - 1 of the buffer on every rank, as a channel of their own."""
+        assert 0 <= first_row and first_row + n_rows <= self.capacity_rows
+        return PeerChannelRows(self.local[first_row:first_row + n_rows], self.ptrs + first_row * self.row_bytes,
+                               n_rows, self.row_bytes)
+
+
+@dataclass
+class PeerChannelRows:
+    local: torch.Tensor
+    ptrs: torch.Tensor
+    capacity_rows: int
+    row_bytes: int
 
 
 def peer_fence(token: torch.Tensor, group=None) -> None:
@@ -240,22 +274,31 @@ def scattered_grouped_gemm(x: torch.Tensor, weight: torch.Tensor, group_sizes: t
         _lib.ptr(out_ptrs), _lib.ptr(out_template), M, N, K, G, dt, dt, ws_ptr, ws_bytes, _lib.stream_ptr(x.device)), name)
 
 
-def peer_push(plan: PeerPlan, rows: torch.Tensor, channel: PeerChannel, max_ctas: int = 0) -> None:
+def peer_push(plan: PeerPlan, rows: torch.Tensor, channel, max_ctas: int = 0) -> None:
     """Rows sorted by global expert -> expert-major (local expert, source) order in the owners' `channel`."""
     row_bytes = rows.shape[1] * rows.element_size()
     assert row_bytes == channel.row_bytes
-    dst = (channel.ptrs[plan.dst_rank] + plan.send_row * row_bytes).contiguous()
-    # rows that would not fit into the owner's buffer are dropped, never written past its end
-    limit = (channel.capacity_rows - plan.send_row).clamp(min=0, max=2**31 - 1).to(torch.int32).contiguous()
+    key = ("push", channel.ptrs.data_ptr(), channel.capacity_rows)
+    if key not in plan.cache:
+        dst = (channel.ptrs[plan.dst_rank] + plan.send_row * row_bytes).contiguous()
+        # rows that would not fit into the owner's buffer are dropped, never written past its end
+        limit = (channel.capacity_rows - plan.send_row).clamp(min=0, max=2**31 - 1).to(torch.int32)
+        if plan.send_mask is not None:
+            limit = torch.where(plan.send_mask, limit, torch.zeros_like(limit))  # experts of other plans stay put
+        plan.cache[key] = (dst, limit.contiguous())
+    dst, limit = plan.cache[key]
     # every rank starts with the rows of the next rank's experts, so the ranks' writes fan out
     # over distinct destinations instead of converging on one receiver at a time
-    push_rows(rows, plan.m_sizes, dst, limit, max_ctas, first_expert=((plan.rank + 1) % plan.world) * plan.e_local)
+    e_all = plan.m_sizes.numel() // plan.world
+    push_rows(rows, plan.m_sizes, dst, limit, max_ctas, first_expert=((plan.rank + 1) % plan.world) * e_all)
 
 
-def peer_grouped_gemm(plan: PeerPlan, rows_in: PeerChannel, weight: torch.Tensor, rows_out: PeerChannel,
-                      transposed: bool = False) -> None:
+def peer_grouped_gemm(plan: PeerPlan, rows_in, weight: torch.Tensor, rows_out, transposed: bool = False) -> None:
     """Forward or dX over the rows received in `rows_in`; each (local expert, source) group's
-    results are stored into the source rank's `rows_out` at the rows' position in that rank's order."""
+    results are stored into the source rank's `rows_out` at the rows' position in that rank's order.
+    `weight` holds the plan's local experts only."""
     assert weight.shape[0] == plan.e_local
-    out_ptrs = (rows_out.ptrs[plan.group_src] + plan.return_row * rows_out.row_bytes).contiguous()
-    scattered_grouped_gemm(rows_in.local, weight, plan.group_sizes, plan.weight_index, out_ptrs, rows_out.local, transposed)
+    key = ("gemm", rows_out.ptrs.data_ptr(), rows_out.row_bytes)
+    if key not in plan.cache:
+        plan.cache[key] = (rows_out.ptrs[plan.group_src] + plan.return_row * rows_out.row_bytes).contiguous()
+    scattered_grouped_gemm(rows_in.local, weight, plan.group_sizes, plan.weight_index, plan.cache[key], rows_out.local, transposed)
