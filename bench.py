@@ -736,6 +736,9 @@ def main():
             "tokens_per_s": T * world / (resident_ms * 1e-3),
             "clocks": clocks, "kernel_wait_errors": err_flag,
         }
+        for name in per_kernel:  # spread over the timed steps (this rank), as the reference's do_bench quantiles
+            q = np.percentile(kernel_ms[name], [20, 50, 80])
+            line["kernels"][name].update(ms_p20=float(q[0]), ms_p50=float(q[1]), ms_p80=float(q[2]))
         for name, ms in burst_ms.items():
             line["kernels"][name].update(isolated_ms=ms, isolated_tflops=flops_one / (ms * 1e-3) / 1e12,
                                          isolated_frac_of_burst_peak=flops_one / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"])

@@ -207,11 +207,9 @@ nf4_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__
   __syncthreads();
   const int64_t ngroups = vec_ok ? n_elems / 8 : 0;
   const bool one_scale = bs_shift >= 3;  // the 8 elements of a group share one absmax block
-#pragma unroll 2
-  for (int64_t gi = (int64_t)blockIdx.x * EW_THREADS + threadIdx.x; gi < ngroups; gi += (int64_t)gridDim.x * EW_THREADS) {
-    const uint32_t raw = __ldg(reinterpret_cast<const uint32_t*>(packed) + gi);
+  const int64_t stride = (int64_t)gridDim.x * EW_THREADS;
+  auto decode_store = [&](int64_t gi, uint32_t raw, float a_all) {
     const int64_t base = gi * 8;
-    const float a_all = __ldg(absmax + (base >> bs_shift));
     T vals[8];
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
@@ -225,7 +223,22 @@ nf4_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__
 #pragma unroll
     for (int v = 0; v < NV; ++v)
       __stcs(reinterpret_cast<uint4*>(out + base) + v, reinterpret_cast<const uint4*>(vals)[v]);
+  };
+  int64_t gi = (int64_t)blockIdx.x * EW_THREADS + threadIdx.x;
+  // four groups per step: their loads are issued together
+  for (; gi + 3 * stride < ngroups; gi += 4 * stride) {
+    uint32_t raw[4];
+    float am[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      raw[u] = __ldcs(reinterpret_cast<const uint32_t*>(packed) + gi + u * stride);
+      am[u] = __ldg(absmax + (((gi + u * stride) * 8) >> bs_shift));
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) decode_store(gi + u * stride, raw[u], am[u]);
   }
+  for (; gi < ngroups; gi += stride)
+    decode_store(gi, __ldcs(reinterpret_cast<const uint32_t*>(packed) + gi), __ldg(absmax + ((gi * 8) >> bs_shift)));
   // scalar remainder (or everything when the buffers are not 16-byte aligned)
   const int64_t start = ngroups * 8;
   for (int64_t i = start + (int64_t)blockIdx.x * EW_THREADS + threadIdx.x; i < n_elems; i += (int64_t)gridDim.x * EW_THREADS) {
