@@ -343,6 +343,83 @@ def run_kernel_suite(args):
     assert _lib.read_error_flag() == 0
 
 
+def run_block_suite(args):
+    """Forward of one sparse MoE block over 16384 tokens in total (strong scaling: 16384 / N tokens and
+    128 / N experts per rank), tokens/s over all ranks.  N = 1: `moe_block_forward`; N > 1: `PeerMoeBlock`."""
+    import __graft_entry__ as entry
+
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    if rank == 0:
+        entry.build()
+    if world > 1:
+        dist.barrier()
+    from qwen3_moe_fused import _lib
+    from qwen3_moe_fused.moe_block import moe_block_forward
+
+    H, I, E, k = 2048, 768, 128, 8
+    weak = args.block_tokens_per_gpu is not None
+    T_total = args.block_tokens_per_gpu * world if weak else 16384
+    T, e_local = T_total // world, E // world
+    bf = torch.bfloat16
+    g0 = torch.Generator().manual_seed(5)
+    gate_w = (torch.randn(E, H, generator=g0) * 0.02).to(bf).to(dev)
+    g1 = torch.Generator().manual_seed(50 + rank)
+    mk = lambda *shape: (torch.randn(*shape, generator=g1) * 0.02).to(bf).to(dev)
+    gp, up, dp = mk(e_local, I, H), mk(e_local, I, H), mk(e_local, H, I)
+    hidden = torch.randn(T, H, generator=g1).to(bf).to(dev)
+    if world == 1:
+        def fn():
+            with torch.no_grad():
+                moe_block_forward(hidden.view(1, T, H), gate_w, gp, up, dp, k, True)
+    else:
+        from qwen3_moe_fused.parallel_ep import PeerMoeBlock
+
+        block = PeerMoeBlock(world, rank, dev, H, T * k, bf, capacity_factor=1.5)
+        block.forward(hidden, gate_w, gp, up, dp, k, True, check_capacity=True)
+
+        def fn():
+            block.forward(hidden, gate_w, gp, up, dp, k, True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        fn()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t)
+    err = _lib.read_error_flag()
+    if rank == 0:
+        flops = 2.0 * T_total * H * E + 3 * 2.0 * T_total * k * I * H
+        print(json.dumps({"suite": "block", "what": f"MoE block forward, {T_total} tokens in total, 128 experts, top-8, bf16",
+                          "n_gpus": world, "scaling": "weak" if weak else "strong", "steps": args.steps, "ms": ms,
+                          "tokens_per_s": T_total / ms * 1e3, "tokens_per_s_48_layers": T_total / ms * 1e3 / 48,
+                          "tflops": flops / ms / 1e9, "kernel_wait_errors": err,
+                          "transport": "single GPU" if world == 1 else "peer memory (push + down-projection epilogue stores to the token's rank)"}),
+              flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -352,8 +429,9 @@ def main():
     ap.add_argument("--workload", default="gate_up", choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-rows", type=int, default=4096, help="rows of the bounded CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--suite", default="hotpath", choices=["hotpath", "kernels"],
-                    help="hotpath: the contract line (default); kernels: roofline lines of the surrounding kernels")
+    ap.add_argument("--suite", default="hotpath", choices=["hotpath", "kernels", "block"],
+                    help="hotpath: the contract line (default); kernels: roofline lines of the surrounding kernels; "
+                         "block: MoE block forward, 16384 tokens over N GPUs")
     ap.add_argument("--hbm-only", action="store_true", help="kernel suite: only the HBM-bound kernels (profiling runs)")
     ap.add_argument("--kernel-iters", type=int, default=None, help="kernel suite: timed launches per kernel (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
@@ -362,6 +440,8 @@ def main():
     ap.add_argument("--only", default=None, choices=["fwd", "dx", "dw"], help="run one of the three GEMMs per step")
     ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
                     help="N > 1: rows move by peer-memory stores fused with the GEMM epilogue (default) or by NCCL all-to-all")
+    ap.add_argument("--block-tokens-per-gpu", type=int, default=None,
+                    help="block suite: tokens per GPU (weak scaling) instead of 16384 tokens in total")
     ap.add_argument("--push-ctas", type=int, default=0,
                     help="N > 1, peer transport: CTAs of the row push that overlaps a GEMM (0: four per SM)")
     ap.add_argument("--ep-chunks", type=int, default=1,
@@ -379,6 +459,9 @@ def main():
         return
     if args.suite == "kernels":
         run_kernel_suite(args)
+        return
+    if args.suite == "block":
+        run_block_suite(args)
         return
 
     import __graft_entry__ as entry

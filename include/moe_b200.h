@@ -211,6 +211,20 @@ int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, const void*
                      int m_sizes_dtype, int E, const uint64_t* dst_ptrs,
                      const int32_t* dst_limit, int first_expert, int max_ctas, void* stream);
 
+/* Row bookkeeping of one routing decision for the exchange above, in one launch.
+ * counts (world, E) int32 on the device: rows of every rank per global expert (expert e lives on
+ * rank e / (E / world)).  The plan covers local experts lo..hi-1 of every rank (0, E / world for
+ * all).  Outputs, all on the device: send_row[E] (first row, in the owner's buffer, of this
+ * rank's rows of expert e; 0 outside the range), send_ok[E] (1 inside the range), and for the
+ * G = (hi - lo) * world groups this rank receives, ordered (local expert, slot j) with slot j
+ * holding the rows of source rank (rank + 1 + j) % world: group_sizes[G], weight_index[G]
+ * (local expert minus lo), group_src[G], return_row[G] (first row of the group in its source
+ * rank's sorted order); local_m_sizes[hi - lo]; recv_rows[1]. */
+int moe_ep_plan(const int32_t* counts, int world, int rank, int E, int lo, int hi,
+                int64_t* send_row, int32_t* send_ok, int32_t* group_sizes, int32_t* weight_index,
+                int64_t* group_src, int64_t* return_row, int32_t* local_m_sizes,
+                int64_t* recv_rows, void* stream);
+
 /* moe_grouped_gemm_fwd / moe_grouped_gemm_dx over G groups where group g multiplies by
  * weight slice weight_index[g] (NULL: slice g) of n_weights, and its output rows are
  * written from the address out_ptrs[g] on (DEVICE array of G 64-bit addresses, 16-byte

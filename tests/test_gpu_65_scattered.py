@@ -100,3 +100,23 @@ def test_scattered_rejects_thin(dev):
     ptrs = torch.tensor([out.data_ptr(), out.data_ptr() + 32 * 128], device=dev)
     with pytest.raises(_lib.MoeB200Error):
         scattered_grouped_gemm(x, w, torch.tensor([32, 32], device=dev, dtype=torch.int32), None, ptrs, out)
+
+
+@pytest.mark.parametrize("world,E,rng_", [(2, 16, None), (4, 128, None), (8, 128, (4, 9)), (4, 32, (0, 3)), (1, 8, None)])
+def test_plan_kernel_matches_tensor_plan(dev, world, E, rng_):
+    """`moe_ep_plan` (one launch) against the same plan computed with tensor operations on the host."""
+    from qwen3_moe_fused.parallel_ep import PeerPlan
+
+    g = torch.Generator().manual_seed(world * 1000 + E)
+    counts = torch.randint(0, 700, (world, E), generator=g, dtype=torch.int32)
+    counts[counts % 7 == 0] = 0
+    for rank in range(world):
+        a = PeerPlan.from_counts(counts.to(dev), world, rank, rng_)
+        b = PeerPlan.from_counts(counts, world, rank, rng_)
+        for f in ("m_sizes", "dst_rank", "send_row", "group_sizes", "weight_index", "group_src", "return_row", "local_m_sizes"):
+            assert torch.equal(getattr(a, f).cpu().long(), getattr(b, f).long()), f"{f} rank {rank}"
+        assert int(a.recv_rows) == int(b.recv_rows) and a.expert_lo == b.expert_lo and a.e_local == b.e_local
+        if rng_ is None:
+            assert a.send_mask is None and b.send_mask is None
+        else:
+            assert torch.equal(a.send_mask.cpu(), b.send_mask)

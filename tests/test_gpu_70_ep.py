@@ -178,3 +178,54 @@ def test_peer_memory_expert_parallel_matches_single_gpu(tmp_path):
             ref = dys[sel].T @ xs[sel]
             got = saved[r]["dw"][le].float().numpy()
             assert O.rel_err(got, ref) < 1e-2 if sel.any() else not got.any(), f"dW of expert {e}"
+
+
+def _block_worker(rank, world, port, out_dir):
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    for p in (str(root), str(root / "transformers-qwen3-moe-fused_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from qwen3_moe_fused import _lib
+        from qwen3_moe_fused.moe_block import moe_block_forward
+        from qwen3_moe_fused.parallel_ep import PeerMoeBlock
+
+        E, H, I, T, k = 16, 256, 192, 1000, 4
+        bf = torch.bfloat16
+        e_local = E // world
+        gw = torch.Generator().manual_seed(11)
+        mk = lambda *shape, sc: (torch.randn(*shape, generator=gw) * sc).to(bf).to(dev)
+        gate_w, gate_p, up_p, down_p = mk(E, H, sc=0.05), mk(E, I, H, sc=0.05), mk(E, I, H, sc=0.05), mk(E, H, I, sc=0.05)
+        x = torch.randn(T, H, generator=torch.Generator().manual_seed(200 + rank)).to(bf).to(dev)
+        lo, hi = rank * e_local, (rank + 1) * e_local
+        block = PeerMoeBlock(world, rank, dev, H, T * k, bf, capacity_factor=2.0)
+        for _ in range(2):  # the second call reuses the buffers
+            out, logits = block.forward(x, gate_w, gate_p[lo:hi].contiguous(), up_p[lo:hi].contiguous(),
+                                        down_p[lo:hi].contiguous(), k, True)
+        torch.cuda.synchronize()
+        assert _lib.read_error_flag() == 0
+        with torch.no_grad():
+            ref, ref_logits = moe_block_forward(x.view(1, T, H), gate_w, gate_p, up_p, down_p, k, True)
+        err = float((out.float() - ref.view(T, H).float()).abs().max() / ref.float().abs().max())
+        assert torch.equal(logits, ref_logits) and err < 1e-2, f"rank {rank}: block mismatch {err}"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_memory_block_forward_matches_single_gpu(tmp_path):
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    mp.spawn(_block_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)

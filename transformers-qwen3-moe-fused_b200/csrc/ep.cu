@@ -78,9 +78,84 @@ ep_push_rows_kernel(const uint4* __restrict__ rows, int64_t M, int row_vecs, con
   }
 }
 
+// Row bookkeeping of one routing decision for the peer-memory exchange, in one launch.
+// counts[s][e]: rows of source rank s for global expert e.  Expert e = d * e_all + el lives on
+// rank d.  The plan covers local experts lo..hi-1 of every rank.  On owner d the groups are laid
+// out (local expert, slot j) with slot j holding the rows of source (d + 1 + j) % world.
+constexpr int PLAN_MAX_WORLD = 16;
+constexpr int PLAN_MAX_E = 1024;
+
+__global__ void __launch_bounds__(256)
+ep_plan_kernel(const int32_t* __restrict__ counts, int world, int rank, int E, int lo, int hi,
+               int64_t* __restrict__ send_row, int32_t* __restrict__ send_ok, int32_t* __restrict__ group_sizes,
+               int32_t* __restrict__ weight_index, int64_t* __restrict__ group_src, int64_t* __restrict__ return_row,
+               int32_t* __restrict__ local_m_sizes, int64_t* __restrict__ recv_rows) {
+  extern __shared__ int32_t plan_smem[];
+  int32_t* cnt = plan_smem;                // [world][E]
+  int32_t* begins = cnt + world * E;       // [world][E]: first row of expert e in source s's sorted order
+  int32_t* first = begins + world * E;     // [world][n_local * world]: first row of each group on its owner
+  const int e_all = E / world;
+  const int n_local = hi - lo;
+  const int G = n_local * world;
+  for (int i = threadIdx.x; i < world * E; i += blockDim.x) cnt[i] = counts[i];
+  __syncthreads();
+  if ((int)threadIdx.x < world) {
+    const int s = threadIdx.x;
+    int run = 0;
+    for (int e = 0; e < E; ++e) { begins[s * E + e] = run; run += cnt[s * E + e]; }
+  } else if ((int)threadIdx.x >= 32 && (int)threadIdx.x < 32 + world) {
+    const int d = threadIdx.x - 32;
+    int run = 0;
+    for (int g = 0; g < G; ++g) {
+      const int el = g / world, j = g % world;
+      first[d * G + g] = run;
+      run += cnt[((d + 1 + j) % world) * E + d * e_all + lo + el];
+    }
+    if (d == rank) *recv_rows = run;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int d = e / e_all, el = e % e_all;
+    const bool in = el >= lo && el < hi;
+    const int slot = ((rank - d - 1) % world + world) % world;
+    send_row[e] = in ? first[d * G + (el - lo) * world + slot] : 0;
+    send_ok[e] = in ? 1 : 0;
+  }
+  for (int g = threadIdx.x; g < G; g += blockDim.x) {
+    const int el = g / world, j = g % world;
+    const int src = (rank + 1 + j) % world;
+    const int e = rank * e_all + lo + el;
+    group_sizes[g] = cnt[src * E + e];
+    weight_index[g] = el;
+    group_src[g] = src;
+    return_row[g] = begins[src * E + e];
+  }
+  for (int el = threadIdx.x; el < n_local; el += blockDim.x) {
+    int sum = 0;
+    for (int s = 0; s < world; ++s) sum += cnt[s * E + rank * e_all + lo + el];
+    local_m_sizes[el] = sum;
+  }
+}
+
 }  // namespace moe
 
 using namespace moe;
+
+MOE_API int moe_ep_plan(const int32_t* counts, int world, int rank, int E, int lo, int hi, int64_t* send_row,
+                        int32_t* send_ok, int32_t* group_sizes, int32_t* weight_index, int64_t* group_src,
+                        int64_t* return_row, int32_t* local_m_sizes, int64_t* recv_rows, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (world <= 0 || world > PLAN_MAX_WORLD || E <= 0 || E > PLAN_MAX_E || (E % world) != 0) return MOE_ERR_SHAPE;
+  if (rank < 0 || rank >= world || lo < 0 || hi <= lo || hi > E / world) return MOE_ERR_SHAPE;
+  if (!counts || !send_row || !send_ok || !group_sizes || !weight_index || !group_src || !return_row ||
+      !local_m_sizes || !recv_rows)
+    return MOE_ERR_NULL;
+  const size_t smem = (size_t)(2 * world * E + world * (hi - lo) * world) * sizeof(int32_t);
+  if (smem > 48 * 1024) return MOE_ERR_SHAPE;
+  ep_plan_kernel<<<1, 256, smem, stream>>>(counts, world, rank, E, lo, hi, send_row, send_ok, group_sizes, weight_index,
+                                           group_src, return_row, local_m_sizes, recv_rows);
+  return launch_status();
+}
 
 MOE_API int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, const void* m_sizes, int m_sizes_dtype,
                              int E, const uint64_t* dst_ptrs, const int32_t* dst_limit, int first_expert,

@@ -105,6 +105,17 @@ class ExpertParallelPlan:
 # rank's memory, at the position the rows had there.  One small count all-gather per routing
 # decision and one fence per phase are the only collectives.
 # ------------------------------------------------------------------------------------------
+_DST_RANK_TABLES: dict = {}
+
+
+def _dst_rank_table(E: int, e_all: int, dev) -> torch.Tensor:
+    """Owner of every global expert (a constant of the configuration, built once per device)."""
+    key = (E, e_all, str(dev))
+    if key not in _DST_RANK_TABLES:
+        _DST_RANK_TABLES[key] = torch.arange(E, device=dev) // e_all
+    return _DST_RANK_TABLES[key]
+
+
 @dataclass
 class PeerPlan:
     """Row bookkeeping of one routing decision, all tensors on the device, no host sync.
@@ -157,6 +168,26 @@ class PeerPlan:
         lo, hi = local_range if local_range is not None else (0, e_all)
         assert 0 <= lo < hi <= e_all
         e_local = hi - lo
+        if counts.is_cuda:
+            # one kernel instead of two dozen small tensor operations
+            from . import _lib
+
+            counts = counts.to(torch.int32).contiguous()
+            G = e_local * world
+            i64 = torch.empty(E + 2 * G + 1, dtype=torch.int64, device=dev)
+            i32 = torch.empty(E + 2 * G + e_local, dtype=torch.int32, device=dev)
+            send_row, group_src, return_row, recv_rows = i64[:E], i64[E:E + G], i64[E + G:E + 2 * G], i64[E + 2 * G:]
+            send_ok, group_sizes, weight_index, local_m = i32[:E], i32[E:E + G], i32[E + G:E + 2 * G], i32[E + 2 * G:]
+            with torch.cuda.device(dev):
+                _lib.check(_lib.load().moe_ep_plan(
+                    _lib.ptr(counts), world, rank, E, lo, hi, _lib.ptr(send_row), _lib.ptr(send_ok), _lib.ptr(group_sizes),
+                    _lib.ptr(weight_index), _lib.ptr(group_src), _lib.ptr(return_row), _lib.ptr(local_m), _lib.ptr(recv_rows),
+                    _lib.stream_ptr(dev)), "moe_ep_plan")
+            return PeerPlan(
+                world=world, rank=rank, e_local=e_local, m_sizes=counts[rank], dst_rank=_dst_rank_table(E, e_all, dev),
+                send_row=send_row, group_sizes=group_sizes, weight_index=weight_index, group_src=group_src,
+                return_row=return_row, local_m_sizes=local_m, recv_rows=recv_rows[0],
+                send_mask=None if local_range is None else send_ok.bool(), expert_lo=lo)
         c = counts.view(world, world, e_all).long()[:, :, lo:hi]   # [source, owner, local expert of the range]
         # On owner d the sources of an expert are laid out d+1, d+2, ..., d (mod world): when every
         # rank walks its groups in order, the ranks' result stores go to distinct ranks at any one time.
@@ -302,3 +333,57 @@ def peer_grouped_gemm(plan: PeerPlan, rows_in, weight: torch.Tensor, rows_out, t
     if key not in plan.cache:
         plan.cache[key] = (rows_out.ptrs[plan.group_src] + plan.return_row * rows_out.row_bytes).contiguous()
     scattered_grouped_gemm(rows_in.local, weight, plan.group_sizes, plan.weight_index, plan.cache[key], rows_out.local, transposed)
+
+
+class PeerMoeBlock:
+    """Forward of the sparse MoE block with the experts split over the ranks (inference; no autograd).
+
+    What `moe_block.moe_block_forward` computes for this rank's tokens, with the rows of every
+    token sent to the ranks that own its experts: router, sort and expand run locally; the rows are
+    pushed into the owners' buffers; gate / up / SiLU-mul run on the owners; the down projection's
+    epilogue stores every result row straight back into the token's rank, where the weighted
+    combine runs.  Two fences per call, no all-to-all.
+    """
+
+    def __init__(self, world: int, rank: int, device, hidden: int, max_rows: int, dtype: torch.dtype,
+                 capacity_factor: float = 1.5, group=None):
+        """max_rows: tokens * top_k per rank; a rank can receive up to capacity_factor * max_rows rows."""
+        self.world, self.rank, self.group = world, rank, group
+        cap = (int(max_rows * capacity_factor) + 7) // 8 * 8
+        self.ch_x = PeerChannel(cap, hidden, dtype, device, group)
+        self.ch_y = PeerChannel(max_rows, hidden, dtype, device, group)
+        self.token = torch.zeros(1, device=device)
+        peer_fence(self.token, group)
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, gate_weight: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor,
+                down_proj: torch.Tensor, num_selected: int, norm_topk_prob: bool = True, check_capacity: bool = False):
+        """x (T, H): this rank's tokens; gate_weight (E, H) on every rank; gate_proj / up_proj (E_local, I, H) and
+        down_proj (E_local, H, I): this rank's experts.  Returns (out (T, H), router_logits (T, E))."""
+        from .grouped_gemm.forward import grouped_gemm_forward
+        from .kernels.indexing import get_expert_counts_and_idx
+        from .kernels.routing import _combine, _expand_rows, softmax_topk
+        from .kernels.silu_mul import silu_mul_forward
+
+        T, H = x.shape
+        E, k = gate_weight.shape[0], num_selected
+        assert T * k <= self.ch_y.capacity_rows
+        x = x.contiguous()
+        router_logits = torch.nn.functional.linear(x, gate_weight)
+        weights, selected = softmax_topk(router_logits, k, norm_topk_prob, x.dtype)
+        m_sizes, _, inv_sort_idx = get_expert_counts_and_idx(selected.view(T * k), E)
+        xs = _expand_rows(x, inv_sort_idx, k)
+        plan = PeerPlan.build(m_sizes, self.world, self.rank, self.group)
+        if check_capacity:  # one host read; rows beyond the buffer would be dropped, not written out of bounds
+            assert int(plan.recv_rows) <= self.ch_x.capacity_rows, "receive buffer too small for this routing"
+        peer_push(plan, xs, self.ch_x)
+        peer_fence(self.token, self.group)  # every rank's rows have arrived (and the previous call's reads are over)
+        rows = self.ch_x.local
+        gate_h = grouped_gemm_forward(rows, gate_proj, plan.local_m_sizes)
+        up_h = grouped_gemm_forward(rows, up_proj, plan.local_m_sizes)
+        h = silu_mul_forward(gate_h, up_h)
+        out_ptrs = (self.ch_y.ptrs[plan.group_src] + plan.return_row * self.ch_y.row_bytes).contiguous()
+        scattered_grouped_gemm(h, down_proj, plan.group_sizes, plan.weight_index, out_ptrs, self.ch_y.local)
+        peer_fence(self.token, self.group)  # every rank's results have arrived
+        out = _combine(self.ch_y.local[:T * k], inv_sort_idx, weights)
+        return out, router_logits
