@@ -272,7 +272,7 @@ def run_kernel_suite(args):
     emit("combine bf16 16384 tokens x8 x2048", time_cuda(lambda: _combine(y, inv_sort_idx, w), inner=5), 2 * (T * k * H + T * H) + 6 * T * k)
     del hidden, y
 
-    # ---- NF4: decode alone, fused forward vs decode + GEMM (BASELINE config 4) ----
+    # ---- NF4: decode alone, fused forward vs decode + GEMM (128 experts, 1536 x 2048, blocksize 64, three batch sizes) ----
     E, N, K = 128, 1536, 2048
     wfull = (torch.randn(E, N, K, device=dev) * 0.02).to(bf)
     packed, state = quantize_nf4(wfull, 64)

@@ -31,7 +31,7 @@ def main(ref_root: str) -> None:
 
     # ---- indexing ----
     cases = {
-        "c1": (256, 8, 0),          # BASELINE config 1
+        "c1": (256, 8, 0),          # the small fp32 case
         "ragged": (1000, 11, 1),    # E = 11 as in the reference's tiny model
         "empty_groups": (300, 16, 2),
         "single": (1, 4, 3),
@@ -54,7 +54,7 @@ def main(ref_root: str) -> None:
 
     # ---- moe_fused_linear fwd / dX / dW ----
     lin_cases = {
-        "c1": (256, 64, 128, 8, 0),      # BASELINE config 1: E=8, in=64, out=128, B=256
+        "c1": (256, 64, 128, 8, 0),      # the small fp32 case: E=8, in=64, out=128, B=256
         "odd": (37, 3, 4, 11, 1),        # K=3, N=4, E=11: the reference's tiny-model shapes
         "empty": (96, 16, 24, 6, 2),
     }

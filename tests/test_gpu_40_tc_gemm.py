@@ -34,7 +34,7 @@ def tensors(cuda, rng, M, K, N, E, dtype, empty=0.0, m_sizes=None):
 
 SHAPES = [
     # M, K(in), N(out), E, empty fraction
-    (256, 64, 128, 8, 0.0),        # BASELINE config 1 shape (here in bf16)
+    (256, 64, 128, 8, 0.0),        # shape of the small fp32 case (here in bf16)
     (1024, 2048, 768, 128, 0.0),   # the reference's kernel test shape
     (1000, 192, 320, 7, 0.3),      # ragged, K and N not multiples of the tile
     (4096, 768, 2048, 16, 0.0),    # down_proj shape, few experts
