@@ -287,10 +287,12 @@ def run_kernel_suite(args):
         x = torch.randn(M, K, device=dev, dtype=bf)
         m_sizes = torch.full((E,), M // E, device=dev, dtype=torch.int32)
         flops = 2.0 * M * N * K
-        fused = time_cuda(lambda: grouped_gemm_forward_4bit(x, packed, state, m_sizes), iters=10)
+        fused = time_cuda(lambda: grouped_gemm_forward_4bit(x, packed, state, m_sizes, fused=True), iters=10)
         unfused = time_cuda(lambda: grouped_gemm_forward(x, dequantize_4bit(packed, state, bf), m_sizes), iters=10)
+        auto = time_cuda(lambda: grouped_gemm_forward_4bit(x, packed, state, m_sizes), iters=10)
         wbytes = nel // 2 + nel // 64 * 4
-        emit(f"nf4 fused forward M={M}", fused, wbytes + 2 * M * (K + N), flops, unfused_ms=unfused, speedup_vs_unfused=unfused / fused)
+        emit(f"nf4 fused forward M={M}", fused, wbytes + 2 * M * (K + N), flops, unfused_ms=unfused, speedup_vs_unfused=unfused / fused,
+             public_api_ms=auto, public_api_note="grouped_gemm_forward_4bit picks decode-inside or decode-once by rows per expert")
         del x
     # ---- fused-LoRA expert MLP, rank 16, NF4 base, forward + backward ----
     I, Hh, R = 768, 2048, 16

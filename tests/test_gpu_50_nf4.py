@@ -39,7 +39,7 @@ def test_fused_forward(cuda, path, dtype, M, K, N, E, bs, empty):
     x, packed, state, m_sizes, ref = make(cuda, rng, M, K, N, E, bs, dtype, empty)
     prev = _lib.set_gemm_path(_lib.PATH_SIMT if path == "simt" else _lib.PATH_TC)
     try:
-        y = grouped_gemm_forward_4bit(to_dev(x, dtype, cuda), packed, state, torch.from_numpy(m_sizes).to(cuda))
+        y = grouped_gemm_forward_4bit(to_dev(x, dtype, cuda), packed, state, torch.from_numpy(m_sizes).to(cuda), fused=True)
         torch.cuda.synchronize()
     finally:
         _lib.set_gemm_path(prev)

@@ -30,13 +30,24 @@ def _unnest_absmax(state) -> torch.Tensor:
     return absmax
 
 
+# Rows per expert (on average) from which decoding the whole weight once and running the dense
+# kernel is faster than decoding tiles inside the GEMM: the fused kernel decodes a weight tile
+# once per 256-token tile, so its decode work grows with the rows, while the one-off decode costs
+# about 0.2 ms per 800 MB of 16-bit weight.  Measured crossover on B200 at (128, 1536, 2048):
+# about 1400 rows per expert.
+DECODE_ONCE_ROWS_PER_EXPERT = 1400
+
+
 def grouped_gemm_forward_4bit(
     x: torch.Tensor,
     w_quant: torch.Tensor,
     w_quant_state,
     m_sizes: torch.Tensor,
     dtype: Optional[torch.dtype] = None,
+    fused: Optional[bool] = None,
 ) -> torch.Tensor:
+    """`fused`: True = decode inside the GEMM, False = decode the whole weight, then the dense
+    kernel; None = by the number of rows per expert (see DECODE_ONCE_ROWS_PER_EXPERT)."""
     assert w_quant_state.quant_type == "nf4"
     blocksize = int(w_quant_state.blocksize)
     assert blocksize > 0 and blocksize & (blocksize - 1) == 0
@@ -73,6 +84,13 @@ def grouped_gemm_forward_4bit(
 
     if dtype is None:
         dtype = x.dtype
+    if fused is None:
+        fused = M < DECODE_ONCE_ROWS_PER_EXPERT * E or x.dtype == torch.float32
+    if not fused:
+        from ..quantize.nf4 import dequantize_4bit
+        from .forward import grouped_gemm_forward
+
+        return grouped_gemm_forward(x, dequantize_4bit(w_quant, w_quant_state, x.dtype), m_sizes, dtype)
     y = torch.empty((M, N), device=x.device, dtype=dtype)
     lib = _lib.load()
     m_sizes = _lib.as_index_tensor(m_sizes)
