@@ -206,10 +206,13 @@ int moe_combine(const void* y, const int32_t* inv_sort_idx, const void* weights,
  * mapped into this process; the stores are plain global stores.  The call neither waits
  * for nor signals the receiver.  Rows are visited starting with expert first_expert and
  * wrapping around (ranks that start at different experts do not all write to the same
- * destination at once).  max_ctas <= 0 picks a grid from the SM count. */
+ * destination at once).  With src_index (M int32, may be NULL) sorted row r is read from row
+ * src_index[r] / src_div of `rows`: passing the sort's gather index and k pushes token rows
+ * without expanding them first.  max_ctas <= 0 picks a grid from the SM count. */
 int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, const void* m_sizes,
                      int m_sizes_dtype, int E, const uint64_t* dst_ptrs,
-                     const int32_t* dst_limit, int first_expert, int max_ctas, void* stream);
+                     const int32_t* dst_limit, int first_expert, const int32_t* src_index,
+                     int src_div, int max_ctas, void* stream);
 
 /* Row bookkeeping of one routing decision for the exchange above, in one launch.
  * counts (world, E) int32 on the device: rows of every rank per global expert (expert e lives on

@@ -90,6 +90,24 @@ def test_scattered_gemm(dev, transposed, dtype, E_w, world, M, N, K):
         assert bool((bufs[b][fill[b]:] == 7.0).all()), "rows outside the groups were written"
 
 
+def test_push_rows_expands_tokens(dev):
+    """With the sort's gather index the push reads token rows and delivers the expanded rows."""
+    from oracle import moe_oracle as O
+    from qwen3_moe_fused.parallel_ep import push_rows
+
+    rng = np.random.default_rng(9)
+    T, k, E, W = 300, 4, 12, 256
+    sel = rng.integers(0, E, T * k)
+    counts, sort_idx, _ = O.get_expert_counts_and_idx_fast(sel, E)
+    tokens = torch.randn(T, W, device=dev).to(torch.bfloat16)
+    out = torch.zeros(T * k, W, device=dev, dtype=torch.bfloat16)
+    begins = np.concatenate([[0], np.cumsum(counts)])[:-1]
+    ptrs = torch.from_numpy(out.data_ptr() + begins.astype(np.int64) * W * 2).to(dev)
+    push_rows(tokens, torch.from_numpy(counts).to(dev), ptrs, None, src_index=torch.from_numpy(sort_idx).to(dev), src_div=k)
+    torch.cuda.synchronize()
+    assert torch.equal(out, tokens[torch.from_numpy(sort_idx).to(dev).long() // k])
+
+
 def test_scattered_rejects_thin(dev):
     from qwen3_moe_fused import _lib
     from qwen3_moe_fused.parallel_ep import scattered_grouped_gemm

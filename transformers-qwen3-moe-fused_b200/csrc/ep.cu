@@ -40,7 +40,8 @@ __device__ __forceinline__ void push_build_begins(const void* m_sizes, int ms64,
 template <int UNROLL>
 __global__ void __launch_bounds__(PUSH_THREADS)
 ep_push_rows_kernel(const uint4* __restrict__ rows, int64_t M, int row_vecs, const void* __restrict__ m_sizes, int ms64,
-                    int E, const uint64_t* __restrict__ dst_ptrs, const int32_t* __restrict__ dst_limit, int first_expert) {
+                    int E, const uint64_t* __restrict__ dst_ptrs, const int32_t* __restrict__ dst_limit, int first_expert,
+                    const int32_t* __restrict__ src_index, int src_div) {
   __shared__ int begins[PUSH_MAX_E + 1];
   push_build_begins(m_sizes, ms64, E, begins);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -60,14 +61,15 @@ ep_push_rows_kernel(const uint4* __restrict__ rows, int64_t M, int row_vecs, con
     const int e = lo;
     const int local = (int)r - begins[e];
     if (dst_limit != nullptr && local >= dst_limit[e]) continue;  // would overrun the receiver's buffer
-    const uint4* src = rows + r * row_vecs;
+    // with a source index, sorted row r is row src_index[r] / src_div of `rows` (token rows expanded on the fly)
+    const uint4* src = rows + (src_index ? (int64_t)(src_index[r] / src_div) : r) * row_vecs;
     uint4* dst = reinterpret_cast<uint4*>(dst_ptrs[e]) + (int64_t)local * row_vecs;
     for (int c0 = 0; c0 < row_vecs; c0 += 32 * UNROLL) {
       uint4 v[UNROLL];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const int c = c0 + u * 32 + lane;
-        if (c < row_vecs) v[u] = __ldcs(src + c);  // streaming: a GEMM running beside this kernel keeps its tiles in L2
+        if (c < row_vecs) v[u] = src_index ? __ldg(src + c) : __ldcs(src + c);  // plain rows are read once: streaming
       }
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
@@ -159,11 +161,11 @@ MOE_API int moe_ep_plan(const int32_t* counts, int world, int rank, int E, int l
 
 MOE_API int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, const void* m_sizes, int m_sizes_dtype,
                              int E, const uint64_t* dst_ptrs, const int32_t* dst_limit, int first_expert,
-                             int max_ctas, void* stream_) {
+                             const int32_t* src_index, int src_div, int max_ctas, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (!is_int_dtype(m_sizes_dtype)) return MOE_ERR_DTYPE;
   if (M < 0 || row_bytes < 0 || E <= 0 || E > PUSH_MAX_E || M > 0x7fffffffLL) return MOE_ERR_SHAPE;
-  if (first_expert < 0 || first_expert >= E) return MOE_ERR_SHAPE;
+  if (first_expert < 0 || first_expert >= E || (src_index != nullptr && src_div <= 0)) return MOE_ERR_SHAPE;
   if (M == 0 || row_bytes == 0) return MOE_OK;
   if (!rows || !m_sizes || !dst_ptrs) return MOE_ERR_NULL;
   if ((row_bytes & 15) || ((uintptr_t)rows & 15)) return MOE_ERR_ALIGN;
@@ -172,6 +174,7 @@ MOE_API int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, con
   const int64_t cap = max_ctas > 0 ? max_ctas : (int64_t)sm_count() * 4;
   if (grid > cap) grid = cap;
   ep_push_rows_kernel<8><<<(int)grid, PUSH_THREADS, 0, stream>>>(
-      reinterpret_cast<const uint4*>(rows), M, (int)(row_bytes / 16), m_sizes, m_sizes_dtype == MOE_I64, E, dst_ptrs, dst_limit, first_expert);
+      reinterpret_cast<const uint4*>(rows), M, (int)(row_bytes / 16), m_sizes, m_sizes_dtype == MOE_I64, E, dst_ptrs, dst_limit, first_expert,
+      src_index, src_div);
   return launch_status();
 }

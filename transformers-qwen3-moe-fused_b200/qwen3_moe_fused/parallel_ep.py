@@ -260,10 +260,13 @@ def peer_fence(token: torch.Tensor, group=None) -> None:
 
 
 def push_rows(rows: torch.Tensor, m_sizes: torch.Tensor, dst_ptrs: torch.Tensor,
-              dst_limit: Optional[torch.Tensor] = None, max_ctas: int = 0, first_expert: int = 0) -> None:
+              dst_limit: Optional[torch.Tensor] = None, max_ctas: int = 0, first_expert: int = 0,
+              src_index: Optional[torch.Tensor] = None, src_div: int = 1) -> None:
     """rows (M, W) sorted by expert, m_sizes (E,): row i of expert e is copied to the address
     dst_ptrs[e] + i * row_bytes (int64 device tensor of addresses, local or peer memory); rows
-    with i >= dst_limit[e] are dropped.  The copy starts with the rows of `first_expert`."""
+    with i >= dst_limit[e] are dropped.  The copy starts with the rows of `first_expert`.
+    With `src_index` (int32, one entry per sorted row) sorted row r is read from
+    rows[src_index[r] // src_div]: token rows are expanded while they are pushed."""
     from . import _lib
 
     assert rows.is_cuda and rows.is_contiguous() and rows.dim() == 2
@@ -271,10 +274,14 @@ def push_rows(rows: torch.Tensor, m_sizes: torch.Tensor, dst_ptrs: torch.Tensor,
     m_sizes = _lib.as_index_tensor(m_sizes).contiguous()
     if dst_limit is not None:
         assert dst_limit.dtype == torch.int32 and dst_limit.is_contiguous() and dst_limit.numel() == m_sizes.numel()
+    n_rows = rows.shape[0]
+    if src_index is not None:
+        assert src_index.dtype == torch.int32 and src_index.is_contiguous()
+        n_rows = src_index.numel()
     _lib.check(_lib.load().moe_ep_push_rows(
-        _lib.ptr(rows), rows.shape[0], rows.shape[1] * rows.element_size(), _lib.ptr(m_sizes), _lib.int_code(m_sizes.dtype),
-        m_sizes.numel(), _lib.ptr(dst_ptrs), _lib.ptr(dst_limit), first_expert, max_ctas, _lib.stream_ptr(rows.device)),
-        "moe_ep_push_rows")
+        _lib.ptr(rows), n_rows, rows.shape[1] * rows.element_size(), _lib.ptr(m_sizes), _lib.int_code(m_sizes.dtype),
+        m_sizes.numel(), _lib.ptr(dst_ptrs), _lib.ptr(dst_limit), first_expert, _lib.ptr(src_index), src_div, max_ctas,
+        _lib.stream_ptr(rows.device)), "moe_ep_push_rows")
 
 
 def scattered_grouped_gemm(x: torch.Tensor, weight: torch.Tensor, group_sizes: torch.Tensor,
@@ -305,8 +312,10 @@ def scattered_grouped_gemm(x: torch.Tensor, weight: torch.Tensor, group_sizes: t
         _lib.ptr(out_ptrs), _lib.ptr(out_template), M, N, K, G, dt, dt, ws_ptr, ws_bytes, _lib.stream_ptr(x.device)), name)
 
 
-def peer_push(plan: PeerPlan, rows: torch.Tensor, channel, max_ctas: int = 0) -> None:
-    """Rows sorted by global expert -> expert-major (local expert, source) order in the owners' `channel`."""
+def peer_push(plan: PeerPlan, rows: torch.Tensor, channel, max_ctas: int = 0,
+              src_index: Optional[torch.Tensor] = None, src_div: int = 1) -> None:
+    """Rows sorted by global expert -> expert-major (local expert, source) order in the owners' `channel`.
+    With `src_index` / `src_div` the sorted rows are rows[src_index // src_div] (see push_rows)."""
     row_bytes = rows.shape[1] * rows.element_size()
     assert row_bytes == channel.row_bytes
     key = ("push", channel.ptrs.data_ptr(), channel.capacity_rows)
@@ -321,7 +330,8 @@ def peer_push(plan: PeerPlan, rows: torch.Tensor, channel, max_ctas: int = 0) ->
     # every rank starts with the rows of the next rank's experts, so the ranks' writes fan out
     # over distinct destinations instead of converging on one receiver at a time
     e_all = plan.m_sizes.numel() // plan.world
-    push_rows(rows, plan.m_sizes, dst, limit, max_ctas, first_expert=((plan.rank + 1) % plan.world) * e_all)
+    push_rows(rows, plan.m_sizes, dst, limit, max_ctas, first_expert=((plan.rank + 1) % plan.world) * e_all,
+              src_index=src_index, src_div=src_div)
 
 
 def peer_grouped_gemm(plan: PeerPlan, rows_in, weight: torch.Tensor, rows_out, transposed: bool = False) -> None:
@@ -362,7 +372,7 @@ class PeerMoeBlock:
         down_proj (E_local, H, I): this rank's experts.  Returns (out (T, H), router_logits (T, E))."""
         from .grouped_gemm.forward import grouped_gemm_forward
         from .kernels.indexing import get_expert_counts_and_idx
-        from .kernels.routing import _combine, _expand_rows, softmax_topk
+        from .kernels.routing import _combine, softmax_topk
         from .kernels.silu_mul import silu_mul_forward
 
         T, H = x.shape
@@ -371,12 +381,11 @@ class PeerMoeBlock:
         x = x.contiguous()
         router_logits = torch.nn.functional.linear(x, gate_weight)
         weights, selected = softmax_topk(router_logits, k, norm_topk_prob, x.dtype)
-        m_sizes, _, inv_sort_idx = get_expert_counts_and_idx(selected.view(T * k), E)
-        xs = _expand_rows(x, inv_sort_idx, k)
+        m_sizes, sort_idx, inv_sort_idx = get_expert_counts_and_idx(selected.view(T * k), E)
         plan = PeerPlan.build(m_sizes, self.world, self.rank, self.group)
         if check_capacity:  # one host read; rows beyond the buffer would be dropped, not written out of bounds
             assert int(plan.recv_rows) <= self.ch_x.capacity_rows, "receive buffer too small for this routing"
-        peer_push(plan, xs, self.ch_x)
+        peer_push(plan, x, self.ch_x, src_index=sort_idx, src_div=k)  # token rows are expanded while they travel
         peer_fence(self.token, self.group)  # every rank's rows have arrived (and the previous call's reads are over)
         rows = self.ch_x.local
         gate_h = grouped_gemm_forward(rows, gate_proj, plan.local_m_sizes)
