@@ -333,6 +333,19 @@ def run_kernel_suite(args):
         emit("gate_up forward vs torch._grouped_mm (library)", ours, flops=2.0 * M * N * K, library="unavailable: " + str(exc)[:120])
     del x, wg
 
+    # ---- gate + up + SiLU-mul in one kernel against the three kernels it stands for (block size) ----
+    from qwen3_moe_fused.kernels.fused_mlp import gate_up_silu_forward
+
+    M, I_, K = 131072, 768, 2048
+    x = torch.randn(M, K, device=dev, dtype=bf)
+    wg, wu = mk(E, I_, K, sc=0.02), mk(E, I_, K, sc=0.02)
+    m_sizes = torch.full((E,), M // E, device=dev, dtype=torch.int32)
+    fused_ms = time_cuda(lambda: gate_up_silu_forward(x, wg, wu, m_sizes), iters=10)
+    three_ms = time_cuda(lambda: silu_mul_forward(grouped_gemm_forward(x, wg, m_sizes), grouped_gemm_forward(x, wu, m_sizes)), iters=10)
+    emit("gate_up_silu fused forward, 131072 rows, 2048 -> 768 x 2", fused_ms, flops=2 * 2.0 * M * I_ * K, three_kernels_ms=three_ms,
+         speedup_vs_three_kernels=three_ms / fused_ms)
+    del x, wg, wu
+
     # ---- one full MoE block forward at the block workload (16384 tokens) ----
     T = 16384
     hidden = torch.randn(1, T, 2048, device=dev, dtype=bf)

@@ -123,6 +123,17 @@ int moe_grouped_gemm_dw(const void* x, const void* y, const void* m_sizes, int m
                         void* w, int64_t M, int N, int K, int E, int dtype_in, int dtype_out,
                         void* ws, size_t ws_bytes, void* stream);
 
+/* Gate projection, up projection and SiLU-mul of the expert MLP in one kernel:
+ *   h[m,i] = T(T(silu(e)) * g),  e = T(sum_k w_gate[e(m),i,k] x[m,k]),  g = T(sum_k w_up[e(m),i,k] x[m,k])
+ * with T = dtype: bit-identical to moe_grouped_gemm_fwd twice followed by moe_silu_mul_fwd, without
+ * writing or re-reading the two projections.  x (M,K), w_gate / w_up (E,I,K), h (M,I).
+ * Replaces qwen3_moe_fused/modular_qwen3_moe_fused.py:105-108 (inference; the projections are
+ * not kept for a backward pass).  Tensor-core CTA-pair kernel only: bf16/fp16, workspace
+ * required; MOE_ERR_UNSUPPORTED otherwise. */
+int moe_gate_up_silu_fwd(const void* x, const void* w_gate, const void* w_up, const void* m_sizes,
+                         int m_sizes_dtype, void* h, int64_t M, int I, int K, int E, int dtype,
+                         void* ws, size_t ws_bytes, void* stream);
+
 /* Forward with an NF4 weight decoded inside the kernel:
  *   w[e,n,k] = code[nibble(e,n,k)] * absmax[(e*N*K + n*K + k) / blocksize], rounded to
  *   dtype_in, then as moe_grouped_gemm_fwd.  packed: E*N*K/2 bytes, element 2j in the

@@ -179,3 +179,33 @@ def test_linearity_at_full_gate_up_shape(cuda):
     rows = torch.arange(E, device=cuda) * (M // E) + torch.randint(0, M // E, (E,), device=cuda)
     ref = torch.einsum("enk,ek->en", w.float(), x1[rows].float())
     assert float((y1[rows] - ref).abs().max() / ref.abs().max()) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("M,K,I,E,empty", [
+    (3000, 256, 384, 8, 0.2),
+    (8192, 2048, 768, 16, 0.0),     # the model's gate / up shape
+    (700, 72, 192, 3, 0.0),         # features not a multiple of 128: the last pair tile is half empty
+    (50, 64, 64, 4, 0.5),
+])
+def test_gate_up_silu_fused_equals_three_kernels(cuda, dtype, M, K, I, E, empty):
+    """gate GEMM + up GEMM + SiLU-mul in one kernel: bit-identical to the separate kernels."""
+    from qwen3_moe_fused import _lib
+    from qwen3_moe_fused.grouped_gemm.forward import grouped_gemm_forward
+    from qwen3_moe_fused.kernels.fused_mlp import gate_up_silu_forward
+    from qwen3_moe_fused.kernels.silu_mul import silu_mul_forward
+
+    rng = np.random.default_rng(M + K + I)
+    x = to_dev(rounded(rng.standard_normal((M, K)), dtype), dtype, cuda)
+    wg = to_dev(rounded(rng.standard_normal((E, I, K)) / np.sqrt(K) * 2, dtype), dtype, cuda)
+    wu = to_dev(rounded(rng.standard_normal((E, I, K)) / np.sqrt(K), dtype), dtype, cuda)
+    m = torch.from_numpy(random_m_sizes(rng, M, E, empty)).to(cuda)
+    prev = _lib.set_gemm_path(_lib.PATH_AUTO)
+    try:
+        h = gate_up_silu_forward(x, wg, wu, m)
+        ref = silu_mul_forward(grouped_gemm_forward(x, wg, m), grouped_gemm_forward(x, wu, m))
+        torch.cuda.synchronize()
+    finally:
+        _lib.set_gemm_path(prev)
+    assert _lib.read_error_flag() == 0
+    assert torch.equal(h, ref)

@@ -24,6 +24,8 @@ int tc_grouped_gemm_scattered(int which, const void* a, const void* b, const voi
                               const int* weight_index, int n_weights, const uint64_t* out_ptrs, void* out_template,
                               int64_t M, int N, int K, int G, int dtype_in, int dtype_out, void* ws, size_t ws_bytes,
                               cudaStream_t stream);
+int tc_gate_up_silu(const void* x, const void* w_gate, const void* w_up, const void* m_sizes, int ms64, void* h,
+                    int64_t M, int I, int K, int E, int dtype, void* ws, size_t ws_bytes, cudaStream_t stream);
 int tc_read_error(int* flag_out, bool clear);
 const char* tc_last_detail();
 
@@ -163,6 +165,21 @@ MOE_API int moe_grouped_gemm_dx_nf4(const void* x, const uint8_t* packed, const 
     return MOE_ERR_UNSUPPORTED;
   return tc_grouped_gemm_nf4(x, packed, code, absmax, blocksize, m_sizes, msd == MOE_I64, y, M, N, K, E, dtype_in,
                              dtype_out, ws, ws_bytes, (cudaStream_t)stream, true);
+}
+
+MOE_API int moe_gate_up_silu_fwd(const void* x, const void* w_gate, const void* w_up, const void* m_sizes, int msd,
+                                 void* h, int64_t M, int I, int K, int E, int dtype, void* ws, size_t ws_bytes,
+                                 void* stream) {
+  int st = check_common(x, w_gate, m_sizes, msd, h, M, I, K, E, dtype, dtype);
+  if (st != MOE_OK) return st;
+  if (M > 0 && I > 0 && K > 0 && !w_up) return MOE_ERR_NULL;
+  if (M == 0 || I == 0) return MOE_OK;
+  if (!device_is_sm100()) return MOE_ERR_DEVICE;
+  // CTA-pair tensor-core kernel only: 16-bit data, 16-byte aligned rows and bases
+  if (K == 0 || dtype == MOE_F32 || !tc_eligible(0, x, w_gate, h, M, I, K, E, dtype, dtype) ||
+      ((uintptr_t)w_up & 15) || ((uintptr_t)h & 15))
+    return MOE_ERR_UNSUPPORTED;
+  return tc_gate_up_silu(x, w_gate, w_up, m_sizes, msd == MOE_I64, h, M, I, K, E, dtype, ws, ws_bytes, (cudaStream_t)stream);
 }
 
 static int run_scattered(int which, const void* x, const void* w, const void* group_sizes, int msd,

@@ -297,7 +297,11 @@ __device__ __forceinline__ void stmatrix_x4_trans(uint32_t smem_addr, uint32_t r
   asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1, %2, %3, %4};"
                ::"r"(smem_addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
 }
-
+// Two 8x8 matrices; lanes 0..15 supply the row addresses.
+__device__ __forceinline__ void stmatrix_x2_trans(uint32_t smem_addr, uint32_t r0, uint32_t r1) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x2.trans.shared.b16 [%0], {%1, %2};"
+               ::"r"(smem_addr), "r"(r0), "r"(r1) : "memory");
+}
 
 // ---------------------------------------------------------------------------------------
 // Descriptors

@@ -716,11 +716,11 @@ static int pair_grouped_gemm(int which, const void* a, const void* b, const void
     if (which == 0) {
       if ((st = set_smem(pair_fwd_kernel<false>, bytes)) != MOE_OK) return st;
       const int grid = 2 * resident_pairs(pair_fwd_kernel<false>, bytes);
-      pair_fwd_kernel<false><<<grid, PAIR_THREADS, bytes, stream>>>(mw, mx, p);
+      pair_fwd_kernel<false><<<grid, PAIR_THREADS, bytes, stream>>>(mw, mx, p, mw);
     } else {
       if ((st = set_smem(pair_fwd_kernel<true>, bytes)) != MOE_OK) return st;
       const int grid = 2 * resident_pairs(pair_fwd_kernel<true>, bytes);
-      pair_fwd_kernel<true><<<grid, PAIR_THREADS, bytes, stream>>>(mw, mx, p);
+      pair_fwd_kernel<true><<<grid, PAIR_THREADS, bytes, stream>>>(mw, mx, p, mw);
     }
     return launch_status();
   }
@@ -866,6 +866,38 @@ int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes
     return launch_status();
   }
   return MOE_ERR_UNSUPPORTED;
+}
+
+// h = silu(x w_gate^T) * (x w_up^T) per expert in one launch (pair_fwd_kernel<false, true>).
+int tc_gate_up_silu(const void* x, const void* w_gate, const void* w_up, const void* m_sizes, int ms64, void* h,
+                    int64_t M, int I, int K, int E, int dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  using namespace tc;
+  bind_context_once();
+  if (ws == nullptr || ((uintptr_t)ws & 127) || ws_bytes < (size_t)2 * E * sizeof(CUtensorMap)) return MOE_ERR_WORKSPACE;
+  GemmParams p;
+  p.a = x; p.b = w_gate;
+  p.m_sizes = m_sizes; p.out = h; p.M = M; p.N = I; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype; p.debug = debug_flags();
+  p.idesc = make_idesc(dtype == MOE_BF16 ? 1 : 0, 0, 0, 256, 0);
+  CUtensorMap mg, mu, mx;
+  int st;
+  if ((st = make_map(&mg, dtype, w_gate, (uint64_t)K, (uint64_t)I, (uint64_t)E, 16)) != MOE_OK) return st;
+  if ((st = make_map(&mu, dtype, w_up, (uint64_t)K, (uint64_t)I, (uint64_t)E, 16)) != MOE_OK) return st;
+  if ((st = make_map(&mx, dtype, x, (uint64_t)K, (uint64_t)M, 0, 128)) != MOE_OK) return st;
+  GroupMapTemplates tm;
+  tm.count = 2;
+  tm.t[GM_IN] = mx;
+  if ((st = make_map(&tm.t[GM_OUT], dtype, h, (uint64_t)I, (uint64_t)M, 0, 32)) != MOE_OK) return st;
+  const int gm_smem = 8 * 128 + 2 * (E + 1) * 4 + 128;
+  build_group_maps_kernel<<<(E + 7) / 8, 256, gm_smem, stream>>>(tm, m_sizes, ms64, E, M, reinterpret_cast<CUtensorMap*>(ws));
+  if ((st = launch_status()) != MOE_OK) return st;
+  p.group_maps = reinterpret_cast<const CUtensorMap*>(ws);
+  const int bytes = PAIR_STAGES * 2 * PAIR_HALF_BYTES + 4 * PAIR_STAGING_BYTES + (int)sizeof(PairControl) + 2 * (E + 1) * 4 + 1024;
+  if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
+  auto kern = pair_fwd_kernel<false, true>;
+  if ((st = set_smem(kern, bytes)) != MOE_OK) return st;
+  const int grid = 2 * resident_pairs(kern, bytes);
+  kern<<<grid, PAIR_THREADS, bytes, stream>>>(mg, mx, p, mu);
+  return launch_status();
 }
 
 // Scattered forward (which = 0) / dX (which = 1) on the CTA-pair kernels: see pair_grouped_gemm.

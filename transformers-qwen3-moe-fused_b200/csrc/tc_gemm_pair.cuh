@@ -96,13 +96,71 @@ __device__ __forceinline__ void pair_store_tile_staged(uint8_t* staging, uint32_
   }
 }
 
+// h = T(T(e * sigmoid(e)) * g) for e = T(acc_gate), g = T(acc_up): the rounding points of the
+// separate kernels (grouped GEMM output in T, then qwen3_moe_fused/kernels/silu_mul.py:34-39),
+// so the fused result is bit-identical to forward + forward + SiLU-mul.
+template <typename T>
+__device__ __forceinline__ float gate_up_one(float acc_gate, float acc_up) {
+  const float e = to_f32(from_f32<T>(acc_gate));
+  const float g = to_f32(from_f32<T>(acc_up));
+  const float f = to_f32(from_f32<T>(e * __fdividef(1.f, 1.f + __expf(-e))));
+  return f * g;  // rounded to T by the caller's pack
+}
+
+// Epilogue of the fused gate/up kernel.  A warp's 32 accumulator rows are 16 gate rows (TMEM
+// lanes 0..15 of its quarter) and the 16 up rows of the same features (lanes 16..31): the two
+// 16x256b loads put gate and up of one (feature, token) into the same register index of the same
+// thread.  The warp stores 16 features x 32 tokens per round (two transposed 8x8 matrices per
+// 8 tokens); the CTA's four warps fill a [32 tokens][64 features] tile that leaves by TMA.
+__device__ __forceinline__ void pair_store_tile_gate_up(uint8_t* staging, uint32_t& chunk_it, uint32_t taddr, int n_mma,
+                                                        int quarter, int lane, int epi_tid, bool is_bf16,
+                                                        const CUtensorMap* my, int feat_cta, int t0, int n_feat, int debug) {
+  const int chunk = 2 * quarter + ((lane >> 3) & 1);  // 16-byte chunk of the 128-byte staging row
+#pragma unroll 1
+  for (int c = 0; c < n_mma; c += 32, ++chunk_it) {
+    uint8_t* buf = staging + (chunk_it & 1) * (2 * PAIR_STAGING_BYTES);
+    if (epi_tid == 0) tma_store_wait_read<1>();
+    named_barrier_sync(1, 128);
+    uint32_t lo[16], hi[16];
+    tmem_ld_16x256b_x4(taddr + c, lo);
+    tmem_ld_16x256b_x4(taddr + c + (16u << 16), hi);
+    tmem_ld_wait();
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float h[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float a = __uint_as_float(lo[4 * g + i]), b = __uint_as_float(hi[4 * g + i]);
+        h[i] = is_bf16 ? gate_up_one<__nv_bfloat16>(a, b) : gate_up_one<__half>(a, b);
+      }
+      const uint32_t m0 = is_bf16 ? pack2<__nv_bfloat16>(h[0], h[1]) : pack2<__half>(h[0], h[1]);
+      const uint32_t m1 = is_bf16 ? pack2<__nv_bfloat16>(h[2], h[3]) : pack2<__half>(h[2], h[3]);
+      const int trow = 8 * g + (lane & 7);
+      stmatrix_x2_trans(smem_u32(buf + trow * 128 + ((chunk ^ (trow & 7)) << 4)), m0, m1);
+    }
+    fence_proxy_async_smem();
+    named_barrier_sync(1, 128);
+    if (epi_tid == 0 && !(debug & 1)) {
+      if (feat_cta < n_feat) tma_store_2d(my, buf, feat_cta, t0 + c);  // columns past the last feature are clipped
+      tma_store_commit();
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // forward / dX
+//
+// GATE_UP (forward only): tmap_w / tmap_w2 are the gate and up weights (E, I, K); the pair's 256
+// accumulator rows are 128 features x {gate, up}, interleaved in slabs of 16 rows
+// [gate f..f+15][up f..f+15]... so that a warp's quarter of TMEM holds gate and up of the same 16
+// features; the epilogue writes h = silu(gate) * up (p.N = I columns) and neither projection.
 // ---------------------------------------------------------------------------------------
-template <bool W_MN>
+template <bool W_MN, bool GATE_UP = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                const GemmParams p) {
+                const GemmParams p, const __grid_constant__ CUtensorMap tmap_w2) {
+  static_assert(!(W_MN && GATE_UP), "the fused gate/up form reads K-major weights");
+  constexpr int TILE_N = GATE_UP ? 128 : 256;  // output columns (features) per pair
   constexpr int STAGE_BYTES = 2 * PAIR_HALF_BYTES;  // A half-tile + B half-tile per CTA
   constexpr int STAGES = PAIR_STAGES;
   constexpr uint32_t TMEM_COLS = 512;  // two accumulators of up to 256 token columns
@@ -138,7 +196,7 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
 
-  const int n_tiles = (p.N + 255) / 256;  // 256 weight rows per pair
+  const int n_tiles = (p.N + TILE_N - 1) / TILE_N;  // 256 weight rows per pair
   const int k_blocks = (p.K + BK - 1) / BK;
   const int64_t total_tiles = (int64_t)tt_start[p.E] * n_tiles;
   const int pair_id = blockIdx.x >> 1;
@@ -151,7 +209,7 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     const int tt_e = tt_start[e + 1] - tt_start[e];
     const int j = (int)(tile - (int64_t)tt_start[e] * n_tiles);
     t0 = row_start[e] + (j % tt_e) * PAIR_TOKENS;
-    n0 = (j / tt_e) * 256;
+    n0 = (j / tt_e) * TILE_N;
     const int left = row_start[e + 1] - t0;
     n_mma = left >= PAIR_TOKENS ? PAIR_TOKENS : ((left + 15) & ~15);
   };
@@ -180,7 +238,14 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           uint8_t* sb = sa + PAIR_HALF_BYTES;
           const uint32_t bar = full_leader0 + s * 8;
           if (leader) mbar_expect_tx(&ctl->full[s], 2 * STAGE_BYTES);  // both CTAs' bytes
-          if constexpr (!W_MN) {
+          if constexpr (GATE_UP) {
+            const int feat = n0 + (int)rank * 64;  // this CTA's 64 features
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              tma_load_3d_pair(sa + (2 * q) * 2048, &tmap_w, bar, kb * BK, feat + 16 * q, we);
+              tma_load_3d_pair(sa + (2 * q + 1) * 2048, &tmap_w2, bar, kb * BK, feat + 16 * q, we);
+            }
+          } else if constexpr (!W_MN) {
             tma_load_3d_pair(sa, &tmap_w, bar, kb * BK, w_row, we);
           } else {
             tma_load_3d_pair(sa, &tmap_w, bar, w_row, kb * BK, we);
@@ -248,7 +313,11 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       if (!mbar_wait_cluster(&ctl->tmem_full[acc], acc_ph, abort_flag, PW_TMEM_FULL)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * PAIR_TOKENS + ((uint32_t)(quarter * 32) << 16);
-      if (staged) {
+      if constexpr (GATE_UP) {
+        // (the host only launches this form with per-expert output maps and a 16-bit output)
+        pair_store_tile_gate_up(staging, chunk_it, taddr, n_mma, quarter, lane, epi_tid, is_bf16, my,
+                                n0 + (int)rank * 64, t0, p.N, p.debug);
+      } else if (staged) {
         pair_store_tile_staged(staging, chunk_it, taddr, n_mma, quarter, lane, epi_tid, is_bf16, my,
                                n0 + (int)rank * 128, t0, p.N, p.debug);
       } else {

@@ -16,6 +16,7 @@ import torch
 from torch import nn
 
 from .functional import moe_fused_linear
+from .kernels.fused_mlp import gate_up_silu_forward
 from .kernels.indexing import get_expert_counts_and_idx
 from .kernels.routing import combine, gather_rows, softmax_topk_autograd
 from .kernels.silu_mul import silu_mul
@@ -67,9 +68,13 @@ def moe_block_forward(hidden_states: torch.Tensor, gate_weight: torch.Tensor, ga
     routing_weights, selected = route(router_logits, k, norm_topk_prob, x.dtype)
     m_sizes, sort_idx, inv_sort_idx = get_expert_counts_and_idx(selected.view(T * k), E)
     xs = gather_rows(x.contiguous(), sort_idx, inv_sort_idx, k)
-    gate_h = moe_fused_linear(xs, gate_proj, m_sizes)
-    up_h = moe_fused_linear(xs, up_proj, m_sizes)
-    h = silu_mul(gate_h, up_h)
+    if not torch.is_grad_enabled():
+        # inference: gate, up and SiLU-mul in one kernel (same result bit for bit)
+        h = gate_up_silu_forward(xs, gate_proj, up_proj, m_sizes)
+    else:
+        gate_h = moe_fused_linear(xs, gate_proj, m_sizes)
+        up_h = moe_fused_linear(xs, up_proj, m_sizes)
+        h = silu_mul(gate_h, up_h)
     y = moe_fused_linear(h, down_proj, m_sizes)
     out = combine(y, sort_idx, inv_sort_idx, routing_weights)
     return out.view(B, S, H), router_logits

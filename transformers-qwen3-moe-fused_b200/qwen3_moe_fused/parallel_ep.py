@@ -370,10 +370,9 @@ class PeerMoeBlock:
                 down_proj: torch.Tensor, num_selected: int, norm_topk_prob: bool = True, check_capacity: bool = False):
         """x (T, H): this rank's tokens; gate_weight (E, H) on every rank; gate_proj / up_proj (E_local, I, H) and
         down_proj (E_local, H, I): this rank's experts.  Returns (out (T, H), router_logits (T, E))."""
-        from .grouped_gemm.forward import grouped_gemm_forward
+        from .kernels.fused_mlp import gate_up_silu_forward
         from .kernels.indexing import get_expert_counts_and_idx
         from .kernels.routing import _combine, softmax_topk
-        from .kernels.silu_mul import silu_mul_forward
 
         T, H = x.shape
         E, k = gate_weight.shape[0], num_selected
@@ -388,9 +387,7 @@ class PeerMoeBlock:
         peer_push(plan, x, self.ch_x, src_index=sort_idx, src_div=k)  # token rows are expanded while they travel
         peer_fence(self.token, self.group)  # every rank's rows have arrived (and the previous call's reads are over)
         rows = self.ch_x.local
-        gate_h = grouped_gemm_forward(rows, gate_proj, plan.local_m_sizes)
-        up_h = grouped_gemm_forward(rows, up_proj, plan.local_m_sizes)
-        h = silu_mul_forward(gate_h, up_h)
+        h = gate_up_silu_forward(rows, gate_proj, up_proj, plan.local_m_sizes)
         out_ptrs = (self.ch_y.ptrs[plan.group_src] + plan.return_row * self.ch_y.row_bytes).contiguous()
         scattered_grouped_gemm(h, down_proj, plan.group_sizes, plan.weight_index, out_ptrs, self.ch_y.local)
         peer_fence(self.token, self.group)  # every rank's results have arrived
