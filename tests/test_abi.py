@@ -53,6 +53,16 @@ def test_argument_errors_return_before_any_launch(lib):
     assert lib.moe_router_softmax_topk(None, 0, 4, 128, 64, 1, None, 0, None, None) == -2  # k > 32
     assert lib.moe_nf4_dequant(None, None, None, 48, None, 64, 1, None) == -2  # blocksize not 2^n
     assert lib.moe_silu_mul_fwd(None, None, None, -1, 1, None) == -2
+    # expert-parallel and fused entry points
+    assert lib.moe_ep_plan(None, 3, 0, 128, 0, 42, None, None, None, None, None, None, None, None, None) == -2  # 128 % 3
+    assert lib.moe_ep_plan(None, 4, 0, 128, 0, 32, None, None, None, None, None, None, None, None, None) == -3
+    assert lib.moe_ep_push_rows(None, 8, 64, None, 9, 4, None, None, 0, None, 1, 0, None) == -1
+    assert lib.moe_ep_push_rows(None, 8, 64, None, 3, 4, None, None, 7, None, 1, 0, None) == -2  # first_expert >= E
+    assert lib.moe_ep_push_rows(None, 8, 64, None, 3, 4, None, None, 0, None, 1, 0, None) == -3
+    assert lib.moe_gate_up_silu_fwd(None, None, None, None, 3, None, 4, 4, 4, 2, 9, None, 0, None) == -1
+    assert lib.moe_grouped_gemm_dx_nf4(None, None, None, None, 48, None, 3, None, 4, 4, 4, 2, 1, 1, None, 0, None) == -3
+    assert lib.moe_grouped_gemm_fwd_scattered(None, None, None, 3, None, 2, None, None, -1, 4, 4, 2, 1, 1, None, 0, None) == -2
+    assert lib.moe_expand_rows(None, None, 0, None, 4, 4, 1, None) == -2  # k <= 0
 
 
 def test_sort_workspace_query(lib):
