@@ -56,7 +56,9 @@ def test_silu_mul_autograd_and_unaligned(cuda):
     assert torch.allclose(e32.grad, ee.grad, rtol=1e-4, atol=1e-5) and torch.allclose(g32.grad, gg.grad, rtol=1e-4, atol=1e-5)
 
 
-@pytest.mark.parametrize("T,E,k", [(8192, 128, 8), (1000, 11, 3), (77, 60, 4), (5, 1024, 32), (16, 8, 8)])
+@pytest.mark.parametrize("T,E,k", [(8192, 128, 8), (1000, 11, 3), (77, 60, 4), (5, 1024, 32), (16, 8, 8),
+                                   (140000, 128, 8),   # above the size where the eight-lanes-per-token form takes over
+                                   (300, 256, 16), (64, 64, 8)])
 @pytest.mark.parametrize("norm", [True, False])
 def test_router_fp32_logits(cuda, T, E, k, norm):
     from qwen3_moe_fused.kernels.routing import softmax_topk
@@ -86,6 +88,20 @@ def test_router_ties_pick_lowest_expert(cuda):
     rw, ridx = O.router_softmax_topk(to_np(logits), 8, True, "bf16")
     np.testing.assert_array_equal(idx.cpu().numpy(), ridx)
     assert idx[1].tolist() == list(range(8))
+    assert np.abs(to_np(w) - rw).max() <= 2 ** -7
+
+
+@pytest.mark.parametrize("T", [2000, 135000])  # one size for each form of the kernel
+def test_router_many_ties(cuda, T):
+    """Logits from a set of five values: every row has many exact ties, and distinct logits have
+    clearly distinct probabilities, so the (value descending, expert ascending) rule is checked exactly."""
+    from qwen3_moe_fused.kernels.routing import softmax_topk
+
+    rng = np.random.default_rng(T)
+    logits = (rng.integers(0, 5, (T, 128)) * 0.5).astype(np.float32)
+    w, idx = softmax_topk(torch.from_numpy(logits).to(cuda).to(torch.bfloat16), 8, True, torch.bfloat16)
+    rw, ridx = O.router_softmax_topk(logits, 8, True, "bf16")
+    np.testing.assert_array_equal(idx.cpu().numpy(), ridx)
     assert np.abs(to_np(w) - rw).max() <= 2 ** -7
 
 
