@@ -459,6 +459,8 @@ def main():
                     help="block suite: tokens per GPU (weak scaling) instead of 16384 tokens in total")
     ap.add_argument("--push-ctas", type=int, default=0,
                     help="N > 1, peer transport: CTAs of the row push that overlaps a GEMM (0: four per SM)")
+    ap.add_argument("--ep-overlap", default="on", choices=["on", "off"],
+                    help="N > 1, peer transport: run the second row push beside the first GEMM (on) or before it (off)")
     ap.add_argument("--ep-chunks", type=int, default=1,
                     help="N > 1, peer transport: chunks of local experts whose exchange and GEMMs are pipelined")
     ap.add_argument("--gemm-path", default="auto", choices=["auto", "tc", "tc_single", "simt"],
@@ -602,8 +604,9 @@ def main():
             e_x = [torch.cuda.Event() for _ in range(nc)]
             e_dy = [torch.cuda.Event() for _ in range(nc)]
             # dY (the smaller operand) goes first and dX runs first: the exposed first push is shorter
+            push_stream = comm_stream if args.ep_overlap == "on" else main
             comm_stream.wait_stream(main)
-            with torch.cuda.stream(comm_stream):
+            with torch.cuda.stream(push_stream):
                 for rows, chans, events, ctas in ((dy_d, peer["dy"], e_dy, 0), (x_d, peer["x"], e_x, args.push_ctas)):
                     for i in range(nc):
                         peer_push(peer["plans"][i], rows, chans[i], ctas)  # the second push runs beside a GEMM
