@@ -10,9 +10,19 @@ whole job with inputs resident in HBM; `e2e` is the same figure through the publ
 API with inputs in pinned host memory (router epilogue, sort, gather and the three GEMMs,
 host->device and device->host copies inside the timed region).
 
+`e2e` copies the step's results (y, dX and dW) back into pinned host
+memory inside the timed region as well.
+
 With N > 1 the 128 experts are sharded over the ranks (expert parallel); every rank routes
-its own 8192 tokens, rows travel to the rank that owns their expert by NCCL all-to-all and
-gradients travel back (weak scaling: per-GPU rows are fixed).
+its own 8192 tokens and rows travel to the rank that owns their expert and results travel
+back (weak scaling: per-GPU rows are fixed).  Default transport: rows are stored into the
+owner's memory over NVLink by a copy kernel, and the forward / dX epilogues store their
+results straight into the source rank's memory (`--ep-transport peer`); `--ep-transport
+nccl` moves both directions by NCCL all-to-all instead.  After the timed loop one step's
+results are checked against the single-GPU kernels (`ep_check` in the line).
+
+At N = 1 the line also carries `extra_workloads`: the same measurement on the down_proj
+shape with Zipf(1.2) routing (skewed, ragged and empty groups).
 """
 from __future__ import annotations
 
@@ -38,10 +48,20 @@ WORKLOADS = {
     "gate_up": dict(tokens=8192, K=2048, N=1536, E=128, k=8, routing="softmax-top8 of N(0,1) logits"),
     "down": dict(tokens=8192, K=768, N=2048, E=128, k=8, routing="zipf(1.2) expert ids, 3 experts emptied"),
 }
-# dram__bytes_read + dram__bytes_write over algorithmic bytes, from one ncu capture per kernel on the
-# reduced case (16384 rows, 32 experts; profiles/pair_kernels_gate_up_16k_rows.md).  Traffic grows in
+# DRAM bytes (ncu dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each GEMM on a reduced
+# case, with that case's algorithmic bytes, as recorded beside the ncu summaries.  Traffic grows in
 # proportion to rows and experts, so the ratio carries over to the full workload.
-NCU_TRAFFIC_RATIO = {"fwd": 0.95, "dx": 0.94, "dw": 0.83}
+NCU_TRAFFIC_FILE = ROOT / "profiles" / "grouped_gemm_dram_traffic.json"
+
+
+def ncu_traffic_ratio(kernel: str):
+    """(DRAM bytes / algorithmic bytes, description of the capture) or (None, reason)."""
+    try:
+        rec = json.loads(NCU_TRAFFIC_FILE.read_text())
+        k = rec["kernels"][kernel]
+        return float(k["dram_bytes"]) / float(k["algorithmic_bytes"]), rec["case"]
+    except (OSError, KeyError, ValueError) as exc:
+        return None, f"no ncu traffic record: {exc}"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -68,7 +88,8 @@ def make_routing(cfg, seed: int):
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock, power and throttle reasons while a timed region runs: NVML every 5 ms from a
+    thread of this process (read-only queries), or `nvidia-smi -lms 100` where NVML cannot be loaded."""
 
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -76,10 +97,33 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index = index
-        self.rows = []
+        self.rows = []       # nvidia-smi rows
+        self.samples = []    # NVML samples: (sm MHz, power W, reasons bit mask)
         self.proc = None
+        self.nvml = None
+        self.stop_flag = threading.Event()
+
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if self.index < len(ids) and ids[self.index].isdigit():
+                return int(ids[self.index])
+        return self.index
 
     def start(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
@@ -89,11 +133,35 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        n = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append((float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)),
+                                     n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0,
+                                     int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))))
+            except Exception:
+                break
+            time.sleep(0.005)
+
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
+        if self.nvml is not None:
+            n = self.nvml
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            names = (("hw_slowdown", n.nvmlClocksThrottleReasonHwSlowdown),
+                     ("hw_thermal_slowdown", n.nvmlClocksThrottleReasonHwThermalSlowdown),
+                     ("sw_thermal_slowdown", n.nvmlClocksThrottleReasonSwThermalSlowdown),
+                     ("sw_power_cap", n.nvmlClocksThrottleReasonSwPowerCap))
+            reasons = sorted({name for _, _, mask in self.samples for name, bit in names if mask & bit})
+            sm = [c for c, _, _ in self.samples]
+            return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_min_mhz": min(sm) if sm else None,
+                    "sm_max_mhz": self.max_mhz, "power_w_max": max((p for _, p, _ in self.samples), default=None),
+                    "reasons": reasons, "samples": len(sm), "source": "nvml, 5 ms period"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -110,7 +178,8 @@ class ClockSampler:
             for name, col in (("hw_slowdown", 3), ("hw_thermal_slowdown", 4), ("sw_thermal_slowdown", 5), ("sw_power_cap", 6)):
                 if len(r) > col and r[col].lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm),
+                "source": "nvidia-smi, 100 ms period"}
 
 
 def cpu_reference_arm(cfg, steps: int, warmup: int, sample_rows: int):
@@ -435,6 +504,59 @@ def run_block_suite(args):
         dist.destroy_process_group()
 
 
+def measure_single_gpu_workload(name: str, steps: int, warmup: int, dev):
+    """fwd + dX + dW of one workload on one GPU, inputs resident: per-kernel CUDA-event times inside a
+    back-to-back loop and launched alone.  Used for the `extra_workloads` entry of the line."""
+    from qwen3_moe_fused.grouped_gemm.backward_dw import grouped_gemm_backward_dw
+    from qwen3_moe_fused.grouped_gemm.forward import grouped_gemm_forward
+    from qwen3_moe_fused.grouped_gemm.forward_transposed import grouped_gemm_forward_transposed
+    from qwen3_moe_fused.kernels.indexing import get_expert_counts_and_idx
+    from qwen3_moe_fused.kernels.routing import softmax_topk
+
+    cfg = dict(WORKLOADS[name])
+    T, K, N, E, k = cfg["tokens"], cfg["K"], cfg["N"], cfg["E"], cfg["k"]
+    M = T * k
+    bf = torch.bfloat16
+    logits_h, ids_h = make_routing(cfg, seed=0)
+    if logits_h is not None:
+        ids_d = softmax_topk(logits_h.to(dev), k, True, bf)[1].view(-1)
+    else:
+        ids_d = ids_h.to(dev)
+    m_sizes, _, _ = get_expert_counts_and_idx(ids_d, E)
+    gen = torch.Generator(device=dev).manual_seed(4321)
+    x = torch.randn(M, K, generator=gen, device=dev).to(bf)
+    dy = torch.randn(M, N, generator=gen, device=dev).to(bf)
+    w = (torch.randn(E, N, K, generator=gen, device=dev) * 0.02).to(bf)
+    fns = {"fwd": lambda: grouped_gemm_forward(x, w, m_sizes), "dx": lambda: grouped_gemm_forward_transposed(dy, w, m_sizes),
+           "dw": lambda: grouped_gemm_backward_dw(x, dy, m_sizes, bf)}
+    for _ in range(max(warmup, 3)):
+        for fn in fns.values():
+            fn()
+    torch.cuda.synchronize()
+    marks = []
+    for _ in range(steps):
+        row = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        row[0].record()
+        for i, fn in enumerate(fns.values()):
+            fn()
+            row[i + 1].record()
+        marks.append(row)
+    torch.cuda.synchronize()
+    step_ms = marks[0][0].elapsed_time(marks[-1][3]) / steps
+    flops_one = 2.0 * M * N * K
+    peaks, _ = measured_peaks()
+    out = {"workload": config_dict(argparse.Namespace(workload=name, gpus=1, ep_transport="peer"), cfg)["workload"],
+           "routing": cfg["routing"], "rows_per_expert": {"max": int(m_sizes.max()), "empty_experts": int((m_sizes == 0).sum())},
+           "steps": steps, "ms_per_step": step_ms, "value": 3 * flops_one / (step_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "kernels": {}}
+    for i, kname in enumerate(fns):
+        ms = float(np.mean([r[i].elapsed_time(r[i + 1]) for r in marks]))
+        alone = time_cuda(fns[kname], iters=20)
+        out["kernels"][kname] = {"ms": ms, "tflops": flops_one / (ms * 1e-3) / 1e12, "isolated_ms": alone,
+                                 "isolated_tflops": flops_one / (alone * 1e-3) / 1e12,
+                                 "isolated_frac_of_burst_peak": flops_one / (alone * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -444,6 +566,7 @@ def main():
     ap.add_argument("--workload", default="gate_up", choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-rows", type=int, default=4096, help="rows of the bounded CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the extra_workloads entry (down_proj shape, Zipf routing)")
     ap.add_argument("--suite", default="hotpath", choices=["hotpath", "kernels", "block"],
                     help="hotpath: the contract line (default); kernels: roofline lines of the surrounding kernels; "
                          "block: MoE block forward, 16384 tokens over N GPUs")
@@ -682,6 +805,7 @@ def main():
     t_end.record()
     barrier()
     resident_ms = t_start.elapsed_time(t_end) / args.steps
+    clocks = sampler.stop() if rank == 0 else None  # samples of the resident loop only
     first, second = ("dx", "fwd") if peer is not None else ("fwd", "dx")  # the peer schedule runs dX first
     for marks in all_marks:
         kernel_ms[first].append(marks[0].elapsed_time(marks[1]))
@@ -690,15 +814,21 @@ def main():
 
     # ---- end to end through the public API, inputs in pinned host memory ----
     h2d = hidden_h.numel() * 2 + dy_h.numel() * 2 + (logits_h.numel() * 4 if logits_h is not None else ids_h.numel() * 8)
-    d2h = 3 * 4 + E * 4
+    # results of a step: y (M, N), dX (M, K), dW (E_local, N, K), all bf16, plus m_sizes
+    d2h = 2 * (M * N + M * K + E_local * N * K) + E * 4
 
     # Inputs are double-buffered on the device: the upload of step i+1 (copy stream) runs beside the
     # compute of step i.  Every step's inputs still cross PCIe inside the timed region.
     copy_stream = torch.cuda.Stream(device=dev)
+    back_stream = torch.cuda.Stream(device=dev)  # results -> pinned host memory, beside the next step's compute
     slots = [{"hd": torch.empty_like(hidden_d), "dyd": torch.empty_like(dy_d),
               "lg": torch.empty_like(logits_d) if logits_d is not None else None,
               "idd": torch.empty_like(ids_d) if ids_d is not None else None,
               "ready": torch.cuda.Event(), "free": torch.cuda.Event()} for _ in range(2)]
+    back = [] if args.no_e2e else [
+        {"y": torch.empty((M, N), dtype=bf).pin_memory(), "dx": torch.empty((M, K), dtype=bf).pin_memory(),
+         "dw": torch.empty((E_local, N, K), dtype=bf).pin_memory(), "ms": torch.empty(E, dtype=torch.int32).pin_memory(),
+         "done": torch.cuda.Event()} for _ in range(2)]
 
     def upload(slot):
         sl = slots[slot]
@@ -741,25 +871,45 @@ def main():
             y = pl.combine(pl.grouped(grouped_gemm_forward, xl, w))
             dx = pl.combine(pl.grouped(grouped_gemm_forward_transposed, dyl, w))
             dw = pl.grouped_dw(grouped_gemm_backward_dw, xl, dyl, bf, E_local)
-        stats = torch.stack([y[0].float().sum(), dx[0].float().sum(), dw[0, 0].float().sum()])
         sl["free"].record()
-        return stats.cpu(), ms.cpu()  # device -> host read of the step's result
+        # device -> host copy of the step's results (y, dX, dW, m_sizes) into pinned memory, on a stream of
+        # its own so that it runs beside the next step; the host buffers alternate like the input slots
+        bk = back[i % 2]
+        bk["done"].synchronize()  # the copy that last wrote these host buffers has finished
+        computed = torch.cuda.Event()
+        computed.record()
+        with torch.cuda.stream(back_stream):
+            back_stream.wait_event(computed)
+            for name, t in (("y", y), ("dx", dx), ("dw", dw), ("ms", ms)):
+                bk[name][:t.shape[0]].copy_(t, non_blocking=True)
+            bk["done"].record()
+        bk["keep"] = (y, dx, dw, ms)  # the device tensors stay allocated until their copy has finished
+        if world > 1 and peer is not None:
+            # y / dX live in buffers that the next step's remote stores overwrite: the copy has to finish first
+            torch.cuda.current_stream().wait_event(bk["done"])
 
     e2e_ms = float("nan")
+    e2e_sampler = None
     if not args.no_e2e:
         upload(0)
         for i in range(3):
             step_e2e(i, i == 2)
         barrier()
+        if rank == 0:
+            e2e_sampler = ClockSampler(local_rank)
+            e2e_sampler.start()
         e0, e1 = ev(), ev()
         e0.record()
         upload(0)  # the first step's upload is inside the timed region too
         for i in range(args.steps):
             step_e2e(i, i == args.steps - 1)
+        torch.cuda.current_stream().wait_stream(back_stream)  # the last step's results have reached the host
         e1.record()
         barrier()
         e2e_ms = e0.elapsed_time(e1) / args.steps
-    clocks = sampler.stop() if rank == 0 else None
+        for bk in back:
+            bk.pop("keep", None)
+    e2e_clocks = e2e_sampler.stop() if e2e_sampler is not None else None
 
     # ---- each GEMM alone (N = 1): isolated launches with idle time between them, i.e. at burst
     # clocks, to set beside the burst cuBLAS figure; the timed loop above runs under the power cap ----
@@ -793,6 +943,39 @@ def main():
         barrier()
         xchg_ms = x0.elapsed_time(x1) / 10
 
+    # ---- N > 1: one step's results against the single-GPU kernels (not timed) ----
+    ep_check = None
+    if world > 1 and not args.only and args.ep_chunks == 1:
+        _, (y_ep, dx_ep, dw_ep) = step_resident(False)
+        barrier()
+        # every rank's rows and gradients, and every rank's share of the weights, on every rank
+        xs_all = [torch.empty_like(x_d) for _ in range(world)]
+        dys_all = [torch.empty_like(dy_d) for _ in range(world)]
+        dist.all_gather(xs_all, x_d)
+        dist.all_gather(dys_all, dy_d)
+        counts_all = torch.empty(world * E, dtype=torch.int32, device=dev)
+        dist.all_gather_into_tensor(counts_all, m_sizes.to(torch.int32).contiguous())
+        counts_all = counts_all.view(world, E)
+        if rank == 0:
+            rel = lambda a, b: float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-30))
+            w_full = torch.cat([(torch.randn(E_local, N, K, generator=torch.Generator().manual_seed(99 + r)) * 0.02).to(bf).to(dev)
+                                for r in range(world)])
+            errs = {"y": rel(y_ep[:M], grouped_gemm_forward(x_d, w_full, m_sizes)),
+                    "dx": rel(dx_ep[:M], grouped_gemm_forward_transposed(dy_d, w_full, m_sizes))}
+            # dW of this rank's experts: their rows from every rank, expert by expert
+            begins = (counts_all.long().cumsum(dim=1) - counts_all.long()).cpu()
+            cnt = counts_all.cpu()
+            take = lambda rows_all: torch.cat([rows_all[r][int(begins[r, e]):int(begins[r, e]) + int(cnt[r, e])]
+                                               for e in range(E_local) for r in range(world)])
+            m_local = cnt[:, :E_local].sum(dim=0).to(torch.int32).to(dev)
+            errs["dw"] = rel(dw_ep, grouped_gemm_backward_dw(take(xs_all), take(dys_all), m_local, bf))
+            ep_check = {"what": "rank 0's y and dX rows and its experts' dW after one expert-parallel step, against the "
+                                "single-GPU kernels on the same rows; max |a - b| / max |b|", "tolerance": 1e-2, **errs,
+                        "ok": all(v <= 1e-2 for v in errs.values())}
+            del w_full
+        del xs_all, dys_all
+        barrier()
+
     # max over ranks
     times = torch.tensor([resident_ms, e2e_ms, float(np.mean(kernel_ms["fwd"])), float(np.mean(kernel_ms["dx"])),
                           float(np.mean(kernel_ms["dw"])), xchg_ms], device=dev, dtype=torch.float64)
@@ -811,28 +994,43 @@ def main():
         total_flops = len(per_kernel) * flops_one * world
         dominant = max(per_kernel, key=per_kernel.get)
         achieved = flops_one / (per_kernel[dominant] * 1e-3) / 1e12
-        peak = peaks["bf16_tflops_sustained"]
         alg_bytes = 2.0 * (M * K + E_local * N * K + M * N)
+        # Which measured cuBLAS figure the timed loop is comparable with: the sustained one only when the
+        # loop ran long enough for the power cap to act (>= 1 s) and the sampled SM clock sat below its
+        # maximum; a short loop at full clock is the burst regime.
+        timed_s = resident_ms * 1e-3 * args.steps
+        sm, sm_max = (clocks or {}).get("sm_mhz"), (clocks or {}).get("sm_max_mhz")
+        sustained = timed_s >= 1.0 and sm is not None and sm_max is not None and sm < 0.97 * sm_max
+        peak_name = "bf16_tflops_sustained" if sustained else "bf16_tflops"
+        peak = peaks[peak_name]
+        ratio, traffic_case = ncu_traffic_ratio(dominant) if args.gemm_path == "auto" and world == 1 else (None, "not captured for this configuration")
         line = {
             "metric": "moe_fused_linear fwd+dX+dW algorithmic TFLOP/s", "value": total_flops / (resident_ms * 1e-3) / 1e12,
             "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": n_warm, "ms_per_step": resident_ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": config_dict(args, cfg),
             "kernels": {name: {"ms": ms, "tflops": flops_one / (ms * 1e-3) / 1e12,
-                               "frac_of_sustained_peak": flops_one / (ms * 1e-3) / 1e12 / peak,
+                               "frac_of_sustained_peak": flops_one / (ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
                                "frac_of_burst_peak": flops_one / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
                                "frac_of_nominal_2250": flops_one / (ms * 1e-3) / 1e12 / 2250.0,
                                "algorithmic_gbs": alg_bytes / (ms * 1e-3) / 1e9}
                         for name, ms in per_kernel.items()},
             "roofline": {"bound": "tensor", "kernel": f"tc grouped gemm {dominant}", "achieved": achieved, "peak": peak,
-                         "unit": "TFLOP/s", "frac": achieved / peak, "peak_kind": f"bf16_tflops_sustained, {peaks_kind}",
-                         "traffic": NCU_TRAFFIC_RATIO[dominant] * alg_bytes if args.gemm_path == "auto" and world == 1 else None,
-                         "traffic_note": "ncu DRAM bytes of the reduced case scaled by units (profiles/pair_kernels_gate_up_16k_rows.md)",
+                         "unit": "TFLOP/s", "frac": achieved / peak, "peak_kind": f"{peak_name}, {peaks_kind}",
+                         "frac_of_burst_peak": achieved / peaks["bf16_tflops"],
+                         "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"],
+                         "regime": {"timed_region_s": timed_s, "sm_mhz_median": sm, "sm_max_mhz": sm_max,
+                                    "denominator": "sustained" if sustained else "burst",
+                                    # tensor work per SM clock: comparable across runs whose clocks differ
+                                    "flop_per_sm_clock": (flops_one / (per_kernel[dominant] * 1e-3) / (sm * 1e6)) if sm else None},
+                         "traffic": ratio * alg_bytes if ratio is not None else None,
+                         "traffic_note": f"ncu DRAM bytes / algorithmic bytes of the capture, scaled by units ({traffic_case})",
                          "algorithmic_bytes": alg_bytes},
             "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "note": "inputs double-buffered: the upload of step i+1 runs beside the compute of step i",
-                    "tokens_per_s": T * world / (e2e_ms * 1e-3)},
+                    "note": "inputs double-buffered: the upload of step i+1 runs beside the compute of step i; y, dX, dW and "
+                            "m_sizes of every step are copied back into pinned host memory inside the timed region",
+                    "tokens_per_s": T * world / (e2e_ms * 1e-3), "clocks": e2e_clocks},
             "gpu_launches": args.steps * (2 if args.only else launches_per_step),
             "tokens_per_s": T * world / (resident_ms * 1e-3),
             "clocks": clocks, "kernel_wait_errors": err_flag,
@@ -843,15 +1041,22 @@ def main():
         for name, ms in burst_ms.items():
             line["kernels"][name].update(isolated_ms=ms, isolated_tflops=flops_one / (ms * 1e-3) / 1e12,
                                          isolated_frac_of_burst_peak=flops_one / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"])
+        if ep_check is not None:
+            line["ep_check"] = ep_check
         if world > 1:
             line["exchange"] = {"what": "dispatch of x alone (rows to their experts' ranks), rank 0's remote bytes",
                                 "transport": args.ep_transport, "ms": xchg_ms, "remote_bytes": remote_bytes,
                                 "gbs_out": remote_bytes / (xchg_ms * 1e-3) / 1e9, "nvlink_peak_gbs_per_direction": 900.0}
+        if world == 1 and not args.no_extra and not args.only and args.workload == "gate_up" and not args.tokens and not args.experts:
+            line["extra_workloads"] = [measure_single_gpu_workload("down", min(args.steps, 50), args.warmup, dev)]
+            line["kernel_wait_errors"] = err_flag | _lib.read_error_flag()
         if world == 1 and not args.no_cpu_baseline:
             tf, dt, cores = cpu_reference_arm(cfg, 1, 0, args.cpu_rows)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                                     "sample": f"{args.cpu_rows} of {M} sorted rows, fp32, fwd+dX+dW row loops, 1 pass, {dt:.1f} s"}
         print(json.dumps(line), flush=True)
+        if ep_check is not None and not ep_check["ok"]:
+            raise SystemExit(f"expert-parallel results differ from the single-GPU kernels: {ep_check}")
     if world > 1:
         dist.destroy_process_group()
 
