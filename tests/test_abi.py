@@ -69,7 +69,7 @@ def test_sort_workspace_query(lib):
     assert lib.moe_sort_workspace_bytes(0, 128) == 128 * 4
     assert lib.moe_sort_workspace_bytes(2048, 128) == 2 * 128 * 4
     assert lib.moe_sort_workspace_bytes(2049, 128) == 3 * 128 * 4
-    assert lib.moe_grouped_gemm_workspace_bytes(0, 65536, 1536, 2048, 128) == 4 * 128 * 128
+    assert lib.moe_grouped_gemm_workspace_bytes(0, 65536, 1536, 2048, 128) == 3 * 128 * 128 + 128
 
 
 def test_gemm_path_switch(lib):

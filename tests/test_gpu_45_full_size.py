@@ -251,7 +251,7 @@ def test_moe_fused_linear_module(cuda):
     E, K, N, M = 16, 256, 384, 2000
     layer = MoeFusedLinear(K, N, E, device=cuda, dtype=torch.bfloat16)
     assert layer.weight.shape == (E, N, K)
-    assert float(layer.weight.float().abs().max()) <= (15 / K) ** 0.5 * (1 + 2.0 ** -8)
+    assert float(layer.weight.detach().float().abs().max()) <= (15 / K) ** 0.5 * (1 + 2.0 ** -8)
     assert "num_experts=16" in repr(layer)
     ms = np.random.default_rng(3).multinomial(M, np.ones(E) / E).astype(np.int32)
     ms[3] += ms[4]; ms[4] = 0

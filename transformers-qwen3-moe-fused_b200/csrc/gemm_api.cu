@@ -27,6 +27,7 @@ int tc_grouped_gemm_scattered(int which, const void* a, const void* b, const voi
 int tc_gate_up_silu(const void* x, const void* w_gate, const void* w_up, const void* m_sizes, int ms64, void* h,
                     int64_t M, int I, int K, int E, int dtype, void* ws, size_t ws_bytes, cudaStream_t stream);
 int tc_read_error(int* flag_out, bool clear);
+size_t tc_workspace_bytes(int E);
 const char* tc_last_detail();
 
 static std::atomic<int> g_path{MOE_PATH_AUTO};
@@ -93,8 +94,8 @@ MOE_API int moe_set_gemm_path(int path) {
 MOE_API int moe_get_gemm_path(void) { return g_path.load(); }
 
 MOE_API size_t moe_grouped_gemm_workspace_bytes(int, int64_t, int, int, int E) {
-  // room for up to four per-expert tensor maps (128 bytes each)
-  return E > 0 ? (size_t)4 * (size_t)E * 128 : 0;
+  // per-expert tensor maps derived from m_sizes on the device, and the launch's work-item counter
+  return tc_workspace_bytes(E);
 }
 
 MOE_API int moe_grouped_gemm_fwd(const void* x, const void* w, const void* m_sizes, int msd, void* y, int64_t M,

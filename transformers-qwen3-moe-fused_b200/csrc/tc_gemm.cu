@@ -14,6 +14,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 #include "tc_common.cuh"
 
@@ -40,9 +41,9 @@ struct GemmParams {
   uint32_t idesc;
   const CUtensorMap* group_maps;  // per-expert tensor maps in workspace ([slot][expert]), or null
   const int* weight_index = nullptr;  // weight slice of each group (null: group e uses slice e)
-  int debug;      // experiment switches (MOE_B200_DEBUG): 1 = no global stores, 2 = no TMEM loads, 4 = no MMA,
-                  // 32 = pair forward / dX without per-expert maps (register-store epilogue),
-                  // 64 = single-CTA NF4 kernel instead of the pair one
+  int* tile_counter = nullptr;  // work items are drawn from this counter (zeroed by build_group_maps_kernel); null: round-robin
+  int stages = 0;               // CTA-pair forward / dX: depth of the operand ring
+  int small_maps = 0;           // CTA-pair forward / dX: per-expert maps with the small token box exist (slot GM_IN_SMALL)
 };
 
 struct Control {
@@ -59,9 +60,10 @@ struct Control {
 enum WaitCode { W_EMPTY = 1, W_FULL = 2, W_TMEM_EMPTY = 3, W_TMEM_FULL = 4 };
 
 // Fills row_start[0..E] (first row of each group, saturated at M) and mt_start[0..E]
-// (number of BM-row tiles before each group).  Called by every thread of the CTA.
+// (number of tile_rows-row tiles before each group).  With `tail` > 0 the last tile of a group
+// may hold up to tile_rows + tail rows.  Called by every thread of the CTA.
 __device__ void build_group_tables(const void* m_sizes, int ms64, int E, int64_t M, int tile_rows,
-                                   int* row_start, int* mt_start) {
+                                   int* row_start, int* mt_start, int tail = 0) {
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int64_t v = load_index(m_sizes, ms64, e);
     v = v < 0 ? 0 : (v > M ? M : v);
@@ -86,7 +88,8 @@ __device__ void build_group_tables(const void* m_sizes, int ms64, int E, int64_t
       int64_t begin = end - v;
       end = end > M ? M : end;
       begin = begin > M ? M : begin;
-      const int tiles = (int)((end - begin + tile_rows - 1) / tile_rows);
+      const int64_t rows = end - begin;
+      const int tiles = rows <= 0 ? 0 : (rows <= tail ? 1 : (int)((rows - tail + tile_rows - 1) / tile_rows));
       int tincl = tiles;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
@@ -279,7 +282,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             // K-major: 16 elements = 32 bytes inside the swizzle row; MN-major: 16 rows of 128 B.
             const uint64_t a_adv = (uint64_t)((k * UMMA_K * 2) >> 4);
             const uint64_t b_adv = B_MN ? (uint64_t)((k * UMMA_K * 128) >> 4) : a_adv;
-            if (!(p.debug & 4)) umma_f16(d_tmem, da + a_adv, db + b_adv, p.idesc, (kb | k) != 0);
+            umma_f16(d_tmem, da + a_adv, db + b_adv, p.idesc, (kb | k) != 0);
           }
           umma_commit(&ctl->empty[s]);  // frees the stage when these MMAs have read it
         }
@@ -311,14 +314,9 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       for (int c = 0; c < BN; c += 32) {
         if (n0 + c >= p.N) break;  // warp-uniform
         uint32_t v[32];
-        if (!(p.debug & 2)) {
-          tmem_ld_32x32(taddr + c, v);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = c + i;
-        }
-        if (row_ok && !(p.debug & 1)) {
+        tmem_ld_32x32(taddr + c, v);
+        tmem_ld_wait();
+        if (row_ok) {
           const int ncols = min(32, p.N - (n0 + c));
           store_acc(p.out, p.dtype_out, grow * p.N + n0 + c, v, ncols, vec);
         }
@@ -630,11 +628,6 @@ bool tc_eligible(int which, const void* a, const void* b, const void* out, int64
 // The driver's tensor-map encoder needs a current context on the calling thread; threads
 // that have not yet issued a runtime call of this library (autograd worker threads) get the
 // primary context bound here, once per thread and device.
-static int debug_flags() {
-  static int v = []() { const char* e = getenv("MOE_B200_DEBUG"); return e ? atoi(e) : 0; }();
-  return v;
-}
-
 static void bind_context_once() {
   thread_local int bound = -1;
   int dev = 0;
@@ -671,6 +664,51 @@ static int launch_pair(void (*kernel)(KArgs...), int grid, int smem_bytes, cudaS
 template <typename... KArgs, typename... Args>
 static int launch_pair_threads(void (*kernel)(KArgs...), int grid, int threads, int smem_bytes, cudaStream_t stream, Args... args);
 
+// Workspace of the tensor-core grouped GEMMs: GroupMapTemplates::MAX per-expert tensor maps per expert
+// (slot-major, 128 bytes each), then the work-item counter of the launch.
+static size_t ws_maps_bytes(int E) { return (size_t)tc::GroupMapTemplates::MAX * (size_t)E * sizeof(CUtensorMap); }
+size_t tc_workspace_bytes(int E) { return E > 0 ? ws_maps_bytes(E) + 128 : 0; }
+static bool ws_usable(const void* ws, size_t ws_bytes, int E) {
+  return ws != nullptr && (((uintptr_t)ws & 127) == 0) && ws_bytes >= tc_workspace_bytes(E);
+}
+static int* ws_counter(void* ws, int E) { return reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(ws) + ws_maps_bytes(E)); }
+
+// Shared-memory footprint of the CTA-pair forward / dX kernels with `stages` ring slots.
+static int pair_smem_bytes(int stages, int E) {
+  using namespace tc;
+  return stages * PAIR_STAGE_BYTES + 4 * PAIR_STAGING_BYTES + (int)sizeof(PairControl) + 2 * (E + 1) * 4 + 1024;
+}
+// Deepest ring that fits (0: none does).
+static int pair_stages(int E) {
+  for (int st = tc::PAIR_MAX_STAGES; st >= 3; --st)
+    if (pair_smem_bytes(st, E) <= tc::SMEM_LIMIT) return st;
+  return 0;
+}
+
+// Launches build_group_maps_kernel for the forward / dX / gate-up kernels: per-expert copies of the
+// token maps (128-row and small box) and, for 16-bit outputs, of the output map.
+static int build_pair_maps(tc::GemmParams& p, const CUtensorMap& mx, const void* a, void* out, int dtype_in, int dtype_out,
+                           void* ws, cudaStream_t stream, const uint64_t* out_ptrs) {
+  using namespace tc;
+  GroupMapTemplates tm;
+  int st;
+  tm.mask = (1 << GM_IN) | (1 << GM_IN_SMALL);
+  tm.t[GM_IN] = mx;
+  if ((st = make_map(&tm.t[GM_IN_SMALL], dtype_in, a, (uint64_t)p.K, (uint64_t)p.M, 0, PAIR_SMALL_BOX)) != MOE_OK) return st;
+  if (dtype_out != MOE_F32) {
+    tm.mask |= 1 << GM_OUT;
+    if ((st = make_map(&tm.t[GM_OUT], dtype_out, out, (uint64_t)p.N, (uint64_t)p.M, 0, 32)) != MOE_OK) return st;
+  }
+  const int gm_smem = 8 * 128 + 2 * (p.E + 1) * 4 + 128;
+  build_group_maps_kernel<<<(p.E + 7) / 8, 256, gm_smem, stream>>>(tm, p.m_sizes, p.ms64, p.E, p.M, reinterpret_cast<CUtensorMap*>(ws),
+                                                                   ws_counter(ws, p.E), out_ptrs, GM_OUT, (int64_t)p.N * 2);
+  if ((st = launch_status()) != MOE_OK) return st;
+  p.group_maps = reinterpret_cast<const CUtensorMap*>(ws);
+  p.tile_counter = ws_counter(ws, p.E);
+  p.small_maps = 1;
+  return MOE_OK;
+}
+
 // `weight_index` / `n_weights` / `out_ptrs` (all optional) describe the scattered form: group e
 // multiplies by weight slice weight_index[e] of n_weights, and its output rows start at the
 // address out_ptrs[e] instead of row row_start[e] of `out`.
@@ -679,52 +717,44 @@ static int pair_grouped_gemm(int which, const void* a, const void* b, const void
                              cudaStream_t stream, const int* weight_index = nullptr, int n_weights = 0,
                              const uint64_t* out_ptrs = nullptr) {
   using namespace tc;
+  if (which != 0 && which != 1) return MOE_ERR_UNSUPPORTED;
   if (n_weights <= 0) n_weights = E;
   GemmParams p;
   p.weight_index = weight_index;
   p.a = a; p.b = b;
-  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags();
+  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out;
   const int fmt = dtype_in == MOE_BF16 ? 1 : 0;
   p.group_maps = nullptr;
+  // tile ids are 32-bit
+  if (((M + PAIR_TOKENS - 1) / PAIR_TOKENS + E) * (int64_t)((N + 255) / 256) >= (int64_t)1 << 30) return MOE_ERR_UNSUPPORTED;
   CUtensorMap mw, mx;
   int st;
-  if (which == 0 || which == 1) {
-    // A = weight (accumulator rows), B = activations (accumulator columns = tokens)
-    if (which == 0) st = make_map(&mw, dtype_in, b, (uint64_t)K, (uint64_t)N, (uint64_t)n_weights, 128);
-    else st = make_map(&mw, dtype_in, b, (uint64_t)N, (uint64_t)K, (uint64_t)n_weights, BK);
-    if (st != MOE_OK) return st;
-    if ((st = make_map(&mx, dtype_in, a, (uint64_t)K, (uint64_t)M, 0, 128)) != MOE_OK) return st;
-    p.idesc = make_idesc(fmt, which == 1, 0, 256, 0);  // N field is filled per tile
-    // Per-expert copies of the token and output maps (row extent = the group's last row): partial
-    // tiles then load no rows of the next expert, and 16-bit outputs can leave through TMA stores.
-    const bool ws_ok = ws != nullptr && (((uintptr_t)ws & 127) == 0) && ws_bytes >= (size_t)2 * E * sizeof(CUtensorMap);
-    if (ws_ok && (((uintptr_t)out & 15) == 0 || dtype_out == MOE_F32) && !(p.debug & 32)) {
-      GroupMapTemplates tm;
-      tm.count = dtype_out == MOE_F32 ? 1 : 2;
-      tm.t[GM_IN] = mx;
-      if (tm.count == 2 && (st = make_map(&tm.t[GM_OUT], dtype_out, out, (uint64_t)N, (uint64_t)M, 0, 32)) != MOE_OK) return st;
-      const int gm_smem = 8 * 128 + 2 * (E + 1) * 4 + 128;
-      build_group_maps_kernel<<<(E + 7) / 8, 256, gm_smem, stream>>>(tm, m_sizes, ms64, E, M, reinterpret_cast<CUtensorMap*>(ws),
-                                                                     out_ptrs, GM_OUT, (int64_t)N * 2);
-      if ((st = launch_status()) != MOE_OK) return st;
-      p.group_maps = reinterpret_cast<const CUtensorMap*>(ws);
-    }
-    // scattered outputs exist only as per-group output maps
-    if (out_ptrs != nullptr && (p.group_maps == nullptr || dtype_out == MOE_F32)) return MOE_ERR_UNSUPPORTED;
-    const int bytes = PAIR_STAGES * 2 * PAIR_HALF_BYTES + 4 * PAIR_STAGING_BYTES + (int)sizeof(PairControl) + 2 * (E + 1) * 4 + 1024;
-    if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
-    if (which == 0) {
-      if ((st = set_smem(pair_fwd_kernel<false>, bytes)) != MOE_OK) return st;
-      const int grid = 2 * resident_pairs(pair_fwd_kernel<false>, bytes);
-      pair_fwd_kernel<false><<<grid, PAIR_THREADS, bytes, stream>>>(mw, mx, p, mw);
-    } else {
-      if ((st = set_smem(pair_fwd_kernel<true>, bytes)) != MOE_OK) return st;
-      const int grid = 2 * resident_pairs(pair_fwd_kernel<true>, bytes);
-      pair_fwd_kernel<true><<<grid, PAIR_THREADS, bytes, stream>>>(mw, mx, p, mw);
-    }
-    return launch_status();
+  // A = weight (accumulator rows), B = activations (accumulator columns = tokens)
+  if (which == 0) st = make_map(&mw, dtype_in, b, (uint64_t)K, (uint64_t)N, (uint64_t)n_weights, 128);
+  else st = make_map(&mw, dtype_in, b, (uint64_t)N, (uint64_t)K, (uint64_t)n_weights, BK);
+  if (st != MOE_OK) return st;
+  if ((st = make_map(&mx, dtype_in, a, (uint64_t)K, (uint64_t)M, 0, 128)) != MOE_OK) return st;
+  p.idesc = make_idesc(fmt, which == 1, 0, 256, 0);  // N field is filled per tile
+  // Per-expert copies of the token and output maps (row extent = the group's last row): partial
+  // tiles then load no rows of the next expert, and 16-bit outputs can leave through TMA stores.
+  if (ws_usable(ws, ws_bytes, E) && (((uintptr_t)out & 15) == 0 || dtype_out == MOE_F32)) {
+    if ((st = build_pair_maps(p, mx, a, out, dtype_in, dtype_out, ws, stream, out_ptrs)) != MOE_OK) return st;
   }
-  return MOE_ERR_UNSUPPORTED;
+  // scattered outputs exist only as per-group output maps
+  if (out_ptrs != nullptr && (p.group_maps == nullptr || dtype_out == MOE_F32)) return MOE_ERR_UNSUPPORTED;
+  p.stages = pair_stages(E);
+  if (p.stages == 0) return MOE_ERR_UNSUPPORTED;
+  const int bytes = pair_smem_bytes(p.stages, E);
+  if (which == 0) {
+    if ((st = set_smem(pair_fwd_kernel<false>, bytes)) != MOE_OK) return st;
+    const int grid = 2 * resident_pairs(pair_fwd_kernel<false>, bytes);
+    pair_fwd_kernel<false><<<grid, PAIR_THREADS, bytes, stream>>>(mw, mx, p, mw);
+  } else {
+    if ((st = set_smem(pair_fwd_kernel<true>, bytes)) != MOE_OK) return st;
+    const int grid = 2 * resident_pairs(pair_fwd_kernel<true>, bytes);
+    pair_fwd_kernel<true><<<grid, PAIR_THREADS, bytes, stream>>>(mw, mx, p, mw);
+  }
+  return launch_status();
 }
 
 // Launch with a cluster of 2 CTAs.
@@ -753,18 +783,21 @@ static int dw_grouped_gemm(const void* x, const void* dy, const void* m_sizes, i
                            int K, int E, int dtype_in, int dtype_out, void* ws, size_t ws_bytes, cudaStream_t stream,
                            bool single_cta) {
   using namespace tc;
-  if (ws == nullptr || ((uintptr_t)ws & 127) || ws_bytes < (size_t)2 * E * sizeof(CUtensorMap)) return MOE_ERR_WORKSPACE;
+  if (!ws_usable(ws, ws_bytes, E)) return MOE_ERR_WORKSPACE;
   GemmParams p;
-  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags();
+  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out;
   p.group_maps = reinterpret_cast<const CUtensorMap*>(ws);
+  p.tile_counter = ws_counter(ws, E);
+  if ((int64_t)E * ((N + 127) / 128) * (int64_t)((K + 127) / 128) >= (int64_t)1 << 30) return MOE_ERR_UNSUPPORTED;  // 32-bit work-item ids
   const int fmt = dtype_in == MOE_BF16 ? 1 : 0;
   int st;
   GroupMapTemplates tm;
-  tm.count = 2;
+  tm.mask = (1 << GM_DY) | (1 << GM_X);
   if ((st = make_map(&tm.t[GM_DY], dtype_in, dy, (uint64_t)N, (uint64_t)M, 0, BK)) != MOE_OK) return st;
   if ((st = make_map(&tm.t[GM_X], dtype_in, x, (uint64_t)K, (uint64_t)M, 0, BK)) != MOE_OK) return st;
   const int gm_smem = 8 * 128 + 2 * (E + 1) * 4 + 128;
-  build_group_maps_kernel<<<(E + 7) / 8, 256, gm_smem, stream>>>(tm, m_sizes, ms64, E, M, reinterpret_cast<CUtensorMap*>(ws));
+  build_group_maps_kernel<<<(E + 7) / 8, 256, gm_smem, stream>>>(tm, m_sizes, ms64, E, M, reinterpret_cast<CUtensorMap*>(ws),
+                                                                 ws_counter(ws, E));
   if ((st = launch_status()) != MOE_OK) return st;
 
   const bool staged = dtype_out != MOE_F32;
@@ -825,7 +858,7 @@ int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes
     if (pair_ok) return pair_grouped_gemm(which, a, b, m_sizes, ms64, out, M, N, K, E, dtype_in, dtype_out, ws, ws_bytes, stream);
   }
   GemmParams p;
-  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags();
+  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out;
   const int fmt = dtype_in == MOE_BF16 ? 1 : 0;
   const int grid = sm_count();
   CUtensorMap ma, mb;
@@ -873,26 +906,21 @@ int tc_gate_up_silu(const void* x, const void* w_gate, const void* w_up, const v
                     int64_t M, int I, int K, int E, int dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
   using namespace tc;
   bind_context_once();
-  if (ws == nullptr || ((uintptr_t)ws & 127) || ws_bytes < (size_t)2 * E * sizeof(CUtensorMap)) return MOE_ERR_WORKSPACE;
+  if (!ws_usable(ws, ws_bytes, E)) return MOE_ERR_WORKSPACE;
   GemmParams p;
   p.a = x; p.b = w_gate;
-  p.m_sizes = m_sizes; p.out = h; p.M = M; p.N = I; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype; p.debug = debug_flags();
+  p.m_sizes = m_sizes; p.out = h; p.M = M; p.N = I; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype;
   p.idesc = make_idesc(dtype == MOE_BF16 ? 1 : 0, 0, 0, 256, 0);
+  if (((M + PAIR_TOKENS - 1) / PAIR_TOKENS + E) * (int64_t)((I + 127) / 128) >= (int64_t)1 << 30) return MOE_ERR_UNSUPPORTED;
   CUtensorMap mg, mu, mx;
   int st;
   if ((st = make_map(&mg, dtype, w_gate, (uint64_t)K, (uint64_t)I, (uint64_t)E, 16)) != MOE_OK) return st;
   if ((st = make_map(&mu, dtype, w_up, (uint64_t)K, (uint64_t)I, (uint64_t)E, 16)) != MOE_OK) return st;
   if ((st = make_map(&mx, dtype, x, (uint64_t)K, (uint64_t)M, 0, 128)) != MOE_OK) return st;
-  GroupMapTemplates tm;
-  tm.count = 2;
-  tm.t[GM_IN] = mx;
-  if ((st = make_map(&tm.t[GM_OUT], dtype, h, (uint64_t)I, (uint64_t)M, 0, 32)) != MOE_OK) return st;
-  const int gm_smem = 8 * 128 + 2 * (E + 1) * 4 + 128;
-  build_group_maps_kernel<<<(E + 7) / 8, 256, gm_smem, stream>>>(tm, m_sizes, ms64, E, M, reinterpret_cast<CUtensorMap*>(ws));
-  if ((st = launch_status()) != MOE_OK) return st;
-  p.group_maps = reinterpret_cast<const CUtensorMap*>(ws);
-  const int bytes = PAIR_STAGES * 2 * PAIR_HALF_BYTES + 4 * PAIR_STAGING_BYTES + (int)sizeof(PairControl) + 2 * (E + 1) * 4 + 1024;
-  if (bytes > SMEM_LIMIT) return MOE_ERR_UNSUPPORTED;
+  if ((st = build_pair_maps(p, mx, x, h, dtype, dtype, ws, stream, nullptr)) != MOE_OK) return st;
+  p.stages = pair_stages(E);
+  if (p.stages == 0) return MOE_ERR_UNSUPPORTED;
+  const int bytes = pair_smem_bytes(p.stages, E);
   auto kern = pair_fwd_kernel<false, true>;
   if ((st = set_smem(kern, bytes)) != MOE_OK) return st;
   const int grid = 2 * resident_pairs(kern, bytes);
@@ -926,7 +954,7 @@ int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code,
   using namespace tc;
   bind_context_once();
   GemmParams p;
-  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.debug = debug_flags(); p.group_maps = nullptr;
+  p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out; p.group_maps = nullptr;
   p.idesc = make_idesc(dtype_in == MOE_BF16 ? 1 : 0, 0, 0, BM, NF4_BN);
   if (transposed && N < 192) return MOE_ERR_UNSUPPORTED;  // only the CTA-pair kernel has the transposed decode
   Nf4Params q;
@@ -934,7 +962,7 @@ int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code,
   while ((1 << q.shift) < blocksize) ++q.shift;
   CUtensorMap ma, mq;
   int st;
-  if (N >= 192 && (transposed || !(p.debug & 64))) {
+  if (N >= 192) {
     // CTA-pair form: 128 weight rows of packed codes per CTA and stage (transposed: 64
     // contraction rows x 128 output features)
     EncodeTiledFn fn = encode_fn();
@@ -955,14 +983,16 @@ int tc_grouped_gemm_nf4(const void* x, const uint8_t* packed, const float* code,
     p.idesc = make_idesc(dtype_in == MOE_BF16 ? 1 : 0, transposed ? 1 : 0, 0, 256, 0);
     const int pbytes = NF4P_STAGES * NF4P_STAGE_BYTES + 4 * PAIR_STAGING_BYTES + (int)sizeof(Nf4PairControl) + 2 * (E + 1) * 4 + 1024;
     if (pbytes <= SMEM_LIMIT) {
-      const bool ws_ok = ws != nullptr && (((uintptr_t)ws & 127) == 0) && ws_bytes >= (size_t)2 * E * sizeof(CUtensorMap);
-      if (ws_ok && (((uintptr_t)out & 15) == 0 || dtype_out == MOE_F32) && !(p.debug & 32)) {
+      if (ws_usable(ws, ws_bytes, E) && (((uintptr_t)out & 15) == 0 || dtype_out == MOE_F32)) {
         GroupMapTemplates tm;
-        tm.count = dtype_out == MOE_F32 ? 1 : 2;
+        tm.mask = 1 << GM_IN;
         tm.t[GM_IN] = ma;
-        if (tm.count == 2 && (st = make_map(&tm.t[GM_OUT], dtype_out, out, (uint64_t)N, (uint64_t)M, 0, 32)) != MOE_OK) return st;
+        if (dtype_out != MOE_F32) {
+          tm.mask |= 1 << GM_OUT;
+          if ((st = make_map(&tm.t[GM_OUT], dtype_out, out, (uint64_t)N, (uint64_t)M, 0, 32)) != MOE_OK) return st;
+        }
         const int gm_smem = 8 * 128 + 2 * (E + 1) * 4 + 128;
-        build_group_maps_kernel<<<(E + 7) / 8, 256, gm_smem, stream>>>(tm, m_sizes, ms64, E, M, reinterpret_cast<CUtensorMap*>(ws));
+        build_group_maps_kernel<<<(E + 7) / 8, 256, gm_smem, stream>>>(tm, m_sizes, ms64, E, M, reinterpret_cast<CUtensorMap*>(ws), nullptr);
         if ((st = launch_status()) != MOE_OK) return st;
         p.group_maps = reinterpret_cast<const CUtensorMap*>(ws);
       }

@@ -13,40 +13,50 @@
 //   PAIR = false: one CTA per work item (expert, 128 weight rows, BN weight columns)
 //   PAIR = true : a CTA pair per work item (expert, 256 weight rows, 256 weight columns),
 //                 tcgen05 cta_group::2; both CTAs' loads complete on the leader's barrier
-// Work items are ordered by decreasing group size and dealt in snake order.  16-bit outputs
-// leave through a swizzled staging tile and TMA stores (the output has no ragged dimension;
-// TMA clips at N and K); fp32 outputs (single-CTA form only) are stored from registers.
+// Work items are ordered by decreasing group size and handed out one by one from a global
+// counter (drawn by the otherwise idle warp 1 of the non-leader CTA and passed to the working
+// roles through a ring in shared memory): longest items first onto whichever CTA pair is free,
+// so one expert with a quarter of the rows does not leave most of the GPU waiting for the few
+// pairs that drew its items.  Without a counter the items are dealt round-robin.
+// The last reduction block of an expert only issues the MMA k-steps that hold real rows.
+// 16-bit outputs leave through a swizzled staging tile and TMA stores (the output has no ragged
+// dimension; TMA clips at N and K); fp32 outputs (single-CTA form only) are stored from registers.
 #pragma once
 
 namespace moe {
 namespace tc {
 
 struct GroupMapTemplates {
-  CUtensorMap t[3];
-  int count;
+  static constexpr int MAX = 3;
+  CUtensorMap t[MAX];
+  int mask;  // bit t set: slot t is derived for every expert
 };
 
 // out[t * E + e] = templates.t[t] with the extent of dimension 1 (rows) set to the last row
-// of expert e (exclusive).  One warp per expert.
+// of expert e (exclusive), for every slot t of templates.mask.  One warp per expert.
+// Also resets the work-item counter of the GEMM launched after it.
 // With `out_ptrs`, slot `ptr_slot` of group e is additionally re-based so that row row_start[e]
 // of the map is the address out_ptrs[e]: each group's rows then land in a buffer of their own
 // (possibly in a peer GPU's memory) while the kernels keep addressing rows by their position in
 // the concatenated input.  `row_bytes` is the pitch of that slot's rows.
 __global__ void __launch_bounds__(256)
 build_group_maps_kernel(const __grid_constant__ GroupMapTemplates tm, const void* __restrict__ m_sizes, int ms64,
-                        int E, int64_t M, CUtensorMap* __restrict__ out,
+                        int E, int64_t M, CUtensorMap* __restrict__ out, int* __restrict__ counters,
                         const uint64_t* __restrict__ out_ptrs = nullptr, int ptr_slot = -1, int64_t row_bytes = 0) {
   extern __shared__ uint8_t gm_smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gm_smem_raw) + 127) & ~(uintptr_t)127);
   CUtensorMap* slots = reinterpret_cast<CUtensorMap*>(base);  // 8 slots, one per warp
   int* row_start = reinterpret_cast<int*>(base + 8 * 128);
   int* scratch = row_start + (E + 1);
+  // the GEMM that follows draws its work items from counters[0]
+  if (counters != nullptr && blockIdx.x == 0 && threadIdx.x == 0) counters[0] = 0;
   build_group_tables(m_sizes, ms64, E, M, 64, row_start, scratch);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int e = blockIdx.x * 8 + warp;
   if (e >= E) return;
   const uint32_t row_end = (uint32_t)max(row_start[e + 1], 1);
-  for (int t = 0; t < tm.count; ++t) {
+  for (int t = 0; t < GroupMapTemplates::MAX; ++t) {
+    if (!(tm.mask & (1 << t))) continue;
     reinterpret_cast<uint32_t*>(&slots[warp])[lane] = reinterpret_cast<const uint32_t*>(&tm.t[t])[lane];
     __syncwarp();
     if (lane == 0) {
@@ -73,6 +83,7 @@ struct DwControl {
   uint64_t empty[8];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  SchedRing sched;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -104,6 +115,7 @@ dw_kernel(const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 4 * NCTA); }
+    TileFeed<NCTA>::init(&ctl->sched);
     ctl->abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_out);
@@ -140,22 +152,36 @@ dw_kernel(const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
   const int n_tiles = (p.N + ROWS - 1) / ROWS;
   const int k_tiles = (p.K + BN - 1) / BN;
   const int per_expert = n_tiles * k_tiles;
-  const int64_t total_items = (int64_t)p.E * per_expert;
+  const int total_items = p.E * per_expert;
   const int G = PAIR ? (gridDim.x >> 1) : gridDim.x;
   const int unit = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
-  const int64_t rounds = (total_items + G - 1) / G;
-  auto item_of = [&](int64_t r) -> int64_t { return r * G + ((r & 1) ? (G - 1 - unit) : unit); };
-
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (elect_one()) {
+      TileFeed<NCTA> feed(&ctl->sched, abort_flag);
       const uint32_t full0 = PAIR ? map_to_cta(smem_u32(&ctl->full[0]), 0) : smem_u32(&ctl->full[0]);
       uint32_t it = 0;
       bool ok = true;
       int last_e = -1;
-      for (int64_t r = 0; r < rounds && ok; ++r) {
-        const int64_t item = item_of(r);
-        if (item >= total_items) continue;
+      // single-CTA form: this thread also draws the work items (the value of a draw is first looked
+      // at one item later, so that the atomic's round trip overlaps the loads in between)
+      uint32_t drawn = 0;
+      auto draw = [&]() -> int64_t {
+        const int64_t t = p.tile_counter ? (int64_t)atomicAdd(p.tile_counter, 1) : (int64_t)unit + (int64_t)drawn * G;
+        ++drawn;
+        return t;
+      };
+      int64_t next = PAIR ? 0 : draw();
+      while (ok) {
+        int item;
+        if constexpr (PAIR) {
+          item = feed.take();
+        } else {
+          item = next < total_items ? (int)next : -1;
+          if (!feed.publish(item)) break;
+          if (item >= 0) next = draw();
+        }
+        if (item < 0) break;
         const int e = sorted[item / per_expert];
         const int j = (int)(item % per_expert);
         const int n0 = (j % n_tiles) * ROWS + (int)rank * 128;
@@ -190,15 +216,25 @@ dw_kernel(const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA) ------------------------------
-    if (leader && elect_one()) {
+    if (!leader) {
+      // (CTA pairs only) this warp has no MMAs to issue in the non-leader CTA: it draws the work items
+      if (elect_one()) {
+        TileFeed<NCTA> feed(&ctl->sched, abort_flag);
+        feed.run(p.tile_counter, total_items, unit, G);
+      }
+    } else if (elect_one()) {
+      TileFeed<NCTA> feed(&ctl->sched, abort_flag);
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
-      for (int64_t r = 0; r < rounds && ok; ++r) {
-        const int64_t item = item_of(r);
-        if (item >= total_items) continue;
+      while (ok) {
+        const int item = feed.take();
+        if (item < 0) break;
         const int e = sorted[item / per_expert];
-        const int m_blocks = (row_start[e + 1] - row_start[e] + BK - 1) / BK;
+        const int rows = row_start[e + 1] - row_start[e];
+        const int m_blocks = (rows + BK - 1) / BK;
         if (m_blocks == 0) continue;  // empty expert: the epilogue writes zeros on its own
+        // rows of the last block past the expert's end are zero-filled by TMA: their k-steps are skipped
+        const int last_steps = (rows - (m_blocks - 1) * BK + UMMA_K - 1) / UMMA_K;
         const uint32_t acc = acc_it & 1;
         const uint32_t acc_ph = (acc_it >> 1) & 1;
         if (!mbar_wait_cluster(&ctl->tmem_empty[acc], acc_ph ^ 1, abort_flag, W_TMEM_EMPTY)) { ok = false; break; }
@@ -213,10 +249,11 @@ dw_kernel(const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
           const uint32_t sb = sa + 2 * CHUNK_BYTES;
           const uint64_t da = make_smem_desc(sa, CHUNK_BYTES, 1024);
           const uint64_t db = make_smem_desc(sb, CHUNK_BYTES, 1024);
+          const int steps = mb == m_blocks - 1 ? last_steps : BK / UMMA_K;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t adv = (uint64_t)((k * UMMA_K * 128) >> 4);
-            if (!(p.debug & 4)) {
+            if (k < steps) {
               if constexpr (PAIR) umma_f16_pair(d_tmem, da + adv, db + adv, p.idesc, (mb | k) != 0);
               else umma_f16(d_tmem, da + adv, db + adv, p.idesc, (mb | k) != 0);
             }
@@ -236,11 +273,12 @@ dw_kernel(const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
     const bool staged = p.dtype_out != MOE_F32;
     const bool is_bf16 = p.dtype_out == MOE_BF16;
     const bool vec = ((p.K * (int)dtype_size(p.dtype_out)) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    TileFeed<NCTA> feed(&ctl->sched, abort_flag);
     uint32_t acc_it = 0, chunk_it = 0;
     bool ok = true;
-    for (int64_t r = 0; r < rounds && ok; ++r) {
-      const int64_t item = item_of(r);
-      if (item >= total_items) continue;
+    while (ok) {
+      const int item = feed.take_warp(lane);
+      if (item < 0) break;
       const int e = sorted[item / per_expert];
       const int j = (int)(item % per_expert);
       const int n0 = (j % n_tiles) * ROWS + (int)rank * 128;
@@ -257,7 +295,7 @@ dw_kernel(const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
       for (int c = 0; c < BN / 64; ++c) {
         if (k0 + c * 64 >= p.K) break;  // uniform over the CTA
         uint32_t v[64];
-        if (rows > 0 && !(p.debug & 2)) {
+        if (rows > 0) {
           tmem_ld_32x32(taddr + c * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
           tmem_ld_32x32(taddr + c * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
           tmem_ld_wait();
@@ -268,7 +306,7 @@ dw_kernel(const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
         if (!staged) {
           // fp32 output: straight from registers
           const int n = n0 + row;
-          if (n < p.N && !(p.debug & 1)) {
+          if (n < p.N) {
             const int64_t o = ((int64_t)e * p.N + n) * p.K + k0 + c * 64;
             store_acc(p.out, p.dtype_out, o, *reinterpret_cast<uint32_t(*)[32]>(&v[0]), min(32, p.K - (k0 + c * 64)), vec);
             if (k0 + c * 64 + 32 < p.K)
@@ -299,7 +337,7 @@ dw_kernel(const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
         }
         fence_proxy_async_smem();
         named_barrier_sync(1, 128);
-        if (epi_tid == 0 && !(p.debug & 1)) {
+        if (epi_tid == 0) {
           tma_store_3d(&tmap_out, buf, k0 + c * 64, n0, e);  // rows / columns past N / K are clipped
           tma_store_commit();
         }

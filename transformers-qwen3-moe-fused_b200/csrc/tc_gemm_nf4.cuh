@@ -212,7 +212,7 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t adv = (uint64_t)((k * UMMA_K * 2) >> 4);
             const uint64_t a_adv = W_T ? (uint64_t)((k * UMMA_K * 128) >> 4) : adv;
-            if (!(p.debug & 4)) umma_f16_pair(d_tmem, da + a_adv, db + adv, idesc, (kb | k) != 0);
+            umma_f16_pair(d_tmem, da + a_adv, db + adv, idesc, (kb | k) != 0);
           }
           umma_commit_pair(&ctl->empty[s], 3);
         }
@@ -243,14 +243,14 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const uint32_t taddr = tmem_base + acc * PAIR_TOKENS + ((uint32_t)(quarter * 32) << 16);
       if (staged) {
         pair_store_tile_staged(staging, chunk_it, taddr, n_mma, quarter, lane, epi_tid, p.dtype_out == MOE_BF16, my,
-                               n0 + (int)rank * 128, t0, p.N, p.debug);
+                               n0 + (int)rank * 128, t0, p.N);
       } else {
 #pragma unroll 1
       for (int c = 0; c < n_mma; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32(taddr + c, v);
         tmem_ld_wait();
-        if (n_ok && !(p.debug & 1)) {
+        if (n_ok) {
           const int64_t base = (int64_t)(t0 + c) * p.N + n;
           const int valid = min(32, t_end - (t0 + c));
           if (p.dtype_out == MOE_BF16) {
@@ -331,14 +331,12 @@ pair_fwd_nf4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const uint32_t words[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
         uint8_t* dst_row = st + row * 128;
         const Nf4Planes pl = nf4_make_planes<IS_BF16>(code, am);
-        if (!(p.debug & 128)) {  // (experiment switch: hand-shake only, no decode work)
 #pragma unroll
-          for (int w = 0; w < 8; ++w) {  // 4 bytes -> 8 values -> one 16-byte chunk
-            uint32_t outw[4];
-            nf4_lookup4(pl, words[w] & 0xffffu, outw[0], outw[1]);
-            nf4_lookup4(pl, words[w] >> 16, outw[2], outw[3]);
-            *reinterpret_cast<uint4*>(dst_row + ((w ^ (row & 7)) << 4)) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
-          }
+        for (int w = 0; w < 8; ++w) {  // 4 bytes -> 8 values -> one 16-byte chunk
+          uint32_t outw[4];
+          nf4_lookup4(pl, words[w] & 0xffffu, outw[0], outw[1]);
+          nf4_lookup4(pl, words[w] >> 16, outw[2], outw[3]);
+          *reinterpret_cast<uint4*>(dst_row + ((w ^ (row & 7)) << 4)) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
         }
         fence_proxy_async_smem();
         __syncwarp();

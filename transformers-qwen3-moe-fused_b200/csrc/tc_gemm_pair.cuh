@@ -9,34 +9,75 @@
 //
 // Forward / dX are computed "swapped": the accumulator rows are WEIGHT rows (always a full
 // 256-row slice) and the accumulator columns are TOKENS, so the ragged dimension becomes the
-// MMA's N extent, which is chosen per tile in steps of 16.  An expert with 520 rows costs
-// 256 + 256 + 16 token columns instead of five 128-row tiles.
+// MMA's N extent, which is chosen per tile in steps of 16.
 //
 //   pair_fwd_kernel<false>: y[t,n] = sum_k w[e,n,k] x[t,k]   A = w (K-major),  B = x (K-major)
 //   pair_fwd_kernel<true> : y[t,n] = sum_k w[e,k,n] x[t,k]   A = w (MN-major), B = x (K-major)
+//
+// Tiles with a tail.  Streaming a 256 x K weight slice through shared memory costs the same
+// for 16 tokens as for 256, so an expert with 520 rows must not become 256 + 256 + 8: its
+// last tile carries the extra tokens as a second, narrow MMA on the same weight stage
+// ("main" up to 256 columns + "tail" up to PAIR_TAIL columns).  TMEM has 512 columns, exactly
+// two main accumulators, so the tails live inside the OTHER accumulator's column range:
+//
+//     columns   0 ........ 256-T | 256-T .. 256 | 256 .. 256+T | 256+T ........ 512
+//     region          E0         |      RA      |      RB      |        E1
+//     even tile   main ................main      | tail         |
+//     odd tile                   | tail         | main ................ main
+//
+// Each region has its own "drained" barrier.  The epilogue drains the two contested regions
+// first, so the next tile's MMAs wait for one or two 32-column rounds of the epilogue, not for
+// all of it; tiles without a tail never wait for each other.
+//
+// Tile order.  Tiles are handed out in index order from a global counter (one atomicAdd per
+// tile, by a thread that has nothing else to do: warp 1 of the non-leader CTA), and travel to
+// the working roles of both CTAs through a small ring in shared memory, several tiles ahead of
+// their use: ragged groups make tile costs uneven, and a static round-robin left a fifth of
+// the pairs idle at the end.  Without a counter (no workspace) the same ring carries a static
+// round-robin order.
 #pragma once
 
 namespace moe {
 namespace tc {
 
+#ifndef MOE_PAIR_TAIL
+#define MOE_PAIR_TAIL 32
+#endif
 constexpr int PAIR_THREADS = 192;
-constexpr int PAIR_STAGES = 6;
-constexpr int PAIR_TOKENS = 256;             // token columns per tile (MMA N), upper bound
+constexpr int PAIR_MAX_STAGES = 6;
+constexpr int PAIR_TOKENS = 256;               // main token columns per tile (MMA N), upper bound
+constexpr int PAIR_TAIL = MOE_PAIR_TAIL;       // extra token columns the last tile of an expert may carry
 constexpr int PAIR_HALF_BYTES = 128 * BK * 2;  // 16 KB: 128 rows x 64 x 16-bit
+constexpr int PAIR_TAIL_BYTES = (PAIR_TAIL / 2) * BK * 2;           // this CTA's half of the tail tokens
+constexpr int PAIR_STAGE_BYTES = 2 * PAIR_HALF_BYTES + PAIR_TAIL_BYTES;
+constexpr int PAIR_SMALL_BOX = 16;             // token rows of the small TMA box (tails and narrow tiles)
+constexpr int SCHED_DEPTH = 8;                 // tile ids in flight between the producer and the other roles
+static_assert(PAIR_TAIL % 32 == 0 && PAIR_TAIL <= 64, "regions are drained in rounds of 32 columns");
+static_assert(PAIR_STAGE_BYTES % 1024 == 0, "stages keep the 1024-byte alignment of the swizzle atoms");
+
+// Ring that carries tile ids from the thread that draws them to the other roles.
+struct SchedRing {
+  uint64_t full[SCHED_DEPTH];
+  uint64_t empty[SCHED_DEPTH];  // the leader CTA's copies are the ones used
+  int tile[SCHED_DEPTH];
+};
 
 struct PairControl {
   uint64_t full[8];
   uint64_t empty[8];
   uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
+  uint64_t tmem_free[4];            // regions E0, RA, RB, E1 (leader CTA's copies are the ones used)
+  SchedRing sched;
   uint32_t tmem_base;
   int abort_flag;
 };
 
-enum { GM_IN = 0, GM_OUT = 1 };            // per-expert tensor-map slots of the forward / dX kernels
+enum { GM_IN = 0, GM_OUT = 1, GM_IN_SMALL = 2 };  // per-expert tensor-map slots of the forward / dX kernels
+enum { REG_E0 = 0, REG_RA = 1, REG_RB = 2, REG_E1 = 3 };
 constexpr int PAIR_STAGING_BYTES = 32 * 128;  // 32 tokens x 64 weight rows x 16 bit
 
-enum PairWaitCode { PW_EMPTY = 11, PW_FULL = 12, PW_TMEM_EMPTY = 13, PW_TMEM_FULL = 14, PW_PEER = 15 };
+enum PairWaitCode { PW_EMPTY = 11, PW_FULL = 12, PW_TMEM_EMPTY = 13, PW_TMEM_FULL = 14, PW_PEER = 15,
+                    PW_SCHED_FULL = 17, PW_SCHED_EMPTY = 18 };
 
 template <typename T>
 __device__ __forceinline__ void store_scalar(void* out, int64_t idx, float v) {
@@ -51,7 +92,7 @@ __device__ __forceinline__ void store_scalar(void* out, int64_t idx, float v) {
 // threads (warps 2..5); `staging` holds 4 * PAIR_STAGING_BYTES.
 __device__ __forceinline__ void pair_store_tile_staged(uint8_t* staging, uint32_t& chunk_it, uint32_t taddr, int n_mma,
                                                        int quarter, int lane, int epi_tid, bool is_bf16,
-                                                       const CUtensorMap* my, int n_cta, int t0, int N, int debug) {
+                                                       const CUtensorMap* my, int n_cta, int t0, int N) {
   const int half = quarter >> 1;
   const int chunk = 4 * (quarter & 1) + (lane >> 3);  // 16-byte chunk of the 128-byte staging row
 #pragma unroll 1
@@ -60,14 +101,9 @@ __device__ __forceinline__ void pair_store_tile_staged(uint8_t* staging, uint32_
     if (epi_tid == 0) tma_store_wait_read<1>();  // the stores of two rounds ago have read this buffer
     named_barrier_sync(1, 128);
     uint32_t lo[16], hi[16];
-    if (!(debug & 2)) {
-      tmem_ld_16x256b_x4(taddr + c, lo);
-      tmem_ld_16x256b_x4(taddr + c + (16u << 16), hi);
-      tmem_ld_wait();
-    } else {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) { lo[i] = 0; hi[i] = 0; }
-    }
+    tmem_ld_16x256b_x4(taddr + c, lo);
+    tmem_ld_16x256b_x4(taddr + c + (16u << 16), hi);
+    tmem_ld_wait();
     uint8_t* tile_buf = buf + half * PAIR_STAGING_BYTES;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -88,7 +124,7 @@ __device__ __forceinline__ void pair_store_tile_staged(uint8_t* staging, uint32_
     }
     fence_proxy_async_smem();
     named_barrier_sync(1, 128);
-    if (epi_tid == 0 && !(debug & 1)) {
+    if (epi_tid == 0) {
       tma_store_2d(my, buf, n_cta, t0 + c);
       if (n_cta + 64 < N) tma_store_2d(my, buf + PAIR_STAGING_BYTES, n_cta + 64, t0 + c);
       tma_store_commit();
@@ -114,7 +150,7 @@ __device__ __forceinline__ float gate_up_one(float acc_gate, float acc_up) {
 // 8 tokens); the CTA's four warps fill a [32 tokens][64 features] tile that leaves by TMA.
 __device__ __forceinline__ void pair_store_tile_gate_up(uint8_t* staging, uint32_t& chunk_it, uint32_t taddr, int n_mma,
                                                         int quarter, int lane, int epi_tid, bool is_bf16,
-                                                        const CUtensorMap* my, int feat_cta, int t0, int n_feat, int debug) {
+                                                        const CUtensorMap* my, int feat_cta, int t0, int n_feat) {
   const int chunk = 2 * quarter + ((lane >> 3) & 1);  // 16-byte chunk of the 128-byte staging row
 #pragma unroll 1
   for (int c = 0; c < n_mma; c += 32, ++chunk_it) {
@@ -140,11 +176,88 @@ __device__ __forceinline__ void pair_store_tile_gate_up(uint8_t* staging, uint32
     }
     fence_proxy_async_smem();
     named_barrier_sync(1, 128);
-    if (epi_tid == 0 && !(debug & 1)) {
+    if (epi_tid == 0) {
       if (feat_cta < n_feat) tma_store_2d(my, buf, feat_cta, t0 + c);  // columns past the last feature are clipped
       tma_store_commit();
     }
   }
+}
+
+// Tile ids travel from the thread that draws them to every role that works on the tile.
+// Slot q of the ring holds one id; `full[q]` (one per CTA) says it is there, `empty[q]` (the copy
+// in the drawing thread's CTA; one arrival per reader) says everybody has read it.
+//   NCTA = 2: the drawing thread is a thread of its own (warp 1 of the non-leader CTA, which has no
+//             MMAs to issue); readers: both producers, the MMA thread, 8 epilogue warps.  It runs up
+//             to SCHED_DEPTH tiles ahead, so the round trip of its atomicAdd is never waited for.
+//   NCTA = 1: the producer thread draws for itself; readers: the MMA thread, 4 epilogue warps.
+template <int NCTA>
+struct TileFeed {
+  static constexpr int READERS = NCTA == 2 ? 11 : 5;
+  static constexpr uint32_t HOME = NCTA == 2 ? 1 : 0;  // CTA of the drawing thread
+  SchedRing* ring;
+  uint32_t home_empty0;  // address of the home CTA's empty[0] (shared::cluster window when NCTA = 2)
+  uint32_t n = 0;        // sequence number of the next tile of this CTA / pair
+  volatile int* abort_flag;
+
+  __device__ __forceinline__ TileFeed(SchedRing* r, volatile int* a)
+      : ring(r), home_empty0(NCTA == 2 ? map_to_cta(smem_u32(&r->empty[0]), HOME) : smem_u32(&r->empty[0])), abort_flag(a) {}
+
+  static __device__ __forceinline__ void init(SchedRing* r) {  // one thread per CTA, before the barriers are used
+    for (int q = 0; q < SCHED_DEPTH; ++q) { mbar_init(&r->full[q], 1); mbar_init(&r->empty[q], READERS); }
+  }
+  // drawing thread: make `tile` (or -1: no more tiles) visible to every reader
+  __device__ __forceinline__ bool publish(int tile) {
+    const uint32_t q = n % SCHED_DEPTH, ph = (n / SCHED_DEPTH) & 1;
+    if (!mbar_wait_cluster(&ring->empty[q], ph ^ 1, abort_flag, PW_SCHED_EMPTY)) return false;
+    ring->tile[q] = tile;
+    if constexpr (NCTA == 2) {
+      st_shared_cluster_u32(map_to_cta(smem_u32(&ring->tile[q]), HOME ^ 1), (uint32_t)tile);
+      mbar_arrive_release_cluster(map_to_cta(smem_u32(&ring->full[q]), 0));
+      mbar_arrive_release_cluster(map_to_cta(smem_u32(&ring->full[q]), 1));
+    } else {
+      mbar_arrive(&ring->full[q]);
+    }
+    ++n;
+    return true;
+  }
+  // Body of the drawing thread when it has nothing else to do (NCTA = 2): ids come from the global
+  // counter, or round-robin (first, first + stride, ...) without one.
+  __device__ __forceinline__ void run(int* counter, int total, int first, int stride) {
+    for (int64_t next = first;; next += stride) {
+      const int64_t t = counter ? (int64_t)atomicAdd(counter, 1) : next;
+      const int tile = t < total ? (int)t : -1;
+      if (!publish(tile) || tile < 0) return;
+    }
+  }
+  // a reader (one thread): next tile id, or -1 when there are no more (or the wait was abandoned)
+  __device__ __forceinline__ int take() {
+    const uint32_t q = n % SCHED_DEPTH, ph = (n / SCHED_DEPTH) & 1;
+    if (!mbar_wait_cluster(&ring->full[q], ph, abort_flag, PW_SCHED_FULL)) return -1;
+    const int tile = *(volatile int*)&ring->tile[q];
+    if constexpr (NCTA == 2) mbar_arrive_cluster(home_empty0 + q * 8);
+    else mbar_arrive(&ring->empty[q]);
+    ++n;
+    return tile;
+  }
+  // a whole warp: lane 0 takes the id and signs the slot off for the warp
+  __device__ __forceinline__ int take_warp(int lane) {
+    int tile = 0;
+    if (lane == 0) tile = take();
+    return __shfl_sync(0xffffffffu, tile, 0);
+  }
+};
+
+struct PairTile {
+  int e, t0, n0;       // expert, first token row, first weight row (output column) of the pair
+  int n_main, n_tail;  // token columns of the two MMAs, multiples of 16 (n_tail may be 0)
+  int t_end;           // first row past the expert
+};
+
+// Regions (bit r of the result) whose columns a tile of the given parity writes.
+__device__ __forceinline__ uint32_t pair_regions(uint32_t parity, int n_main, int n_tail) {
+  if (parity == 0)
+    return (1u << REG_E0) | (n_main > PAIR_TOKENS - PAIR_TAIL ? 1u << REG_RA : 0u) | (n_tail > 0 ? 1u << REG_RB : 0u);
+  return (1u << REG_RB) | (n_main > PAIR_TAIL ? 1u << REG_E1 : 0u) | (n_tail > 0 ? 1u << REG_RA : 0u);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -161,9 +274,9 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 const GemmParams p, const __grid_constant__ CUtensorMap tmap_w2) {
   static_assert(!(W_MN && GATE_UP), "the fused gate/up form reads K-major weights");
   constexpr int TILE_N = GATE_UP ? 128 : 256;  // output columns (features) per pair
-  constexpr int STAGE_BYTES = 2 * PAIR_HALF_BYTES;  // A half-tile + B half-tile per CTA
-  constexpr int STAGES = PAIR_STAGES;
-  constexpr uint32_t TMEM_COLS = 512;  // two accumulators of up to 256 token columns
+  constexpr int STAGE_BYTES = PAIR_STAGE_BYTES;
+  constexpr uint32_t TMEM_COLS = 512;
+  const int STAGES = p.stages;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -177,10 +290,15 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
+  // tails and small boxes need the per-expert small-box maps
+  const bool small_maps = p.group_maps != nullptr && p.small_maps;
+  const int tail = small_maps ? PAIR_TAIL : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 8); }
+    for (int a = 0; a < 2; ++a) mbar_init(&ctl->tmem_full[a], 1);
+    for (int r = 0; r < 4; ++r) mbar_init(&ctl->tmem_free[r], 8);
+    TileFeed<2>::init(&ctl->sched);
     ctl->abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_w);
@@ -190,7 +308,7 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     tmem_alloc_pair(&ctl->tmem_base, TMEM_COLS);
     tmem_relinquish_pair();
   }
-  build_group_tables(p.m_sizes, p.ms64, p.E, p.M, PAIR_TOKENS, row_start, tt_start);
+  build_group_tables(p.m_sizes, p.ms64, p.E, p.M, PAIR_TOKENS, row_start, tt_start, tail);
   tc_fence_before_sync();
   cluster_sync_all();  // barriers of both CTAs are initialised before anybody signals them
   tc_fence_after_sync();
@@ -202,44 +320,73 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
-  // tile -> (expert, first token, token columns rounded up to 16, first weight row)
-  auto decode = [&](int64_t tile, int& e, int& t0, int& n_mma, int& n0) {
-    const int q = (int)(tile / n_tiles);
-    e = find_group(tt_start, p.E, q);
-    const int tt_e = tt_start[e + 1] - tt_start[e];
-    const int j = (int)(tile - (int64_t)tt_start[e] * n_tiles);
-    t0 = row_start[e] + (j % tt_e) * PAIR_TOKENS;
-    n0 = (j / tt_e) * TILE_N;
-    const int left = row_start[e + 1] - t0;
-    n_mma = left >= PAIR_TOKENS ? PAIR_TOKENS : ((left + 15) & ~15);
+  // tile index -> tile.  Within an expert the token tile varies fastest, so neighbouring tiles
+  // (which run at about the same time) read the same weight slice.
+  auto decode = [&](int tile) {
+    PairTile t;
+    const int q = tile / n_tiles;
+    t.e = find_group(tt_start, p.E, q);
+    const int tt_e = tt_start[t.e + 1] - tt_start[t.e];
+    const int j = tile - tt_start[t.e] * n_tiles;
+    const int jt = j % tt_e;
+    t.t0 = row_start[t.e] + jt * PAIR_TOKENS;
+    t.n0 = (j / tt_e) * TILE_N;
+    t.t_end = row_start[t.e + 1];
+    const int left = t.t_end - t.t0;
+    if (left >= PAIR_TOKENS) {
+      t.n_main = PAIR_TOKENS;
+      t.n_tail = (jt == tt_e - 1) ? ((left - PAIR_TOKENS + 15) & ~15) : 0;  // at most `tail` by the tile count
+    } else {
+      t.n_main = (left + 15) & ~15;
+      t.n_tail = 0;
+    }
+    return t;
   };
+  // B-operand loads of one stage: rows of this CTA's half of the main tokens, in boxes of 128 or of
+  // PAIR_SMALL_BOX rows, and bytes both CTAs' loads of the stage bring in
+  auto main_small_boxes = [&](int n_main) {  // 0: one 128-row box
+    const int rows = n_main >> 1;
+    return (small_maps && rows <= 64) ? (rows + PAIR_SMALL_BOX - 1) / PAIR_SMALL_BOX : 0;
+  };
+  auto tail_boxes = [&](int n_tail) { return ((n_tail >> 1) + PAIR_SMALL_BOX - 1) / PAIR_SMALL_BOX; };
 
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
     if (elect_one()) {
+      TileFeed<2> feed(&ctl->sched, abort_flag);
       const uint32_t full_leader0 = map_to_cta(smem_u32(&ctl->full[0]), 0);
       uint32_t it = 0;
+      int s = 0;
+      uint32_t ph = 0;
       bool ok = true;
       int last_e = -1;
-      for (int64_t tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
-        int e, t0, n_mma, n0;
-        decode(tile, e, t0, n_mma, n0);
-        const int we = p.weight_index ? __ldg(p.weight_index + e) : e;  // several groups may share a weight slice
-        const int w_row = n0 + (int)rank * 128;
-        const int tok = t0 + (int)rank * (n_mma >> 1);
+      while (ok) {
+        const int tile = feed.take();
+        if (tile < 0) break;
+        const PairTile t = decode(tile);
+        const int we = p.weight_index ? __ldg(p.weight_index + t.e) : t.e;  // several groups may share a weight slice
+        const int w_row = t.n0 + (int)rank * 128;
+        const int tok = t.t0 + (int)rank * (t.n_main >> 1);
+        const int tok_tail = t.t0 + PAIR_TOKENS + (int)rank * (t.n_tail >> 1);
         // with per-expert maps the token rows past the group's end are zero-filled, not fetched
-        const CUtensorMap* mx = p.group_maps ? p.group_maps + (size_t)GM_IN * p.E + e : &tmap_x;
-        if (p.group_maps && e != last_e) { tensormap_acquire(mx); last_e = e; }
+        const CUtensorMap* mx = p.group_maps ? p.group_maps + (size_t)GM_IN * p.E + t.e : &tmap_x;
+        const CUtensorMap* ms = small_maps ? p.group_maps + (size_t)GM_IN_SMALL * p.E + t.e : nullptr;
+        if (p.group_maps && t.e != last_e) {
+          tensormap_acquire(mx);
+          if (ms) tensormap_acquire(ms);
+          last_e = t.e;
+        }
+        const int nsb = main_small_boxes(t.n_main);
+        const int ntb = tail_boxes(t.n_tail);
+        const uint32_t b_bytes = (nsb ? nsb * PAIR_SMALL_BOX * BK * 2 : PAIR_HALF_BYTES) + ntb * PAIR_SMALL_BOX * BK * 2;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, PW_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + s * STAGE_BYTES;
           uint8_t* sb = sa + PAIR_HALF_BYTES;
           const uint32_t bar = full_leader0 + s * 8;
-          if (leader) mbar_expect_tx(&ctl->full[s], 2 * STAGE_BYTES);  // both CTAs' bytes
+          if (leader) mbar_expect_tx(&ctl->full[s], 2 * (PAIR_HALF_BYTES + b_bytes));  // both CTAs' bytes
           if constexpr (GATE_UP) {
-            const int feat = n0 + (int)rank * 64;  // this CTA's 64 features
+            const int feat = t.n0 + (int)rank * 64;  // this CTA's 64 features
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               tma_load_3d_pair(sa + (2 * q) * 2048, &tmap_w, bar, kb * BK, feat + 16 * q, we);
@@ -251,108 +398,174 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             tma_load_3d_pair(sa, &tmap_w, bar, w_row, kb * BK, we);
             tma_load_3d_pair(sa + BK * 128, &tmap_w, bar, w_row + 64, kb * BK, we);
           }
-          tma_load_2d_pair(sb, mx, bar, kb * BK, tok);
+          if (nsb == 0) {
+            tma_load_2d_pair(sb, mx, bar, kb * BK, tok);
+          } else {
+            for (int b = 0; b < nsb; ++b)
+              tma_load_2d_pair(sb + b * (PAIR_SMALL_BOX * BK * 2), ms, bar, kb * BK, tok + b * PAIR_SMALL_BOX);
+          }
+          for (int b = 0; b < ntb; ++b)
+            tma_load_2d_pair(sb + PAIR_HALF_BYTES + b * (PAIR_SMALL_BOX * BK * 2), ms, bar, kb * BK, tok_tail + b * PAIR_SMALL_BOX);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------ MMA issuer (leader CTA only) ------------------------------
-    if (leader && elect_one()) {
-      uint32_t it = 0, acc_it = 0;
+    // ------------- MMA issuer (leader CTA); the same warp of the other CTA draws the tiles -------------
+    if (!leader) {
+      if (elect_one()) {
+        TileFeed<2> feed(&ctl->sched, abort_flag);
+        feed.run(p.tile_counter, (int)total_tiles, pair_id, num_pairs);
+      }
+    } else if (elect_one()) {
+      TileFeed<2> feed(&ctl->sched, abort_flag);
+      uint32_t seq = 0;
+      uint32_t uses[4] = {0, 0, 0, 0};  // how often each TMEM region has been written so far
+      int s = 0;
+      uint32_t ph = 0;
       bool ok = true;
-      for (int64_t tile = pair_id; tile < total_tiles && ok; tile += num_pairs, ++acc_it) {
-        int e, t0, n_mma, n0;
-        decode(tile, e, t0, n_mma, n0);
-        const uint32_t idesc = p.idesc | ((uint32_t)(n_mma >> 3) << 17);
-        const uint32_t acc = acc_it & 1;
-        const uint32_t acc_ph = (acc_it >> 1) & 1;
-        if (!mbar_wait_cluster(&ctl->tmem_empty[acc], acc_ph ^ 1, abort_flag, PW_TMEM_EMPTY)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * PAIR_TOKENS;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait_cluster(&ctl->full[s], ph, abort_flag, PW_FULL)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-          const uint32_t sb = sa + PAIR_HALF_BYTES;
-          const uint64_t da = W_MN ? make_smem_desc(sa, BK * 128, 1024) : make_smem_desc(sa, 16, 1024);
-          const uint64_t db = make_smem_desc(sb, 16, 1024);
+      while (ok) {
+        const int tile = feed.take();
+        if (tile < 0) break;
+        const PairTile t = decode(tile);
+        const uint32_t par = seq & 1;
+        const uint32_t idesc_main = p.idesc | ((uint32_t)(t.n_main >> 3) << 17);
+        const uint32_t idesc_tail = p.idesc | ((uint32_t)(t.n_tail >> 3) << 17);
+        // every region this tile writes must have been drained by its previous user
+        const uint32_t regs = pair_regions(par, t.n_main, t.n_tail);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t b_adv = (uint64_t)((k * UMMA_K * 2) >> 4);
-            const uint64_t a_adv = W_MN ? (uint64_t)((k * UMMA_K * 128) >> 4) : b_adv;
-            if (!(p.debug & 4)) umma_f16_pair(d_tmem, da + a_adv, db + b_adv, idesc, (kb | k) != 0);
-          }
-          umma_commit_pair(&ctl->empty[s], 3);
+        for (int r = 0; r < 4; ++r) {
+          if (!(regs & (1u << r))) continue;
+          if (ok && !mbar_wait_cluster(&ctl->tmem_free[r], (uses[r] & 1) ^ 1, abort_flag, PW_TMEM_EMPTY)) ok = false;
+          ++uses[r];
         }
-        if (ok) umma_commit_pair(&ctl->tmem_full[acc], 3);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_main = tmem_base + (par ? PAIR_TOKENS : 0);
+        const uint32_t d_tail = tmem_base + (par ? PAIR_TOKENS - PAIR_TAIL : PAIR_TOKENS);
+        // Two copies of the k-loop, with and without the tail MMAs: a test of n_tail between the
+        // MMAs of one loop costs the issuing thread a quarter of its rate.
+        auto k_loop = [&](auto has_tail) {
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!mbar_wait_cluster(&ctl->full[s], ph, abort_flag, PW_FULL)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+            const uint32_t sb = sa + PAIR_HALF_BYTES;
+            const uint64_t da = W_MN ? make_smem_desc(sa, BK * 128, 1024) : make_smem_desc(sa, 16, 1024);
+            const uint64_t db = make_smem_desc(sb, 16, 1024);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t b_adv = (uint64_t)((k * UMMA_K * 2) >> 4);
+              const uint64_t a_adv = W_MN ? (uint64_t)((k * UMMA_K * 128) >> 4) : b_adv;
+              umma_f16_pair(d_main, da + a_adv, db + b_adv, idesc_main, (kb | k) != 0);
+            }
+            if constexpr (decltype(has_tail)::value) {
+              const uint64_t dbt = make_smem_desc(sb + PAIR_HALF_BYTES, 16, 1024);
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k) {
+                const uint64_t b_adv = (uint64_t)((k * UMMA_K * 2) >> 4);
+                const uint64_t a_adv = W_MN ? (uint64_t)((k * UMMA_K * 128) >> 4) : b_adv;
+                umma_f16_pair(d_tail, da + a_adv, dbt + b_adv, idesc_tail, (kb | k) != 0);
+              }
+            }
+            umma_commit_pair(&ctl->empty[s], 3);
+            if (++s == STAGES) { s = 0; ph ^= 1; }
+          }
+        };
+        if (t.n_tail) k_loop(std::true_type{}); else k_loop(std::false_type{});
+        if (ok) umma_commit_pair(&ctl->tmem_full[par], 3);
+        ++seq;
       }
     }
   } else {
     // ------------------------------ epilogue (both CTAs) ------------------------------
+    TileFeed<2> feed(&ctl->sched, abort_flag);
     const int quarter = warp & 3;
     const int epi_tid = threadIdx.x - 64;  // 0..127
-    const uint32_t tmem_empty_leader0 = map_to_cta(smem_u32(&ctl->tmem_empty[0]), 0);
+    const uint32_t tmem_free_leader0 = map_to_cta(smem_u32(&ctl->tmem_free[0]), 0);
     // 16-bit outputs with per-expert output maps leave through shared memory and TMA stores
     const bool staged = p.group_maps != nullptr && p.dtype_out != MOE_F32;
     const bool is_bf16 = p.dtype_out == MOE_BF16;
-    uint32_t acc_it = 0, chunk_it = 0;
+    uint32_t seq = 0, chunk_it = 0;
     int last_e = -1;
-    bool ok = true;
-    for (int64_t tile = pair_id; tile < total_tiles && ok; tile += num_pairs, ++acc_it) {
-      int e, t0, n_mma, n0;
-      decode(tile, e, t0, n_mma, n0);
-      const int n = n0 + (int)rank * 128 + quarter * 32 + lane;  // this thread's weight row = output column
+    while (true) {
+      const int tile = feed.take_warp(lane);
+      if (tile < 0) break;
+      const PairTile t = decode(tile);
+      const uint32_t par = seq & 1;
+      const uint32_t full_ph = (seq >> 1) & 1;
+      const int n = t.n0 + (int)rank * 128 + quarter * 32 + lane;  // this thread's weight row = output column
       const bool n_ok = n < p.N;
-      const int t_end = row_start[e + 1];
-      const uint32_t acc = acc_it & 1;
-      const uint32_t acc_ph = (acc_it >> 1) & 1;
-      const CUtensorMap* my = staged ? p.group_maps + (size_t)GM_OUT * p.E + e : nullptr;
-      if (staged && epi_tid == 0 && e != last_e) { tensormap_acquire(my); last_e = e; }
-      if (!mbar_wait_cluster(&ctl->tmem_full[acc], acc_ph, abort_flag, PW_TMEM_FULL)) { ok = false; break; }
+      const CUtensorMap* my = staged ? p.group_maps + (size_t)GM_OUT * p.E + t.e : nullptr;
+      if (staged && epi_tid == 0 && t.e != last_e) { tensormap_acquire(my); last_e = t.e; }
+      if (!mbar_wait_cluster(&ctl->tmem_full[par], full_ph, abort_flag, PW_TMEM_FULL)) break;
       tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + acc * PAIR_TOKENS + ((uint32_t)(quarter * 32) << 16);
-      if constexpr (GATE_UP) {
-        // (the host only launches this form with per-expert output maps and a 16-bit output)
-        pair_store_tile_gate_up(staging, chunk_it, taddr, n_mma, quarter, lane, epi_tid, is_bf16, my,
-                                n0 + (int)rank * 64, t0, p.N, p.debug);
-      } else if (staged) {
-        pair_store_tile_staged(staging, chunk_it, taddr, n_mma, quarter, lane, epi_tid, is_bf16, my,
-                               n0 + (int)rank * 128, t0, p.N, p.debug);
-      } else {
-#pragma unroll 1
-      for (int c = 0; c < n_mma; c += 32) {
-        uint32_t v[32];
-        if (!(p.debug & 2)) {
-          tmem_ld_32x32(taddr + c, v);
-          tmem_ld_wait();
+      const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+
+      // n_cols accumulator columns from TMEM column `col` on are the tokens tok0, tok0 + 1, ...
+      auto drain = [&](int col, int n_cols, int tok0) {
+        const uint32_t taddr = lane_base + (uint32_t)col;
+        if constexpr (GATE_UP) {
+          // (the host only launches this form with per-expert output maps and a 16-bit output)
+          pair_store_tile_gate_up(staging, chunk_it, taddr, n_cols, quarter, lane, epi_tid, is_bf16, my,
+                                  t.n0 + (int)rank * 64, tok0, p.N);
+        } else if (staged) {
+          pair_store_tile_staged(staging, chunk_it, taddr, n_cols, quarter, lane, epi_tid, is_bf16, my,
+                                 t.n0 + (int)rank * 128, tok0, p.N);
         } else {
+#pragma unroll 1
+          for (int c = 0; c < n_cols; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + c, v);
+            tmem_ld_wait();
+            if (n_ok) {
+              const int64_t base = (int64_t)(tok0 + c) * p.N + n;
+              const int valid = min(32, t.t_end - (tok0 + c));  // tokens of this chunk that belong to the expert
+              if (p.dtype_out == MOE_BF16) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = c + i;
-        }
-        if (n_ok && !(p.debug & 1)) {
-          const int64_t base = (int64_t)(t0 + c) * p.N + n;
-          const int valid = min(32, t_end - (t0 + c));  // tokens of this chunk that belong to the expert
-          if (p.dtype_out == MOE_BF16) {
+                for (int j = 0; j < 32; ++j)
+                  if (j < valid) store_scalar<__nv_bfloat16>(p.out, base + (int64_t)j * p.N, __uint_as_float(v[j]));
+              } else if (p.dtype_out == MOE_F16) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < valid) store_scalar<__nv_bfloat16>(p.out, base + (int64_t)j * p.N, __uint_as_float(v[j]));
-          } else if (p.dtype_out == MOE_F16) {
+                for (int j = 0; j < 32; ++j)
+                  if (j < valid) store_scalar<__half>(p.out, base + (int64_t)j * p.N, __uint_as_float(v[j]));
+              } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < valid) store_scalar<__half>(p.out, base + (int64_t)j * p.N, __uint_as_float(v[j]));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < valid) store_scalar<float>(p.out, base + (int64_t)j * p.N, __uint_as_float(v[j]));
+                for (int j = 0; j < 32; ++j)
+                  if (j < valid) store_scalar<float>(p.out, base + (int64_t)j * p.N, __uint_as_float(v[j]));
+              }
+            }
           }
         }
+      };
+      // this warp has finished reading region r
+      auto release = [&](int r) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tmem_free_leader0 + r * 8);
+      };
+      // The tile's columns as up to three segments (first TMEM column, columns, first token, region),
+      // contested regions first: the next tile's MMAs wait for them.  One loop, so that the drain code
+      // exists once (several inlined copies made the kernel miss in the instruction cache).
+      constexpr int SPLIT = PAIR_TOKENS - PAIR_TAIL;
+      const uint32_t regs = pair_regions(par, t.n_main, t.n_tail);
+#pragma unroll 1
+      for (int i = 0; i < 3; ++i) {
+        int col, n_cols, tok, reg;
+        if (par == 0) {
+          if (i == 0)      { col = PAIR_TOKENS; n_cols = t.n_tail;                 tok = t.t0 + PAIR_TOKENS; reg = REG_RB; }
+          else if (i == 1) { col = SPLIT;       n_cols = max(t.n_main - SPLIT, 0); tok = t.t0 + SPLIT;       reg = REG_RA; }
+          else             { col = 0;           n_cols = min(t.n_main, SPLIT);     tok = t.t0;               reg = REG_E0; }
+        } else {
+          if (i == 0)      { col = SPLIT;                   n_cols = t.n_tail;                     tok = t.t0 + PAIR_TOKENS; reg = REG_RA; }
+          else if (i == 1) { col = PAIR_TOKENS;             n_cols = min(t.n_main, PAIR_TAIL);     tok = t.t0;               reg = REG_RB; }
+          else             { col = PAIR_TOKENS + PAIR_TAIL; n_cols = max(t.n_main - PAIR_TAIL, 0); tok = t.t0 + PAIR_TAIL;   reg = REG_E1; }
+        }
+        if (!(regs & (1u << reg))) continue;  // the tile does not write this region
+        drain(col, n_cols, tok);
+        release(reg);
       }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(tmem_empty_leader0 + acc * 8);
+      ++seq;
     }
     if (staged && epi_tid == 0) tma_store_wait_all();
   }
