@@ -88,8 +88,10 @@ def make_routing(cfg, seed: int):
 
 
 class ClockSampler:
-    """Samples SM clock, power and throttle reasons while a timed region runs: NVML every 5 ms from a
+    """Samples SM clock, power and throttle reasons while a timed region runs: NVML every 10 ms from a
     thread of this process (read-only queries), or `nvidia-smi -lms 100` where NVML cannot be loaded."""
+
+    PERIOD_S = 0.010
 
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -142,7 +144,7 @@ class ClockSampler:
                                      int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))))
             except Exception:
                 break
-            time.sleep(0.005)
+            time.sleep(self.PERIOD_S)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -161,7 +163,7 @@ class ClockSampler:
             sm = [c for c, _, _ in self.samples]
             return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_min_mhz": min(sm) if sm else None,
                     "sm_max_mhz": self.max_mhz, "power_w_max": max((p for _, p, _ in self.samples), default=None),
-                    "reasons": reasons, "samples": len(sm), "source": "nvml, 5 ms period"}
+                    "reasons": reasons, "samples": len(sm), "source": "nvml, 10 ms period"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()

@@ -160,6 +160,14 @@ int moe_grouped_gemm_dx_nf4(const void* x, const uint8_t* packed, const float* c
                             int m_sizes_dtype, void* y, int64_t M, int N, int K, int E,
                             int dtype_in, int dtype_out, void* ws, size_t ws_bytes, void* stream);
 
+/* fp32 absmax from a double-quantised ("nested") one: out[i] = code2[q[i]] * absmax2[i /
+ * blocksize2] + offset[0] (offset may be NULL = 0), product and sum each rounded to fp32.
+ * q: n bytes; code2: 256 fp32 levels; absmax2: fp32 per blocksize2 (a power of two) entries.
+ * Replaces the dequantize_blockwise + offset step at
+ * qwen3_moe_fused/grouped_gemm/forward_4bit.py:149-153 (a bitsandbytes call there). */
+int moe_absmax_unnest(const uint8_t* q, const float* code2, const float* absmax2, int blocksize2,
+                      const float* offset, float* out, int64_t n, void* stream);
+
 /* Stand-alone NF4 decode of n_elems weights (same format as above) to dtype_out.
  * Stands in for the bitsandbytes dequantize_4bit call at
  * qwen3_moe_fused/quantize/layer.py:21 and qwen3_moe_fused/kernels/fast_lora.py:62. */
@@ -211,19 +219,24 @@ int moe_combine(const void* y, const int32_t* inv_sort_idx, const void* weights,
  * ------------------------------------------------------------------------------- */
 
 /* Rows sorted by expert (m_sizes[e] rows each, M in total, row_bytes each) are copied to
- * one destination per expert: row i of expert e goes to dst_ptrs[e] + i * row_bytes, rows
- * with i >= dst_limit[e] are dropped (dst_limit may be NULL).  dst_ptrs is a DEVICE array
- * of E 64-bit addresses, 16-byte aligned, in this GPU's memory or in a peer GPU's memory
- * mapped into this process; the stores are plain global stores.  The call neither waits
- * for nor signals the receiver.  Rows are visited starting with expert first_expert and
- * wrapping around (ranks that start at different experts do not all write to the same
- * destination at once).  With src_index (M int32, may be NULL) sorted row r is read from row
- * src_index[r] / src_div of `rows`: passing the sort's gather index and k pushes token rows
- * without expanding them first.  max_ctas <= 0 picks a grid from the SM count. */
+ * one destination per expert: row i of expert e goes to dst_ptrs[e] + i * row_bytes.
+ * dst_limit (DEVICE array of E int32, may be NULL = no limits): a negative entry leaves the
+ * expert's rows where they are (not part of this push); otherwise rows with i >= dst_limit[e]
+ * would overrun the receiver's buffer: they are NOT written and, when `dropped` is given,
+ * counted there (DEVICE int32, incremented once per dropped row; the caller clears and reads
+ * it: a non-zero count means the receiver's results for those rows are missing).
+ * dst_ptrs is a DEVICE array of E 64-bit addresses, 16-byte aligned, in this GPU's memory or
+ * in a peer GPU's memory mapped into this process; the stores are plain global stores.  The
+ * call neither waits for nor signals the receiver.  Rows are visited starting with expert
+ * first_expert and wrapping around (ranks that start at different experts do not all write
+ * to the same destination at once).  With src_index (M int32, may be NULL) sorted row r is
+ * read from row src_index[r] / src_div of `rows`: passing the sort's gather index and k
+ * pushes token rows without expanding them first.  max_ctas <= 0 picks a grid from the SM
+ * count. */
 int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, const void* m_sizes,
                      int m_sizes_dtype, int E, const uint64_t* dst_ptrs,
                      const int32_t* dst_limit, int first_expert, const int32_t* src_index,
-                     int src_div, int max_ctas, void* stream);
+                     int src_div, int max_ctas, int32_t* dropped, void* stream);
 
 /* Row bookkeeping of one routing decision for the exchange above, in one launch.
  * counts (world, E) int32 on the device: rows of every rank per global expert (expert e lives on

@@ -210,6 +210,13 @@ def nf4_dequantize(packed: np.ndarray, absmax: np.ndarray, code: np.ndarray, blo
     return round_to(vals.reshape(shape), dtype)
 
 
+def absmax_unnest(q: np.ndarray, code2: np.ndarray, absmax2: np.ndarray, blocksize2: int, offset: float) -> np.ndarray:
+    """forward_4bit.py:149-153: a double-quantised absmax back to fp32: table lookup of the byte,
+    times the second-level absmax of its block, plus the offset; each step rounded to fp32."""
+    vals = code2.astype(np.float32)[np.asarray(q, np.uint8)] * np.repeat(np.asarray(absmax2, np.float32), blocksize2)
+    return (vals.astype(np.float32) + np.float32(offset)).astype(np.float32)
+
+
 # ----------------------------------------------------------------------------------
 # SiLU-mul  (qwen3_moe_fused/kernels/silu_mul.py:23-111; plain path
 # qwen3_moe_fused/modular_qwen3_moe_fused.py:108)

@@ -56,9 +56,9 @@ def test_argument_errors_return_before_any_launch(lib):
     # expert-parallel and fused entry points
     assert lib.moe_ep_plan(None, 3, 0, 128, 0, 42, None, None, None, None, None, None, None, None, None) == -2  # 128 % 3
     assert lib.moe_ep_plan(None, 4, 0, 128, 0, 32, None, None, None, None, None, None, None, None, None) == -3
-    assert lib.moe_ep_push_rows(None, 8, 64, None, 9, 4, None, None, 0, None, 1, 0, None) == -1
-    assert lib.moe_ep_push_rows(None, 8, 64, None, 3, 4, None, None, 7, None, 1, 0, None) == -2  # first_expert >= E
-    assert lib.moe_ep_push_rows(None, 8, 64, None, 3, 4, None, None, 0, None, 1, 0, None) == -3
+    assert lib.moe_ep_push_rows(None, 8, 64, None, 9, 4, None, None, 0, None, 1, 0, None, None) == -1
+    assert lib.moe_ep_push_rows(None, 8, 64, None, 3, 4, None, None, 7, None, 1, 0, None, None) == -2  # first_expert >= E
+    assert lib.moe_ep_push_rows(None, 8, 64, None, 3, 4, None, None, 0, None, 1, 0, None, None) == -3
     assert lib.moe_gate_up_silu_fwd(None, None, None, None, 3, None, 4, 4, 4, 2, 9, None, 0, None) == -1
     assert lib.moe_grouped_gemm_dx_nf4(None, None, None, None, 48, None, 3, None, 4, 4, 4, 2, 1, 1, None, 0, None) == -3
     assert lib.moe_grouped_gemm_fwd_scattered(None, None, None, 3, None, 2, None, None, -1, 4, 4, 2, 1, 1, None, 0, None) == -2

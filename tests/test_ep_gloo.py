@@ -187,3 +187,39 @@ def test_peer_plan_sub_ranges(tmp_path, world):
                 start += n
     for s in range(world):
         assert torch.equal(back[s], saved[s]["xs"])
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_push_limits_when_a_receive_buffer_is_too_small(world):
+    """A routing that sends more rows to one owner than its buffer holds: the limits handed to the push
+    kernel keep exactly the rows that fit (in the owner's layout order) and the rest is what the
+    kernel counts as dropped; experts outside a sub-range plan are marked -1."""
+    from qwen3_moe_fused.parallel_ep import PeerPlan, push_limits
+
+    E, e_local = 8, 8 // world
+    g = torch.Generator().manual_seed(world)
+    counts = torch.randint(0, 40, (world, E), generator=g, dtype=torch.int32)
+    counts[:, :e_local] += 100  # everybody sends most rows to rank 0's experts
+    recv = counts.view(world, world, e_local).sum(dim=(0, 2))  # rows each owner receives
+    capacity = int(recv[0]) - 57  # rank 0's buffer is 57 rows short; the others' are large enough
+    assert capacity > int(recv[1:].max())
+    dropped = 0
+    kept_on_owner0 = 0
+    for rank in range(world):
+        plan = PeerPlan.from_counts(counts, world, rank)
+        limit = push_limits(plan, capacity)
+        assert limit.dtype == torch.int32 and (limit >= 0).all()
+        m = counts[rank]
+        kept = torch.minimum(m, limit)
+        dropped += int((m - kept).sum())
+        kept_on_owner0 += int(kept[:e_local].sum())
+        # rows kept never reach past the end of the owner's buffer
+        assert ((plan.send_row + kept.long())[kept > 0] <= capacity).all()
+        # owners with room lose nothing
+        assert torch.equal(kept[e_local:], m[e_local:])
+    assert dropped == 57 and kept_on_owner0 == capacity
+    sub = PeerPlan.from_counts(counts, world, 0, (0, 1))
+    lim = push_limits(sub, 10 ** 6)
+    inside = torch.zeros(E, dtype=torch.bool)
+    inside[torch.arange(world) * e_local] = True
+    assert (lim[~inside] == -1).all() and torch.equal(lim[inside], counts[0][inside].clamp(min=0) * 0 + lim[inside]) and (lim[inside] >= 0).all()

@@ -115,3 +115,45 @@ def test_linear4bit_backward_is_fused_dx(cuda):
     moe_fused_linear_4bit(xa, packed, state, tm, fused=True).backward(dy)
     moe_fused_linear_4bit(xb, packed, state, tm, fused=False).backward(dy)
     assert_close(to_np(xa.grad), to_np(xb.grad), "bf16", "fused dX vs decode + dX")
+
+
+@pytest.mark.parametrize("n,bs2", [(4096, 256), (1000 * 256, 256), (513 * 64, 64)])
+def test_nested_absmax_decoded_on_the_device(cuda, n, bs2):
+    """Double-quantised absmax -> fp32 absmax in one kernel, bit for bit what the oracle computes."""
+    from qwen3_moe_fused.grouped_gemm.forward_4bit import _unnest_absmax
+    from qwen3_moe_fused.quantize.nf4 import AbsmaxState, Nf4State
+
+    rng = np.random.default_rng(n)
+    q = rng.integers(0, 256, n).astype(np.uint8)
+    code2 = np.sort(rng.uniform(-1, 1, 256)).astype(np.float32)
+    absmax2 = rng.uniform(0.01, 0.2, n // bs2).astype(np.float32)
+    offset = np.float32(0.0371)
+    state = Nf4State(absmax=torch.from_numpy(q).to(cuda), code=torch.from_numpy(O.nf4_code()).to(cuda), blocksize=64,
+                     shape=torch.Size((n * 64,)), dtype=torch.bfloat16, nested=True,
+                     state2=AbsmaxState(torch.from_numpy(absmax2).to(cuda), torch.from_numpy(code2).to(cuda), bs2),
+                     offset=torch.tensor([offset], device=cuda))
+    got = _unnest_absmax(state).cpu().numpy()
+    assert np.array_equal(got, O.absmax_unnest(q, code2, absmax2, bs2, offset))
+
+
+def test_fused_forward_with_nested_absmax(cuda):
+    """A weight whose absmax is itself quantised (double quantisation): the fused forward decodes the
+    absmax on the device first and matches decode + GEMM of the oracle on the same quantised data."""
+    from qwen3_moe_fused.grouped_gemm.forward_4bit import grouped_gemm_forward_4bit
+    from qwen3_moe_fused.quantize.nf4 import nest_absmax, quantize_nf4
+
+    rng = np.random.default_rng(21)
+    M, K, N, E, bs = 1024, 512, 512, 8, 64
+    w = torch.from_numpy((rng.standard_normal((E, N, K)) / np.sqrt(K)).astype(np.float32)).to(cuda).to(torch.bfloat16)
+    packed, state = quantize_nf4(w, bs)
+    nested = nest_absmax(state, 256)
+    assert nested.nested and nested.absmax.dtype == torch.uint8
+    absmax = O.absmax_unnest(nested.absmax.cpu().numpy(), nested.state2.code.cpu().numpy(), nested.state2.absmax.cpu().numpy(),
+                             256, float(nested.offset))
+    # the nested absmax is close to the plain one (8-bit second level), and the kernel uses exactly the oracle's values
+    assert np.abs(absmax - state.absmax.cpu().numpy()).max() <= 0.01 * state.absmax.abs().max().item()
+    w_deq = O.nf4_dequantize(packed.cpu().numpy(), absmax, O.nf4_code(), bs, (E, N, K), "bf16")
+    x = rounded(rng.standard_normal((M, K)), "bf16")
+    m_sizes = random_m_sizes(rng, M, E, 0.1)
+    y = grouped_gemm_forward_4bit(to_dev(x, "bf16", cuda), packed, nested, torch.from_numpy(m_sizes).to(cuda), fused=True)
+    assert_close(to_np(y), O.grouped_gemm_fwd(x, w_deq, m_sizes, "bf16"), "bf16", "nested nf4 fwd")

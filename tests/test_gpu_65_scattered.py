@@ -22,12 +22,17 @@ def test_push_rows(dev, E, M, W):
     rng = np.random.default_rng(E * 7 + M)
     m = random_m_sizes(rng, M, E, empty_frac=0.2)
     rows = torch.randn(M, W, device=dev).to(torch.bfloat16)
-    # every expert gets a slot of its own in one of two buffers, in a shuffled order, with one
-    # expert's slot shorter than its rows
+    # every expert gets a slot of its own in one of two buffers, in a shuffled order; one expert's
+    # slot is shorter than its rows (the rest is dropped and counted), another expert is left out
+    # of the push altogether (negative limit: not written, not counted)
     order = rng.permutation(E)
     limit = m.copy()
     big = int(np.argmax(m))
     limit[big] = m[big] // 2
+    others = [e for e in np.argsort(-m) if e != big and m[e] > 0]
+    skip = int(others[0]) if others else -1
+    if skip >= 0:
+        limit[skip] = -1
     bufs = [torch.full((M + 8, W), -1.0, device=dev, dtype=torch.bfloat16) for _ in range(2)]
     ptrs = np.zeros(E, np.int64)
     slot = {}
@@ -36,17 +41,19 @@ def test_push_rows(dev, E, M, W):
         b = int(e) % 2
         slot[int(e)] = (b, fill[b])
         ptrs[e] = bufs[b].data_ptr() + fill[b] * W * 2
-        fill[b] += int(limit[e])
+        fill[b] += max(int(limit[e]), 0)
+    dropped = torch.zeros(1, dtype=torch.int32, device=dev)
     push_rows(rows, torch.from_numpy(m).to(dev), torch.from_numpy(ptrs).to(dev), torch.from_numpy(limit.astype(np.int32)).to(dev),
-              first_expert=(E * 2) // 3)
+              first_expert=(E * 2) // 3, dropped=dropped)
     torch.cuda.synchronize()
     begins = np.concatenate([[0], np.cumsum(m)])
     for e in range(E):
         b, at = slot[e]
-        n = int(limit[e])
+        n = max(int(limit[e]), 0)
         assert torch.equal(bufs[b][at:at + n], rows[begins[e]:begins[e] + n]), f"expert {e}"
     for b in range(2):
         assert bool((bufs[b][fill[b]:] == -1.0).all()), "rows past the limits were written"
+    assert int(dropped) == int(m[big] - limit[big]), "every row that did not fit is counted, skipped experts are not"
 
 
 @pytest.mark.parametrize("transposed", [False, True])
@@ -120,7 +127,8 @@ def test_scattered_rejects_thin(dev):
         scattered_grouped_gemm(x, w, torch.tensor([32, 32], device=dev, dtype=torch.int32), None, ptrs, out)
 
 
-@pytest.mark.parametrize("world,E,rng_", [(2, 16, None), (4, 128, None), (8, 128, (4, 9)), (4, 32, (0, 3)), (1, 8, None)])
+@pytest.mark.parametrize("world,E,rng_", [(2, 16, None), (4, 128, None), (8, 128, (4, 9)), (4, 32, (0, 3)), (1, 8, None),
+                                          (8, 1024, None), (16, 1024, None)])  # the last two need more than 48 KB of shared memory
 def test_plan_kernel_matches_tensor_plan(dev, world, E, rng_):
     """`moe_ep_plan` (one launch) against the same plan computed with tensor operations on the host."""
     from qwen3_moe_fused.parallel_ep import PeerPlan

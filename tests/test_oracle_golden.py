@@ -99,8 +99,15 @@ def test_nf4_table_and_roundtrip():
     code = O.nf4_code()
     assert code.shape == (16,) and code[0] == -1.0 and code[7] == 0.0 and code[15] == 1.0
     assert np.all(np.diff(code) > 0)
-    # widely published values of the NF4 data type, to 1e-6
-    np.testing.assert_allclose(code[[1, 8, 14]], [-0.6961928, 0.0795803, 0.7229568], atol=1e-6)
+    # all 16 levels of the NF4 data type as published with it (QLoRA, appendix E), to 1e-6; the
+    # device-side table of the package is built from the same construction
+    published = [-1.0, -0.6961928009986877, -0.5250730514526367, -0.39491748809814453, -0.28444138169288635,
+                 -0.18477343022823334, -0.09105003625154495, 0.0, 0.07958029955625534, 0.16093020141124725,
+                 0.24611230194568634, 0.33791524171829224, 0.44070982933044434, 0.5626170039176941, 0.7229568362236023, 1.0]
+    np.testing.assert_allclose(code, published, atol=1e-6)
+    from qwen3_moe_fused.quantize.nf4 import nf4_code as package_code
+
+    np.testing.assert_allclose(package_code().numpy(), published, atol=1e-6)
     rng = np.random.default_rng(3)
     w = (rng.standard_normal((4, 8, 64)) * 0.02).astype(np.float32)
     packed, absmax = O.nf4_quantize(w, 64)

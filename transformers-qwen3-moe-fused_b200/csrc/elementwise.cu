@@ -193,6 +193,32 @@ silu_bwd_kernel(const T* dh, const T* e, const T* g, T* h, T* de, T* dg, int64_t
   }
 }
 
+// Double-quantised ("nested") absmax -> fp32 absmax: out[i] = code2[q[i]] * absmax2[i / blocksize2]
+// + offset, the product and the sum each rounded to fp32 (what dequantize_blockwise followed by
+// `+= offset` computes at qwen3_moe_fused/grouped_gemm/forward_4bit.py:149-153).
+__global__ void __launch_bounds__(EW_THREADS)
+absmax_unnest_kernel(const uint8_t* __restrict__ q, const float* __restrict__ code2, const float* __restrict__ absmax2,
+                     int bs_shift, const float* __restrict__ offset, float* __restrict__ out, int64_t n) {
+  __shared__ float tbl[256];
+  for (int i = threadIdx.x; i < 256; i += EW_THREADS) tbl[i] = code2[i];
+  __syncthreads();
+  const float off = offset ? __ldg(offset) : 0.f;
+  const bool vec = ((reinterpret_cast<uintptr_t>(q) & 3) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+  const int64_t stride = (int64_t)gridDim.x * EW_THREADS;
+  const int64_t groups = vec ? n / 4 : 0;
+  for (int64_t g = (int64_t)blockIdx.x * EW_THREADS + threadIdx.x; g < groups; g += stride) {
+    const uint32_t raw = __ldg(reinterpret_cast<const uint32_t*>(q) + g);
+    float4 v;
+    float* pv = reinterpret_cast<float*>(&v);
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+      pv[b] = __fadd_rn(__fmul_rn(tbl[(raw >> (8 * b)) & 0xffu], __ldg(absmax2 + ((g * 4 + b) >> bs_shift))), off);
+    reinterpret_cast<float4*>(out)[g] = v;
+  }
+  for (int64_t i = groups * 4 + (int64_t)blockIdx.x * EW_THREADS + threadIdx.x; i < n; i += stride)
+    out[i] = __fadd_rn(__fmul_rn(tbl[q[i]], __ldg(absmax2 + (i >> bs_shift))), off);
+}
+
 // NF4 decode, 8 weights (4 packed bytes) per thread iteration: a warp reads 128 contiguous
 // bytes and, for 16-bit outputs, writes 512 contiguous bytes per store instruction.
 // Element 2j is the high nibble of byte j, element 2j+1 the low nibble
@@ -463,6 +489,17 @@ MOE_API int moe_silu_mul_bwd_inplace(void* dh, void* e, void* g, int64_t n, int 
   // (dh, e, g) <- (h, de, dg): every element is read before it is overwritten by the
   // same thread, so aliasing inputs and outputs is safe.
   return silu_bwd_impl(dh, e, g, dh, e, g, n, dtype, true, (cudaStream_t)stream);
+}
+
+MOE_API int moe_absmax_unnest(const uint8_t* q, const float* code2, const float* absmax2, int blocksize2,
+                              const float* offset, float* out, int64_t n, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const int shift = ilog2_exact(blocksize2);
+  if (shift < 0 || n < 0) return MOE_ERR_SHAPE;
+  if (n == 0) return MOE_OK;
+  if (!q || !code2 || !absmax2 || !out) return MOE_ERR_NULL;
+  absmax_unnest_kernel<<<ew_grid((n + 3) / 4), EW_THREADS, 0, stream>>>(q, code2, absmax2, shift, offset, out, n);
+  return launch_status();
 }
 
 MOE_API int moe_nf4_dequant(const uint8_t* packed, const float* code, const float* absmax, int blocksize,

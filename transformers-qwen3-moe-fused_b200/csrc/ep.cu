@@ -41,7 +41,7 @@ template <int UNROLL>
 __global__ void __launch_bounds__(PUSH_THREADS)
 ep_push_rows_kernel(const uint4* __restrict__ rows, int64_t M, int row_vecs, const void* __restrict__ m_sizes, int ms64,
                     int E, const uint64_t* __restrict__ dst_ptrs, const int32_t* __restrict__ dst_limit, int first_expert,
-                    const int32_t* __restrict__ src_index, int src_div) {
+                    const int32_t* __restrict__ src_index, int src_div, int32_t* __restrict__ dropped) {
   __shared__ int begins[PUSH_MAX_E + 1];
   push_build_begins(m_sizes, ms64, E, begins);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -60,7 +60,14 @@ ep_push_rows_kernel(const uint4* __restrict__ rows, int64_t M, int row_vecs, con
     }
     const int e = lo;
     const int local = (int)r - begins[e];
-    if (dst_limit != nullptr && local >= dst_limit[e]) continue;  // would overrun the receiver's buffer
+    if (dst_limit != nullptr) {
+      const int limit = dst_limit[e];
+      if (limit < 0) continue;  // this expert's rows are not part of this push
+      if (local >= limit) {     // would overrun the receiver's buffer: not written, but counted
+        if (dropped != nullptr && lane == 0) atomicAdd(dropped, 1);
+        continue;
+      }
+    }
     // with a source index, sorted row r is row src_index[r] / src_div of `rows` (token rows expanded on the fly)
     const uint4* src = rows + (src_index ? (int64_t)(src_index[r] / src_div) : r) * row_vecs;
     uint4* dst = reinterpret_cast<uint4*>(dst_ptrs[e]) + (int64_t)local * row_vecs;
@@ -153,7 +160,11 @@ MOE_API int moe_ep_plan(const int32_t* counts, int world, int rank, int E, int l
       !local_m_sizes || !recv_rows)
     return MOE_ERR_NULL;
   const size_t smem = (size_t)(2 * world * E + world * (hi - lo) * world) * sizeof(int32_t);
-  if (smem > 48 * 1024) return MOE_ERR_SHAPE;
+  if (smem > 227 * 1024) return MOE_ERR_SHAPE;
+  if (smem > 48 * 1024) {  // above the default limit the kernel has to opt in
+    const cudaError_t e = cudaFuncSetAttribute(ep_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_status(e);
+  }
   ep_plan_kernel<<<1, 256, smem, stream>>>(counts, world, rank, E, lo, hi, send_row, send_ok, group_sizes, weight_index,
                                            group_src, return_row, local_m_sizes, recv_rows);
   return launch_status();
@@ -161,7 +172,7 @@ MOE_API int moe_ep_plan(const int32_t* counts, int world, int rank, int E, int l
 
 MOE_API int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, const void* m_sizes, int m_sizes_dtype,
                              int E, const uint64_t* dst_ptrs, const int32_t* dst_limit, int first_expert,
-                             const int32_t* src_index, int src_div, int max_ctas, void* stream_) {
+                             const int32_t* src_index, int src_div, int max_ctas, int32_t* dropped, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (!is_int_dtype(m_sizes_dtype)) return MOE_ERR_DTYPE;
   if (M < 0 || row_bytes < 0 || E <= 0 || E > PUSH_MAX_E || M > 0x7fffffffLL) return MOE_ERR_SHAPE;
@@ -175,6 +186,6 @@ MOE_API int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, con
   if (grid > cap) grid = cap;
   ep_push_rows_kernel<8><<<(int)grid, PUSH_THREADS, 0, stream>>>(
       reinterpret_cast<const uint4*>(rows), M, (int)(row_bytes / 16), m_sizes, m_sizes_dtype == MOE_I64, E, dst_ptrs, dst_limit, first_expert,
-      src_index, src_div);
+      src_index, src_div, dropped);
   return launch_status();
 }

@@ -211,18 +211,23 @@ MOE_API size_t moe_sort_workspace_bytes(int64_t M, int E) {
   return (size_t)(sort_chunks(M) + 1) * (size_t)E * sizeof(int32_t);
 }
 
-MOE_API int moe_sort_by_expert(const void* s, int s_dtype, int64_t M, int E, int32_t* counts,
-                               int32_t* inv_idx, int32_t* idx, void* ws, size_t ws_bytes,
-                               void* stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
+// Argument checks shared by the two sort entry points.
+static int sort_check(const void* s, int s_dtype, int64_t M, int E, const int32_t* counts, const int32_t* inv_idx,
+                      const int32_t* idx) {
   if (!is_int_dtype(s_dtype)) return MOE_ERR_DTYPE;
   if (M < 0 || E <= 0 || E > SORT_MAX_E || M > 0x7fffffffLL) return MOE_ERR_SHAPE;
   if (counts == nullptr || (M > 0 && s == nullptr)) return MOE_ERR_NULL;
   if ((inv_idx == nullptr) != (idx == nullptr)) return MOE_ERR_NULL;
-  if (ws == nullptr || ws_bytes < moe_sort_workspace_bytes(M, E)) return MOE_ERR_WORKSPACE;
-  const int is64 = s_dtype == MOE_I64;
+  return MOE_OK;
+}
+
+// The three launches of the sort, with `scratch` holding moe_sort_workspace_bytes(M, E) bytes.
+// Every word of the scratch that the scan and scatter kernels read is written first by the
+// histogram and scan kernels of the same call, so its previous contents do not matter.
+static int sort_launch(const void* s, int is64, int64_t M, int E, int32_t* counts, int32_t* inv_idx, int32_t* idx,
+                       void* scratch, cudaStream_t stream) {
   const int nchunks = (int)sort_chunks(M);
-  int32_t* hist = (int32_t*)ws;
+  int32_t* hist = (int32_t*)scratch;
   int32_t* offsets = hist + (size_t)nchunks * E;
   if (nchunks > 0) {
     sort_hist_kernel<<<nchunks, SORT_THREADS, E * sizeof(int32_t), stream>>>(s, is64, M, E, hist);
@@ -237,6 +242,15 @@ MOE_API int moe_sort_by_expert(const void* s, int s_dtype, int64_t M, int E, int
     sort_scatter_kernel<<<nchunks, SORT_THREADS, smem, stream>>>(s, is64, M, E, hist, offsets, inv_idx, idx);
   }
   return launch_status();
+}
+
+MOE_API int moe_sort_by_expert(const void* s, int s_dtype, int64_t M, int E, int32_t* counts,
+                               int32_t* inv_idx, int32_t* idx, void* ws, size_t ws_bytes,
+                               void* stream_) {
+  const int st = sort_check(s, s_dtype, M, E, counts, inv_idx, idx);
+  if (st != MOE_OK) return st;
+  if (ws == nullptr || ws_bytes < moe_sort_workspace_bytes(M, E)) return MOE_ERR_WORKSPACE;
+  return sort_launch(s, s_dtype == MOE_I64, M, E, counts, inv_idx, idx, ws, (cudaStream_t)stream_);
 }
 
 MOE_API int moe_batch_begins_ends(const void* s_sorted, int s_dtype, int64_t M, int E,
@@ -290,32 +304,13 @@ MOE_API size_t moe_sort_static_capacity_bytes(void) { return moe::SORT_STATIC_BY
 
 MOE_API int moe_sort_by_expert_static(const void* s, int s_dtype, int64_t M, int E, int32_t* counts,
                                       int32_t* inv_idx, int32_t* idx, void* stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
-  if (!is_int_dtype(s_dtype)) return MOE_ERR_DTYPE;
-  if (M < 0 || E <= 0 || E > SORT_MAX_E || M > 0x7fffffffLL) return MOE_ERR_SHAPE;
-  if (counts == nullptr || (M > 0 && s == nullptr)) return MOE_ERR_NULL;
-  if ((inv_idx == nullptr) != (idx == nullptr)) return MOE_ERR_NULL;
+  const int chk = sort_check(s, s_dtype, M, E, counts, inv_idx, idx);
+  if (chk != MOE_OK) return chk;
   // the fixed array bounds the problem size: refuse anything that would not fit
   if (moe_sort_workspace_bytes(M, E) > SORT_STATIC_BYTES) return MOE_ERR_WORKSPACE;
   void* scratch = nullptr;
   const int st = sort_static_scratch(&scratch);
   if (st != MOE_OK) return st;
-  // Every word of the scratch that the scan and scatter kernels read is written first by
-  // the histogram and scan kernels of this same call, so nothing has to be cleared even
-  // though the array still holds the previous call's contents.
-  const int is64 = s_dtype == MOE_I64;
-  const int nchunks = (int)sort_chunks(M);
-  int32_t* hist = (int32_t*)scratch;
-  int32_t* offsets = hist + (size_t)nchunks * E;
-  if (nchunks > 0) sort_hist_kernel<<<nchunks, SORT_THREADS, E * sizeof(int32_t), stream>>>(s, is64, M, E, hist);
-  sort_scan_kernel<<<1, 1024, 0, stream>>>(hist, nchunks, E, counts, idx ? offsets : nullptr);
-  if (idx != nullptr && nchunks > 0) {
-    const size_t smem = (size_t)SORT_WARPS * E * sizeof(int32_t);
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return cuda_status(e);
-    }
-    sort_scatter_kernel<<<nchunks, SORT_THREADS, smem, stream>>>(s, is64, M, E, hist, offsets, inv_idx, idx);
-  }
-  return launch_status();
+  // the array still holds the previous call's contents; sort_launch does not depend on them
+  return sort_launch(s, s_dtype == MOE_I64, M, E, counts, inv_idx, idx, scratch, (cudaStream_t)stream_);
 }

@@ -15,3 +15,20 @@ if _ref:
     _ref_pkg = _os.path.join(_ref, "qwen3_moe_fused")
     if _os.path.isdir(_ref_pkg) and _ref_pkg not in __path__:
         __path__.append(_ref_pkg)
+
+
+def check_errors() -> None:
+    """Raises if a kernel of this library recorded an error since the last check.
+
+    The tensor-core kernels bound every wait inside them (2 s); a wait that runs out makes the
+    kernel return early with its output incomplete and records a code in a device-side word, and
+    a misaligned per-group output address is recorded the same way.  Launches never read that word
+    (it would cost a device synchronisation per call), so a program that wants to know calls this
+    at a point where a synchronisation is acceptable, for instance once per training step.
+    """
+    from . import _lib
+
+    flag = _lib.read_error_flag()
+    if flag:
+        raise _lib.MoeB200Error(f"a kernel reported error code {flag >> 16} (first reporter: CTA {flag & 0xffff}); "
+                                "outputs of the calls since the last check may be incomplete")

@@ -41,6 +41,7 @@ SIGNATURES = {
     "moe_grouped_gemm_fwd_nf4": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_grouped_gemm_dx_nf4": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_nf4_dequant": (_I, [_P, _P, _P, _I, _P, _L, _I, _P]),
+    "moe_absmax_unnest": (_I, [_P, _P, _P, _I, _P, _P, _L, _P]),
     "moe_silu_mul_fwd": (_I, [_P, _P, _P, _L, _I, _P]),
     "moe_silu_mul_bwd": (_I, [_P, _P, _P, _P, _P, _L, _I, _P]),
     "moe_silu_mul_bwd_inplace": (_I, [_P, _P, _P, _L, _I, _P]),
@@ -49,7 +50,7 @@ SIGNATURES = {
     "moe_expand_rows": (_I, [_P, _P, _I, _P, _L, _I, _I, _P]),
     "moe_combine": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _P]),
     "moe_ep_plan": (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
-    "moe_ep_push_rows": (_I, [_P, _L, _L, _P, _I, _I, _P, _P, _I, _P, _I, _I, _P]),
+    "moe_ep_push_rows": (_I, [_P, _L, _L, _P, _I, _I, _P, _P, _I, _P, _I, _I, _P, _P]),
     "moe_grouped_gemm_fwd_scattered": (_I, [_P, _P, _P, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_grouped_gemm_dx_scattered": (_I, [_P, _P, _P, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_debug_read_error": (_I, [_P, _I]),

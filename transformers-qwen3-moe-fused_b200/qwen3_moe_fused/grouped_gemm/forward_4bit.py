@@ -15,19 +15,29 @@ from .forward import is_int_tensor
 
 
 def _unnest_absmax(state) -> torch.Tensor:
-    """fp32 absmax per block; expands a double-quantised absmax
-    (qwen3_moe_fused/grouped_gemm/forward_4bit.py:149-153)."""
+    """fp32 absmax per block.  A double-quantised ("nested") absmax is expanded by one kernel of
+    this library (qwen3_moe_fused/grouped_gemm/forward_4bit.py:149-153 of the reference calls
+    bitsandbytes for it): `state.absmax` holds one byte per block, `state.state2` the 256-level
+    table `code`, its own fp32 `absmax` and `blocksize`, `state.offset` the mean that was
+    subtracted.  Works on a bitsandbytes `QuantState` and on `quantize.nf4.Nf4State` alike."""
     absmax = state.absmax
-    if getattr(state, "nested", False):
-        state2 = state.state2
-        if hasattr(state2, "dequantize"):  # own container
-            absmax = state2.dequantize(absmax)
-        else:  # bitsandbytes QuantState
-            from bitsandbytes.functional import dequantize_blockwise
-
-            absmax = dequantize_blockwise(absmax, state2)
-        absmax = absmax + state.offset
-    return absmax
+    if not getattr(state, "nested", False):
+        return absmax
+    state2 = state.state2
+    q = absmax.contiguous()
+    assert q.is_cuda and q.dtype == torch.uint8
+    code2 = state2.code.to(device=q.device, dtype=torch.float32).contiguous()
+    absmax2 = state2.absmax.to(device=q.device, dtype=torch.float32).contiguous()
+    assert code2.numel() == 256
+    offset = state.offset
+    if offset is not None:
+        offset = torch.as_tensor(offset, dtype=torch.float32, device=q.device).reshape(1).contiguous()
+    out = torch.empty(q.numel(), device=q.device, dtype=torch.float32)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.load().moe_absmax_unnest(
+            _lib.ptr(q), _lib.ptr(code2), _lib.ptr(absmax2), int(state2.blocksize), _lib.ptr(offset), _lib.ptr(out),
+            q.numel(), _lib.stream_ptr(q.device)), "moe_absmax_unnest")
+    return out
 
 
 # Rows per expert (on average) from which decoding the whole weight once and running the dense

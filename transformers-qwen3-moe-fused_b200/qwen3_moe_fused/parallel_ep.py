@@ -261,10 +261,14 @@ def peer_fence(token: torch.Tensor, group=None) -> None:
 
 def push_rows(rows: torch.Tensor, m_sizes: torch.Tensor, dst_ptrs: torch.Tensor,
               dst_limit: Optional[torch.Tensor] = None, max_ctas: int = 0, first_expert: int = 0,
-              src_index: Optional[torch.Tensor] = None, src_div: int = 1) -> None:
+              src_index: Optional[torch.Tensor] = None, src_div: int = 1,
+              dropped: Optional[torch.Tensor] = None) -> None:
     """rows (M, W) sorted by expert, m_sizes (E,): row i of expert e is copied to the address
-    dst_ptrs[e] + i * row_bytes (int64 device tensor of addresses, local or peer memory); rows
-    with i >= dst_limit[e] are dropped.  The copy starts with the rows of `first_expert`.
+    dst_ptrs[e] + i * row_bytes (int64 device tensor of addresses, local or peer memory).
+    `dst_limit` (int32 per expert): negative = the expert's rows are not part of this push;
+    otherwise rows with i >= dst_limit[e] do not fit into the receiver's buffer: they are not
+    written and are counted in `dropped` (int32 device scalar, incremented per dropped row).
+    The copy starts with the rows of `first_expert`.
     With `src_index` (int32, one entry per sorted row) sorted row r is read from
     rows[src_index[r] // src_div]: token rows are expanded while they are pushed."""
     from . import _lib
@@ -274,6 +278,8 @@ def push_rows(rows: torch.Tensor, m_sizes: torch.Tensor, dst_ptrs: torch.Tensor,
     m_sizes = _lib.as_index_tensor(m_sizes).contiguous()
     if dst_limit is not None:
         assert dst_limit.dtype == torch.int32 and dst_limit.is_contiguous() and dst_limit.numel() == m_sizes.numel()
+    if dropped is not None:
+        assert dropped.dtype == torch.int32 and dropped.is_cuda and dropped.numel() == 1
     n_rows = rows.shape[0]
     if src_index is not None:
         assert src_index.dtype == torch.int32 and src_index.is_contiguous()
@@ -281,7 +287,7 @@ def push_rows(rows: torch.Tensor, m_sizes: torch.Tensor, dst_ptrs: torch.Tensor,
     _lib.check(_lib.load().moe_ep_push_rows(
         _lib.ptr(rows), n_rows, rows.shape[1] * rows.element_size(), _lib.ptr(m_sizes), _lib.int_code(m_sizes.dtype),
         m_sizes.numel(), _lib.ptr(dst_ptrs), _lib.ptr(dst_limit), first_expert, _lib.ptr(src_index), src_div, max_ctas,
-        _lib.stream_ptr(rows.device)), "moe_ep_push_rows")
+        _lib.ptr(dropped), _lib.stream_ptr(rows.device)), "moe_ep_push_rows")
 
 
 def scattered_grouped_gemm(x: torch.Tensor, weight: torch.Tensor, group_sizes: torch.Tensor,
@@ -312,26 +318,35 @@ def scattered_grouped_gemm(x: torch.Tensor, weight: torch.Tensor, group_sizes: t
         _lib.ptr(out_ptrs), _lib.ptr(out_template), M, N, K, G, dt, dt, ws_ptr, ws_bytes, _lib.stream_ptr(x.device)), name)
 
 
+def push_limits(plan: PeerPlan, capacity_rows: int) -> torch.Tensor:
+    """(E,) int32 for `push_rows`: how many of this rank's rows of each expert fit into the owner's
+    buffer of `capacity_rows` rows (the rows start at plan.send_row there); -1 for experts that another
+    plan moves."""
+    limit = (capacity_rows - plan.send_row).clamp(min=0, max=2**31 - 1).to(torch.int32)
+    if plan.send_mask is not None:
+        limit = torch.where(plan.send_mask, limit, torch.full_like(limit, -1))
+    return limit.contiguous()
+
+
 def peer_push(plan: PeerPlan, rows: torch.Tensor, channel, max_ctas: int = 0,
-              src_index: Optional[torch.Tensor] = None, src_div: int = 1) -> None:
+              src_index: Optional[torch.Tensor] = None, src_div: int = 1,
+              dropped: Optional[torch.Tensor] = None) -> None:
     """Rows sorted by global expert -> expert-major (local expert, source) order in the owners' `channel`.
-    With `src_index` / `src_div` the sorted rows are rows[src_index // src_div] (see push_rows)."""
+    With `src_index` / `src_div` the sorted rows are rows[src_index // src_div] (see push_rows).
+    Rows that do not fit into an owner's buffer are never written past its end; they are counted
+    in `dropped` (see push_rows), and the owner's results for them do not exist."""
     row_bytes = rows.shape[1] * rows.element_size()
     assert row_bytes == channel.row_bytes
-    key = ("push", channel.ptrs.data_ptr(), channel.capacity_rows)
+    key = ("push", id(channel))
     if key not in plan.cache:
         dst = (channel.ptrs[plan.dst_rank] + plan.send_row * row_bytes).contiguous()
-        # rows that would not fit into the owner's buffer are dropped, never written past its end
-        limit = (channel.capacity_rows - plan.send_row).clamp(min=0, max=2**31 - 1).to(torch.int32)
-        if plan.send_mask is not None:
-            limit = torch.where(plan.send_mask, limit, torch.zeros_like(limit))  # experts of other plans stay put
-        plan.cache[key] = (dst, limit.contiguous())
-    dst, limit = plan.cache[key]
+        plan.cache[key] = (dst, push_limits(plan, channel.capacity_rows), channel)  # the channel object is kept alive with its key
+    dst, limit, _ = plan.cache[key]
     # every rank starts with the rows of the next rank's experts, so the ranks' writes fan out
     # over distinct destinations instead of converging on one receiver at a time
     e_all = plan.m_sizes.numel() // plan.world
     push_rows(rows, plan.m_sizes, dst, limit, max_ctas, first_expert=((plan.rank + 1) % plan.world) * e_all,
-              src_index=src_index, src_div=src_div)
+              src_index=src_index, src_div=src_div, dropped=dropped)
 
 
 def peer_grouped_gemm(plan: PeerPlan, rows_in, weight: torch.Tensor, rows_out, transposed: bool = False) -> None:
@@ -339,10 +354,14 @@ def peer_grouped_gemm(plan: PeerPlan, rows_in, weight: torch.Tensor, rows_out, t
     results are stored into the source rank's `rows_out` at the rows' position in that rank's order.
     `weight` holds the plan's local experts only."""
     assert weight.shape[0] == plan.e_local
-    key = ("gemm", rows_out.ptrs.data_ptr(), rows_out.row_bytes)
+    key = ("gemm", id(rows_out))
     if key not in plan.cache:
-        plan.cache[key] = (rows_out.ptrs[plan.group_src] + plan.return_row * rows_out.row_bytes).contiguous()
-    scattered_grouped_gemm(rows_in.local, weight, plan.group_sizes, plan.weight_index, plan.cache[key], rows_out.local, transposed)
+        plan.cache[key] = ((rows_out.ptrs[plan.group_src] + plan.return_row * rows_out.row_bytes).contiguous(), rows_out)
+    scattered_grouped_gemm(rows_in.local, weight, plan.group_sizes, plan.weight_index, plan.cache[key][0], rows_out.local, transposed)
+
+
+class ReceiveOverflow(RuntimeError):
+    """Rows of an earlier expert-parallel call did not fit into an owner's receive buffer."""
 
 
 class PeerMoeBlock:
@@ -353,17 +372,41 @@ class PeerMoeBlock:
     pushed into the owners' buffers; gate / up / SiLU-mul run on the owners; the down projection's
     epilogue stores every result row straight back into the token's rank, where the weighted
     combine runs.  Two fences per call, no all-to-all.
+
+    Receive capacity.  In the worst routing every rank sends all its rows to one owner, world *
+    max_rows rows.  By default the receive buffer has that size, so no routing can overflow it.
+    With a smaller `capacity_factor` a skewed routing can: rows that do not fit are never written
+    (nothing is stored out of bounds), the push kernel counts them on the sending rank, and the
+    outputs of the tokens they belong to are WRONG for that call (their result rows are set to NaN,
+    so the output rows are NaN rather than plausible numbers).  The count is copied to the host
+    without stalling the stream and raises `ReceiveOverflow` at the start of the NEXT call on this
+    object, or when `check()` is called; `check_capacity=True` tests before pushing (one host read).
     """
 
     def __init__(self, world: int, rank: int, device, hidden: int, max_rows: int, dtype: torch.dtype,
-                 capacity_factor: float = 1.5, group=None):
-        """max_rows: tokens * top_k per rank; a rank can receive up to capacity_factor * max_rows rows."""
+                 capacity_factor: Optional[float] = None, group=None):
+        """max_rows: tokens * top_k per rank; a rank can receive up to capacity_factor * max_rows rows
+        (None: world * max_rows, which every routing fits into)."""
         self.world, self.rank, self.group = world, rank, group
-        cap = (int(max_rows * capacity_factor) + 7) // 8 * 8
+        factor = float(world) if capacity_factor is None else float(capacity_factor)
+        cap = (int(max_rows * factor) + 7) // 8 * 8
+        self.can_overflow = cap < world * max_rows
         self.ch_x = PeerChannel(cap, hidden, dtype, device, group)
         self.ch_y = PeerChannel(max_rows, hidden, dtype, device, group)
         self.token = torch.zeros(1, device=device)
+        self.dropped = torch.zeros(1, dtype=torch.int32, device=device)   # rows this rank could not deliver, all calls
+        self.dropped_host = torch.zeros(1, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else torch.zeros(1, dtype=torch.int32)
+        self.dropped_seen = torch.cuda.Event()
+        self.dropped_seen.record()
         peer_fence(self.token, group)
+
+    def check(self) -> None:
+        """Raises ReceiveOverflow if rows of an earlier call were dropped (waits for that call's push only)."""
+        self.dropped_seen.synchronize()
+        n = int(self.dropped_host[0])
+        if n:
+            raise ReceiveOverflow(f"{n} rows did not fit into their owners' receive buffers (capacity {self.ch_x.capacity_rows} rows "
+                                  f"per rank); the outputs of the affected tokens were NaN. Build PeerMoeBlock with a larger capacity_factor.")
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, gate_weight: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor,
@@ -377,14 +420,22 @@ class PeerMoeBlock:
         T, H = x.shape
         E, k = gate_weight.shape[0], num_selected
         assert T * k <= self.ch_y.capacity_rows
+        if self.can_overflow:
+            self.check()  # an overflow of the previous call is reported before more work is queued
         x = x.contiguous()
         router_logits = torch.nn.functional.linear(x, gate_weight)
         weights, selected = softmax_topk(router_logits, k, norm_topk_prob, x.dtype)
         m_sizes, sort_idx, inv_sort_idx = get_expert_counts_and_idx(selected.view(T * k), E)
         plan = PeerPlan.build(m_sizes, self.world, self.rank, self.group)
-        if check_capacity:  # one host read; rows beyond the buffer would be dropped, not written out of bounds
+        if check_capacity:  # one host read
             assert int(plan.recv_rows) <= self.ch_x.capacity_rows, "receive buffer too small for this routing"
-        peer_push(plan, x, self.ch_x, src_index=sort_idx, src_div=k)  # token rows are expanded while they travel
+        if self.can_overflow:
+            # result rows that never arrive (their input was dropped) must not be whatever an earlier call left there
+            self.ch_y.local[:T * k].fill_(float("nan"))
+        peer_push(plan, x, self.ch_x, src_index=sort_idx, src_div=k, dropped=self.dropped)  # token rows are expanded while they travel
+        if self.can_overflow:
+            self.dropped_host.copy_(self.dropped, non_blocking=True)
+            self.dropped_seen.record()
         peer_fence(self.token, self.group)  # every rank's rows have arrived (and the previous call's reads are over)
         rows = self.ch_x.local
         h = gate_up_silu_forward(rows, gate_proj, up_proj, plan.local_m_sizes)

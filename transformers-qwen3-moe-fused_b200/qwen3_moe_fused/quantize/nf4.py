@@ -51,6 +51,32 @@ class Nf4State:
     offset: Optional[torch.Tensor] = None
 
 
+@dataclass
+class AbsmaxState:
+    """Second-level state of a double-quantised absmax (the attributes of a bitsandbytes
+    `QuantState.state2` that the decode reads)."""
+    absmax: torch.Tensor  # (n_blocks / blocksize,) fp32
+    code: torch.Tensor  # (256,) fp32 levels in [-1, 1], ascending
+    blocksize: int
+
+
+@torch.no_grad()
+def nest_absmax(state: Nf4State, blocksize2: int = 256) -> Nf4State:
+    """Double quantisation of `state.absmax`: subtract the mean, then 8-bit blockwise absmax
+    quantisation to the nearest of 256 evenly spaced levels.  (bitsandbytes uses a non-uniform
+    256-level table; the decode takes the table as data, so either works.)"""
+    absmax = state.absmax.float()
+    assert absmax.numel() % blocksize2 == 0
+    offset = absmax.mean()
+    centred = (absmax - offset).reshape(-1, blocksize2)
+    absmax2 = centred.abs().amax(dim=1).clamp_min(torch.finfo(torch.float32).tiny)
+    code = torch.linspace(-1.0, 1.0, 256, device=absmax.device, dtype=torch.float32)
+    q = torch.round((centred / absmax2.unsqueeze(1) + 1.0) * 127.5).clamp(0, 255).to(torch.uint8)
+    return Nf4State(absmax=q.reshape(-1).contiguous(), code=state.code, blocksize=state.blocksize, shape=state.shape,
+                    dtype=state.dtype, nested=True, state2=AbsmaxState(absmax2.contiguous(), code, blocksize2),
+                    offset=offset.reshape(1))
+
+
 @torch.no_grad()
 def quantize_nf4(weight: torch.Tensor, blocksize: int = 64) -> tuple[torch.Tensor, Nf4State]:
     """Blockwise absmax NF4 quantisation: each value maps to the nearest table level of
