@@ -238,6 +238,30 @@ int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, const void*
                      const int32_t* dst_limit, int first_expert, const int32_t* src_index,
                      int src_div, int max_ctas, int32_t* dropped, void* stream);
 
+/* Token-deduplicated dispatch: a token whose k experts live on r distinct ranks is sent r times,
+ * not k times.  tokens (T rows of row_bytes) are copied to slot[t * world + d] of rank d's token
+ * buffer (dst_ptrs[d], DEVICE array of `world` addresses; slot is a DEVICE int32 array, -1 = token
+ * t has no expert on rank d).  Slots >= slot_limit would overrun the receiver: not written, counted
+ * in `dropped` (may be NULL).  Destinations are visited starting with first_rank. */
+int moe_ep_push_tokens(const void* tokens, int64_t T, int64_t row_bytes, const int32_t* slot, int world,
+                       int first_rank, const uint64_t* dst_ptrs, int slot_limit, int max_ctas,
+                       int32_t* dropped, void* stream);
+
+/* Companion of moe_ep_push_tokens: for every expanded row r (sorted by expert, m_sizes[e] rows per
+ * expert, M in total; sort_idx[r] / k is its token) the slot of its token on the rank that owns its
+ * expert (expert e lives on rank e / (E / world)) is stored as one int32 at dst_ptrs[e] + 4 i, i =
+ * position of r among the rows of e: the same addressing as moe_ep_push_rows with 4-byte rows.
+ * dst_limit / dropped as there.  The owner reads its rows as tokens[index[row]]. */
+int moe_ep_push_index(const int32_t* slot, int world, const int32_t* sort_idx, int k, int64_t M,
+                      const void* m_sizes, int m_sizes_dtype, int E, const uint64_t* dst_ptrs,
+                      const int32_t* dst_limit, int32_t* dropped, void* stream);
+
+/* Owner's side of the token-deduplicated dispatch: out[r] = tokens[index[r]] for r < min(*n_rows,
+ * max_rows); n_rows is a DEVICE int64 (the received row count of moe_ep_plan), so the call needs no
+ * host read.  An index outside [0, token_rows) reads row 0. */
+int moe_ep_expand_rows(const void* tokens, int64_t token_rows, int64_t row_bytes, const int32_t* index,
+                       const int64_t* n_rows, int64_t max_rows, void* out, void* stream);
+
 /* Row bookkeeping of one routing decision for the exchange above, in one launch.
  * counts (world, E) int32 on the device: rows of every rank per global expert (expert e lives on
  * rank e / (E / world)).  The plan covers local experts lo..hi-1 of every rank (0, E / world for

@@ -223,3 +223,26 @@ def test_push_limits_when_a_receive_buffer_is_too_small(world):
     inside = torch.zeros(E, dtype=torch.bool)
     inside[torch.arange(world) * e_local] = True
     assert (lim[~inside] == -1).all() and torch.equal(lim[inside], counts[0][inside].clamp(min=0) * 0 + lim[inside]) and (lim[inside] >= 0).all()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_token_slots_are_dense_and_unique(world):
+    """Token-deduplicated dispatch bookkeeping: on every destination the slots of all ranks' tokens are
+    exactly 0 .. n-1, rank by rank, each rank's tokens in their own order; a token is sent to a rank iff
+    one of its experts lives there."""
+    from qwen3_moe_fused.parallel_ep import token_destinations, token_slots
+
+    E, T, k = 32, 200, 4
+    e_all = E // world
+    g = torch.Generator().manual_seed(world)
+    sel = [torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]) for _ in range(world)]
+    masks, n_tok = zip(*[token_destinations(s, E, world) for s in sel])
+    tokens_all = torch.stack(n_tok)
+    for s in range(world):
+        want = torch.zeros(T, world, dtype=torch.bool)
+        for d in range(world):
+            want[:, d] = ((sel[s] // e_all) == d).any(dim=1)
+        assert torch.equal(masks[s], want)
+    for d in range(world):
+        got = torch.cat([token_slots(masks[s], tokens_all, s)[:, d][masks[s][:, d]] for s in range(world)])
+        assert torch.equal(got.long(), torch.arange(int(tokens_all[:, d].sum())))

@@ -146,3 +146,54 @@ def test_plan_kernel_matches_tensor_plan(dev, world, E, rng_):
             assert a.send_mask is None and b.send_mask is None
         else:
             assert torch.equal(a.send_mask.cpu(), b.send_mask)
+
+
+class _LocalChannel:
+    """Stand-in for a PeerChannel on one GPU: the buffers of all "ranks" are local tensors."""
+
+    def __init__(self, bufs):
+        self.bufs = bufs
+        self.ptrs = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=bufs[0].device)
+        self.capacity_rows = bufs[0].shape[0]
+        self.row_bytes = bufs[0].shape[1] * bufs[0].element_size()
+
+
+@pytest.mark.parametrize("world,E,T,k,W", [(2, 16, 500, 4, 256), (4, 128, 3000, 8, 512), (8, 128, 1024, 8, 2048)])
+def test_token_deduplicated_dispatch(dev, world, E, T, k, W):
+    """All ranks of an expert-parallel group emulated on one GPU: every token row is stored once per
+    destination rank, every expanded row sends the index of its token there, and the owner's expansion
+    reproduces, bit for bit, the expert-major rows that the one-row-per-(token, expert) push delivers."""
+    from oracle import moe_oracle as O
+    from qwen3_moe_fused.parallel_ep import (PeerPlan, expand_received, peer_push, peer_push_index, peer_push_tokens,
+                                             token_destinations, token_slots)
+
+    rng = np.random.default_rng(world * 100 + T)
+    e_all = E // world
+    sel = [np.stack([rng.choice(E, k, replace=False) for _ in range(T)]) for _ in range(world)]
+    tokens = [torch.randn(T, W, device=dev).to(torch.bfloat16) for _ in range(world)]
+    sorts = [O.get_expert_counts_and_idx_fast(sel[s].reshape(-1), E) for s in range(world)]
+    counts_all = torch.from_numpy(np.stack([c for c, _, _ in sorts])).to(dev)
+    masks, n_tok = zip(*[token_destinations(torch.from_numpy(sel[s]).to(dev), E, world) for s in range(world)])
+    tokens_all = torch.stack(n_tok)
+    # fewer stores than rows: that is the point
+    assert int(tokens_all.sum()) < world * T * k
+    cap = int(counts_all.view(world, world, e_all).sum(dim=(0, 2)).max()) + 8
+    tok_ch = _LocalChannel([torch.zeros(world * T, W, device=dev, dtype=torch.bfloat16) for _ in range(world)])
+    idx_ch = _LocalChannel([torch.full((cap, 1), -7, device=dev, dtype=torch.int32) for _ in range(world)])
+    row_ch = _LocalChannel([torch.zeros(cap, W, device=dev, dtype=torch.bfloat16) for _ in range(world)])
+    plans = [PeerPlan.from_counts(counts_all, world, s) for s in range(world)]
+    for s in range(world):
+        sort_idx = torch.from_numpy(sorts[s][1]).to(dev)
+        slot = token_slots(masks[s], tokens_all, s)
+        assert int((slot >= 0).sum()) == int(tokens_all[s].sum())
+        peer_push_tokens(tokens[s], slot, tok_ch, s)
+        peer_push_index(plans[s], slot, sort_idx, k, idx_ch)
+        peer_push(plans[s], tokens[s], row_ch, src_index=sort_idx, src_div=k)   # the reference dispatch
+    for d in range(world):
+        n = int(plans[d].recv_rows)
+        assert int(tokens_all[:, d].sum()) <= world * T
+        out = torch.full((cap, W), 3.0, device=dev, dtype=torch.bfloat16)
+        expand_received(tok_ch.bufs[d], idx_ch.bufs[d].view(-1), plans[d].recv_rows, out)
+        torch.cuda.synchronize()
+        assert torch.equal(out[:n], row_ch.bufs[d][:n]), f"owner {d}"
+        assert bool((out[n:] == 3.0).all()), "rows past the received count were written"

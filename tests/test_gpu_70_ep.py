@@ -208,16 +208,37 @@ def _block_worker(rank, world, port, out_dir):
         gate_w, gate_p, up_p, down_p = mk(E, H, sc=0.05), mk(E, I, H, sc=0.05), mk(E, I, H, sc=0.05), mk(E, H, I, sc=0.05)
         x = torch.randn(T, H, generator=torch.Generator().manual_seed(200 + rank)).to(bf).to(dev)
         lo, hi = rank * e_local, (rank + 1) * e_local
-        block = PeerMoeBlock(world, rank, dev, H, T * k, bf, capacity_factor=2.0)
-        for _ in range(2):  # the second call reuses the buffers
-            out, logits = block.forward(x, gate_w, gate_p[lo:hi].contiguous(), up_p[lo:hi].contiguous(),
-                                        down_p[lo:hi].contiguous(), k, True)
-        torch.cuda.synchronize()
-        assert _lib.read_error_flag() == 0
         with torch.no_grad():
             ref, ref_logits = moe_block_forward(x.view(1, T, H), gate_w, gate_p, up_p, down_p, k, True)
-        err = float((out.float() - ref.view(T, H).float()).abs().max() / ref.float().abs().max())
-        assert torch.equal(logits, ref_logits) and err < 1e-2, f"rank {rank}: block mismatch {err}"
+        outs = []
+        # token-deduplicated dispatch (default capacity: every routing fits), then one row per (token, expert)
+        for kwargs in (dict(max_tokens=T), dict(capacity_factor=2.0)):
+            block = PeerMoeBlock(world, rank, dev, H, T * k, bf, **kwargs)
+            for _ in range(2):  # the second call reuses the buffers
+                out, logits = block.forward(x, gate_w, gate_p[lo:hi].contiguous(), up_p[lo:hi].contiguous(),
+                                            down_p[lo:hi].contiguous(), k, True)
+            torch.cuda.synchronize()
+            block.check()
+            assert _lib.read_error_flag() == 0
+            err = float((out.float() - ref.view(T, H).float()).abs().max() / ref.float().abs().max())
+            assert torch.equal(logits, ref_logits) and err < 1e-2, f"rank {rank}: block mismatch {err} ({kwargs})"
+            outs.append(out)
+        assert torch.equal(outs[0], outs[1]), "both dispatches deliver the same rows, so the outputs are identical"
+        # a receive buffer that is too small: rows are dropped, never written out of bounds, and the next call raises
+        from qwen3_moe_fused.parallel_ep import ReceiveOverflow
+
+        small = PeerMoeBlock(world, rank, dev, H, T * k, bf, capacity_factor=0.25, max_tokens=T)
+        small.forward(x, gate_w, gate_p[lo:hi].contiguous(), up_p[lo:hi].contiguous(), down_p[lo:hi].contiguous(), k, True)
+        raised = False
+        try:
+            small.forward(x, gate_w, gate_p[lo:hi].contiguous(), up_p[lo:hi].contiguous(), down_p[lo:hi].contiguous(), k, True)
+        except ReceiveOverflow:
+            raised = True
+        flags = torch.tensor([int(raised)], device=dev)
+        dist.all_reduce(flags)
+        assert int(flags) >= 1, "no rank noticed that rows had been dropped"
+        torch.cuda.synchronize()
+        assert _lib.read_error_flag() == 0
     finally:
         dist.destroy_process_group()
 

@@ -87,6 +87,114 @@ ep_push_rows_kernel(const uint4* __restrict__ rows, int64_t M, int row_vecs, con
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Token-deduplicated dispatch.  A token whose k experts live on r distinct ranks travels r
+// times, not k times: every token row is stored once per destination rank, at the slot
+// slot[t][d] of that rank's token buffer (-1: the token has no expert there), and every
+// expanded row (sorted by expert) sends just a 4-byte index, the slot of its token on the
+// rank that owns its expert, to the row's expert-major position there.  The owner expands
+// the rows locally (or gathers them in its GEMM's token load).
+// ---------------------------------------------------------------------------------------
+
+// One warp per token: the row is read once and stored to up to `world` destinations.
+template <int UNROLL>
+__global__ void __launch_bounds__(PUSH_THREADS)
+ep_push_tokens_kernel(const uint4* __restrict__ tokens, int64_t T, int row_vecs, const int32_t* __restrict__ slot,
+                      int world, int first_rank, const uint64_t* __restrict__ dst_ptrs, int slot_limit,
+                      int32_t* __restrict__ dropped) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warps = PUSH_THREADS / 32;
+  for (int64_t t = (int64_t)blockIdx.x * warps + warp; t < T; t += (int64_t)gridDim.x * warps) {
+    const uint4* src = tokens + t * row_vecs;
+    for (int c0 = 0; c0 < row_vecs; c0 += 32 * UNROLL) {
+      uint4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int c = c0 + u * 32 + lane;
+        if (c < row_vecs) v[u] = __ldg(src + c);
+      }
+      // destinations are visited starting at `first_rank`, so that the ranks' stores fan out
+      for (int j = 0; j < world; ++j) {
+        const int d = (first_rank + j) % world;
+        const int sl = slot[t * world + d];
+        if (sl < 0) continue;
+        if (sl >= slot_limit) {  // would overrun the receiver's token buffer: not written, but counted
+          if (dropped != nullptr && lane == 0 && c0 == 0) atomicAdd(dropped, 1);
+          continue;
+        }
+        uint4* dst = reinterpret_cast<uint4*>(dst_ptrs[d]) + (int64_t)sl * row_vecs;
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int c = c0 + u * 32 + lane;
+          if (c < row_vecs) __stcs(dst + c, v[u]);
+        }
+      }
+    }
+  }
+}
+
+// One thread per expanded row r (sorted by expert): the slot of its token on the owner of its expert
+// goes to position i of expert e's index run on that owner (dst_ptrs[e] + 4 i); rows with
+// i >= dst_limit[e] are not written (the row push counts them).
+__global__ void __launch_bounds__(PUSH_THREADS)
+ep_push_index_kernel(const int32_t* __restrict__ slot, int world, int e_all, const int32_t* __restrict__ sort_idx, int k,
+                     int64_t M, const void* __restrict__ m_sizes, int ms64, int E, const uint64_t* __restrict__ dst_ptrs,
+                     const int32_t* __restrict__ dst_limit, int32_t* __restrict__ dropped) {
+  __shared__ int begins[PUSH_MAX_E + 1];
+  push_build_begins(m_sizes, ms64, E, begins);
+  const int64_t total = min(M, (int64_t)begins[E]);
+  for (int64_t r = (int64_t)blockIdx.x * PUSH_THREADS + threadIdx.x; r < total; r += (int64_t)gridDim.x * PUSH_THREADS) {
+    int lo = 0, hi = E;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (begins[mid] <= (int)r) lo = mid; else hi = mid;
+    }
+    const int e = lo;
+    const int local = (int)r - begins[e];
+    if (dst_limit != nullptr) {
+      const int limit = dst_limit[e];
+      if (limit < 0) continue;
+      if (local >= limit) {
+        if (dropped != nullptr) atomicAdd(dropped, 1);
+        continue;
+      }
+    }
+    const int64_t t = sort_idx[r] / k;
+    reinterpret_cast<int32_t*>(dst_ptrs[e])[local] = slot[t * world + e / e_all];
+  }
+}
+
+// The owner's side of the token-deduplicated dispatch: out[r] = tokens[index[r]] for the rows it
+// received, r < min(*n_rows, max_rows) with the count read on the device.  An index outside the
+// token buffer (possible only where a sender dropped rows) reads row 0 instead of faulting.
+template <int UNROLL>
+__global__ void __launch_bounds__(PUSH_THREADS)
+ep_expand_kernel(const uint4* __restrict__ tokens, int64_t token_rows, int row_vecs, const int32_t* __restrict__ index,
+                 const int64_t* __restrict__ n_rows, int64_t max_rows, uint4* __restrict__ out) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warps = PUSH_THREADS / 32;
+  const int64_t total = min(*n_rows, max_rows);
+  for (int64_t r = (int64_t)blockIdx.x * warps + warp; r < total; r += (int64_t)gridDim.x * warps) {
+    int64_t t = index[r];
+    if (t < 0 || t >= token_rows) t = 0;
+    const uint4* src = tokens + t * row_vecs;
+    uint4* dst = out + r * row_vecs;
+    for (int c0 = 0; c0 < row_vecs; c0 += 32 * UNROLL) {
+      uint4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int c = c0 + u * 32 + lane;
+        if (c < row_vecs) v[u] = __ldg(src + c);
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int c = c0 + u * 32 + lane;
+        if (c < row_vecs) __stcs(dst + c, v[u]);
+      }
+    }
+  }
+}
+
 // Row bookkeeping of one routing decision for the peer-memory exchange, in one launch.
 // counts[s][e]: rows of source rank s for global expert e.  Expert e = d * e_all + el lives on
 // rank d.  The plan covers local experts lo..hi-1 of every rank.  On owner d the groups are laid
@@ -187,5 +295,56 @@ MOE_API int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, con
   ep_push_rows_kernel<8><<<(int)grid, PUSH_THREADS, 0, stream>>>(
       reinterpret_cast<const uint4*>(rows), M, (int)(row_bytes / 16), m_sizes, m_sizes_dtype == MOE_I64, E, dst_ptrs, dst_limit, first_expert,
       src_index, src_div, dropped);
+  return launch_status();
+}
+
+MOE_API int moe_ep_push_tokens(const void* tokens, int64_t T, int64_t row_bytes, const int32_t* slot, int world,
+                               int first_rank, const uint64_t* dst_ptrs, int slot_limit, int max_ctas, int32_t* dropped,
+                               void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (T < 0 || row_bytes < 0 || world <= 0 || world > PLAN_MAX_WORLD || T > 0x7fffffffLL || slot_limit < 0) return MOE_ERR_SHAPE;
+  if (first_rank < 0 || first_rank >= world) return MOE_ERR_SHAPE;
+  if (T == 0 || row_bytes == 0) return MOE_OK;
+  if (!tokens || !slot || !dst_ptrs) return MOE_ERR_NULL;
+  if ((row_bytes & 15) || ((uintptr_t)tokens & 15)) return MOE_ERR_ALIGN;
+  const int warps = PUSH_THREADS / 32;
+  int64_t grid = (T + warps - 1) / warps;
+  const int64_t cap = max_ctas > 0 ? max_ctas : (int64_t)sm_count() * 4;
+  if (grid > cap) grid = cap;
+  ep_push_tokens_kernel<8><<<(int)grid, PUSH_THREADS, 0, stream>>>(reinterpret_cast<const uint4*>(tokens), T, (int)(row_bytes / 16),
+                                                                  slot, world, first_rank, dst_ptrs, slot_limit, dropped);
+  return launch_status();
+}
+
+MOE_API int moe_ep_push_index(const int32_t* slot, int world, const int32_t* sort_idx, int k, int64_t M, const void* m_sizes,
+                              int m_sizes_dtype, int E, const uint64_t* dst_ptrs, const int32_t* dst_limit, int32_t* dropped,
+                              void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!is_int_dtype(m_sizes_dtype)) return MOE_ERR_DTYPE;
+  if (M < 0 || M > 0x7fffffffLL || world <= 0 || world > PLAN_MAX_WORLD || E <= 0 || E > PUSH_MAX_E || (E % world) != 0 || k <= 0)
+    return MOE_ERR_SHAPE;
+  if (M == 0) return MOE_OK;
+  if (!slot || !sort_idx || !m_sizes || !dst_ptrs) return MOE_ERR_NULL;
+  int64_t grid = (M + PUSH_THREADS - 1) / PUSH_THREADS;
+  const int64_t cap = (int64_t)sm_count() * 4;
+  if (grid > cap) grid = cap;
+  ep_push_index_kernel<<<(int)grid, PUSH_THREADS, 0, stream>>>(slot, world, E / world, sort_idx, k, M, m_sizes, m_sizes_dtype == MOE_I64,
+                                                             E, dst_ptrs, dst_limit, dropped);
+  return launch_status();
+}
+
+MOE_API int moe_ep_expand_rows(const void* tokens, int64_t token_rows, int64_t row_bytes, const int32_t* index,
+                               const int64_t* n_rows, int64_t max_rows, void* out, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (token_rows < 0 || row_bytes < 0 || max_rows < 0) return MOE_ERR_SHAPE;
+  if (max_rows == 0 || row_bytes == 0) return MOE_OK;
+  if (!tokens || !index || !n_rows || !out || token_rows == 0) return MOE_ERR_NULL;
+  if ((row_bytes & 15) || ((uintptr_t)tokens & 15) || ((uintptr_t)out & 15)) return MOE_ERR_ALIGN;
+  const int warps = PUSH_THREADS / 32;
+  int64_t grid = (max_rows + warps - 1) / warps;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (grid > cap) grid = cap;
+  ep_expand_kernel<8><<<(int)grid, PUSH_THREADS, 0, stream>>>(reinterpret_cast<const uint4*>(tokens), token_rows, (int)(row_bytes / 16),
+                                                             index, n_rows, max_rows, reinterpret_cast<uint4*>(out));
   return launch_status();
 }

@@ -360,6 +360,88 @@ def peer_grouped_gemm(plan: PeerPlan, rows_in, weight: torch.Tensor, rows_out, t
     scattered_grouped_gemm(rows_in.local, weight, plan.group_sizes, plan.weight_index, plan.cache[key][0], rows_out.local, transposed)
 
 
+# ------------------------------------------------------------------------------------------
+# Token-deduplicated dispatch.  With top-k routing a token has k rows, but its experts live on
+# fewer than k ranks (on average 1.99 / 3.6 / 5.25 of 2 / 4 / 8 ranks for k = 8 of 128 experts):
+# the token travels once per destination RANK, and each of its rows sends a 4-byte index.
+# ------------------------------------------------------------------------------------------
+def token_destinations(selected: torch.Tensor, E: int, world: int):
+    """selected (T, k) expert ids.  Returns (mask (T, world) bool: token t has an expert on rank d;
+    n_tokens (world,) int32: tokens this rank sends to each rank)."""
+    T = selected.shape[0]
+    e_all = E // world
+    mask = torch.zeros((T, world), dtype=torch.bool, device=selected.device)
+    mask.scatter_(1, torch.div(selected, e_all, rounding_mode="floor"), True)
+    return mask, mask.sum(dim=0).to(torch.int32)
+
+
+def gather_counts_and_tokens(m_sizes: torch.Tensor, n_tokens: torch.Tensor, world: int, group=None):
+    """One all-gather for both tables: (counts (world, E) int32: rows of every rank per global expert;
+    tokens (world, world) int32: tokens rank s sends to rank d)."""
+    E = m_sizes.numel()
+    mine = torch.cat([m_sizes.to(torch.int32), n_tokens.to(torch.int32)]).contiguous()
+    out = torch.empty(world * (E + world), dtype=torch.int32, device=mine.device)
+    dist.all_gather_into_tensor(out, mine, group=group)
+    out = out.view(world, E + world)
+    return out[:, :E].contiguous(), out[:, E:].contiguous()
+
+
+def token_slots(mask: torch.Tensor, tokens_all: torch.Tensor, rank: int) -> torch.Tensor:
+    """(T, world) int32: slot of this rank's token t in rank d's token buffer (-1 where mask is
+    false).  Rank d's buffer holds the tokens of rank 0, then rank 1, ... ; a rank's tokens keep
+    their order."""
+    base = tokens_all[:rank].sum(dim=0, dtype=torch.int64)              # (world,): tokens of lower ranks on each destination
+    pos = mask.to(torch.int32).cumsum(dim=0, dtype=torch.int64) - 1     # (T, world)
+    return torch.where(mask, pos + base, torch.full_like(pos, -1)).to(torch.int32).contiguous()
+
+
+def peer_push_tokens(tokens: torch.Tensor, slot: torch.Tensor, channel, rank: int, dropped: Optional[torch.Tensor] = None,
+                     max_ctas: int = 0) -> None:
+    """Every token row goes once to each rank that owns one of its experts (slot: see token_slots)."""
+    from . import _lib
+
+    assert tokens.is_cuda and tokens.is_contiguous() and tokens.dim() == 2
+    world = slot.shape[1]
+    assert slot.dtype == torch.int32 and slot.is_contiguous() and slot.shape[0] == tokens.shape[0]
+    row_bytes = tokens.shape[1] * tokens.element_size()
+    assert row_bytes == channel.row_bytes
+    _lib.check(_lib.load().moe_ep_push_tokens(
+        _lib.ptr(tokens), tokens.shape[0], row_bytes, _lib.ptr(slot), world, (rank + 1) % world, _lib.ptr(channel.ptrs),
+        channel.capacity_rows, max_ctas, _lib.ptr(dropped), _lib.stream_ptr(tokens.device)), "moe_ep_push_tokens")
+
+
+def peer_push_index(plan: PeerPlan, slot: torch.Tensor, sort_idx: torch.Tensor, k: int, channel,
+                    dropped: Optional[torch.Tensor] = None) -> None:
+    """The 4-byte companion of peer_push_tokens: for every expanded row (sorted by expert) the slot of its
+    token on the expert's owner, stored at the row's expert-major position in the owners' `channel`
+    (a PeerChannel of int32 rows of width 1)."""
+    from . import _lib
+
+    assert channel.row_bytes == 4 and sort_idx.dtype == torch.int32 and sort_idx.is_contiguous()
+    key = ("index", id(channel))
+    if key not in plan.cache:
+        dst = (channel.ptrs[plan.dst_rank] + plan.send_row * 4).contiguous()
+        plan.cache[key] = (dst, push_limits(plan, channel.capacity_rows), channel)
+    dst, limit, _ = plan.cache[key]
+    _lib.check(_lib.load().moe_ep_push_index(
+        _lib.ptr(slot), plan.world, _lib.ptr(sort_idx), k, sort_idx.numel(), _lib.ptr(plan.m_sizes), _lib.int_code(plan.m_sizes.dtype),
+        plan.m_sizes.numel(), _lib.ptr(dst), _lib.ptr(limit), _lib.ptr(dropped), _lib.stream_ptr(slot.device)), "moe_ep_push_index")
+
+
+def expand_received(tokens: torch.Tensor, index: torch.Tensor, n_rows: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = tokens[index[r]] for the first n_rows rows (n_rows: int64 device scalar, e.g. plan.recv_rows;
+    never read on the host).  Rows beyond stay as they are."""
+    from . import _lib
+
+    assert tokens.is_contiguous() and out.is_contiguous() and index.dtype == torch.int32 and n_rows.dtype == torch.int64
+    assert tokens.shape[1] == out.shape[1] and tokens.dtype == out.dtype
+    max_rows = min(out.shape[0], index.numel())
+    _lib.check(_lib.load().moe_ep_expand_rows(
+        _lib.ptr(tokens), tokens.shape[0], tokens.shape[1] * tokens.element_size(), _lib.ptr(index), _lib.ptr(n_rows), max_rows,
+        _lib.ptr(out), _lib.stream_ptr(tokens.device)), "moe_ep_expand_rows")
+    return out
+
+
 class ReceiveOverflow(RuntimeError):
     """Rows of an earlier expert-parallel call did not fit into an owner's receive buffer."""
 
@@ -367,45 +449,60 @@ class ReceiveOverflow(RuntimeError):
 class PeerMoeBlock:
     """Forward of the sparse MoE block with the experts split over the ranks (inference; no autograd).
 
-    What `moe_block.moe_block_forward` computes for this rank's tokens, with the rows of every
-    token sent to the ranks that own its experts: router, sort and expand run locally; the rows are
-    pushed into the owners' buffers; gate / up / SiLU-mul run on the owners; the down projection's
-    epilogue stores every result row straight back into the token's rank, where the weighted
-    combine runs.  Two fences per call, no all-to-all.
+    What `moe_block.moe_block_forward` computes for this rank's tokens, with every token sent to the
+    ranks that own its experts: router and sort run locally; each token row is stored ONCE into the
+    token buffer of every rank that owns one of its experts, and each of its k rows sends a 4-byte
+    index to its expert-major position there (token-deduplicated dispatch); the owner expands its
+    rows from the received tokens, runs gate / up / SiLU-mul, and the down projection's epilogue
+    stores every result row straight back into the token's rank, where the weighted combine runs.
+    Two fences per call, no all-to-all.  (`max_tokens=None` selects the older dispatch that sends
+    one row per (token, expert).)
 
     Receive capacity.  In the worst routing every rank sends all its rows to one owner, world *
-    max_rows rows.  By default the receive buffer has that size, so no routing can overflow it.
+    max_rows rows.  By default the receive buffers have that size, so no routing can overflow them.
     With a smaller `capacity_factor` a skewed routing can: rows that do not fit are never written
-    (nothing is stored out of bounds), the push kernel counts them on the sending rank, and the
+    (nothing is stored out of bounds), the push kernels count them on the sending rank, and the
     outputs of the tokens they belong to are WRONG for that call (their result rows are set to NaN,
-    so the output rows are NaN rather than plausible numbers).  The count is copied to the host
-    without stalling the stream and raises `ReceiveOverflow` at the start of the NEXT call on this
-    object, or when `check()` is called; `check_capacity=True` tests before pushing (one host read).
+    so the output rows are NaN rather than plausible numbers).  The counts of all ranks are summed
+    inside the call's first fence and copied to the host without stalling the stream; a non-zero
+    sum raises `ReceiveOverflow` on EVERY rank at the start of the NEXT call on this object (so no
+    rank is left waiting in a collective), or when `check()` is called; `check_capacity=True` tests
+    this rank's own receive count before pushing (one host read).
     """
 
     def __init__(self, world: int, rank: int, device, hidden: int, max_rows: int, dtype: torch.dtype,
-                 capacity_factor: Optional[float] = None, group=None):
-        """max_rows: tokens * top_k per rank; a rank can receive up to capacity_factor * max_rows rows
-        (None: world * max_rows, which every routing fits into)."""
+                 capacity_factor: Optional[float] = None, group=None, max_tokens: Optional[int] = None):
+        """max_rows: tokens * top_k per rank; max_tokens: tokens per rank (enables the token-deduplicated
+        dispatch); a rank can receive up to capacity_factor * max_rows rows (None: world * max_rows, which
+        every routing fits into)."""
         self.world, self.rank, self.group = world, rank, group
         factor = float(world) if capacity_factor is None else float(capacity_factor)
         cap = (int(max_rows * factor) + 7) // 8 * 8
         self.can_overflow = cap < world * max_rows
-        self.ch_x = PeerChannel(cap, hidden, dtype, device, group)
+        self.dedup = max_tokens is not None
+        if self.dedup:
+            self.ch_tok = PeerChannel(world * max_tokens, hidden, dtype, device, group)  # every rank's tokens fit
+            self.ch_idx = PeerChannel(cap, 1, torch.int32, device, group)
+            self.rows = torch.empty((cap, hidden), dtype=dtype, device=device)           # expanded locally
+        else:
+            self.ch_x = PeerChannel(cap, hidden, dtype, device, group)
+        self.capacity_rows = cap
         self.ch_y = PeerChannel(max_rows, hidden, dtype, device, group)
-        self.token = torch.zeros(1, device=device)
+        self.token = torch.zeros(2, device=device)   # fence payload: [0] nothing, [1] rows dropped by all ranks
         self.dropped = torch.zeros(1, dtype=torch.int32, device=device)   # rows this rank could not deliver, all calls
-        self.dropped_host = torch.zeros(1, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else torch.zeros(1, dtype=torch.int32)
+        self.dropped_host = torch.zeros(1, dtype=torch.float32).pin_memory()
         self.dropped_seen = torch.cuda.Event()
         self.dropped_seen.record()
         peer_fence(self.token, group)
 
     def check(self) -> None:
-        """Raises ReceiveOverflow if rows of an earlier call were dropped (waits for that call's push only)."""
+        """Raises ReceiveOverflow if rows of an earlier call were dropped by any rank (waits for that call's
+        first fence only).  The count is summed over the ranks inside the fence, so every rank raises at
+        the same call and none is left waiting in a collective."""
         self.dropped_seen.synchronize()
         n = int(self.dropped_host[0])
         if n:
-            raise ReceiveOverflow(f"{n} rows did not fit into their owners' receive buffers (capacity {self.ch_x.capacity_rows} rows "
+            raise ReceiveOverflow(f"{n} rows did not fit into their owners' receive buffers (capacity {self.capacity_rows} rows "
                                   f"per rank); the outputs of the affected tokens were NaN. Build PeerMoeBlock with a larger capacity_factor.")
 
     @torch.no_grad()
@@ -426,18 +523,34 @@ class PeerMoeBlock:
         router_logits = torch.nn.functional.linear(x, gate_weight)
         weights, selected = softmax_topk(router_logits, k, norm_topk_prob, x.dtype)
         m_sizes, sort_idx, inv_sort_idx = get_expert_counts_and_idx(selected.view(T * k), E)
-        plan = PeerPlan.build(m_sizes, self.world, self.rank, self.group)
+        if self.dedup:
+            assert T * self.world <= self.ch_tok.capacity_rows
+            mask, n_tokens = token_destinations(selected, E, self.world)
+            counts_all, tokens_all = gather_counts_and_tokens(m_sizes, n_tokens, self.world, self.group)
+            plan = PeerPlan.from_counts(counts_all, self.world, self.rank)
+        else:
+            plan = PeerPlan.build(m_sizes, self.world, self.rank, self.group)
         if check_capacity:  # one host read
-            assert int(plan.recv_rows) <= self.ch_x.capacity_rows, "receive buffer too small for this routing"
+            assert int(plan.recv_rows) <= self.capacity_rows, "receive buffer too small for this routing"
         if self.can_overflow:
             # result rows that never arrive (their input was dropped) must not be whatever an earlier call left there
             self.ch_y.local[:T * k].fill_(float("nan"))
-        peer_push(plan, x, self.ch_x, src_index=sort_idx, src_div=k, dropped=self.dropped)  # token rows are expanded while they travel
+        if self.dedup:
+            slot = token_slots(mask, tokens_all, self.rank)
+            peer_push_tokens(x, slot, self.ch_tok, self.rank)
+            peer_push_index(plan, slot, sort_idx, k, self.ch_idx, dropped=self.dropped)
+        else:
+            peer_push(plan, x, self.ch_x, src_index=sort_idx, src_div=k, dropped=self.dropped)  # rows are expanded while they travel
         if self.can_overflow:
-            self.dropped_host.copy_(self.dropped, non_blocking=True)
-            self.dropped_seen.record()
+            self.token[1:2].copy_(self.dropped)  # summed over the ranks by the fence
         peer_fence(self.token, self.group)  # every rank's rows have arrived (and the previous call's reads are over)
-        rows = self.ch_x.local
+        if self.can_overflow:
+            self.dropped_host.copy_(self.token[1:2], non_blocking=True)
+            self.dropped_seen.record()
+        if self.dedup:
+            rows = expand_received(self.ch_tok.local, self.ch_idx.local.view(-1), plan.recv_rows, self.rows)
+        else:
+            rows = self.ch_x.local
         h = gate_up_silu_forward(rows, gate_proj, up_proj, plan.local_m_sizes)
         out_ptrs = (self.ch_y.ptrs[plan.group_src] + plan.return_row * self.ch_y.row_bytes).contiguous()
         scattered_grouped_gemm(h, down_proj, plan.group_sizes, plan.weight_index, out_ptrs, self.ch_y.local)
