@@ -238,7 +238,7 @@ def config_dict(args, cfg):
                         f"{cfg['tokens'] * cfg['k']} rows/GPU, in={cfg['K']}, out={cfg['N']}, experts={cfg['E']}",
             "routing": cfg["routing"], "l2": "inputs larger than L2 (weights alone exceed 400 MB); no flush needed",
             "parallelism": "single GPU" if args.gpus == 1 else (
-                f"expert parallel ep{args.gpus}, rows pushed over peer memory, GEMM epilogues store to the source rank"
+                f"expert parallel ep{args.gpus}, rows pushed over peer memory (x once per token and destination rank), GEMM epilogues store to the source rank"
                 if args.ep_transport == "peer" else f"expert parallel ep{args.gpus} (NCCL all-to-all dispatch/combine)")}
 
 
@@ -469,7 +469,7 @@ def run_block_suite(args):
     else:
         from qwen3_moe_fused.parallel_ep import PeerMoeBlock
 
-        block = PeerMoeBlock(world, rank, dev, H, T * k, bf, capacity_factor=1.5)
+        block = PeerMoeBlock(world, rank, dev, H, T * k, bf, capacity_factor=2.0, max_tokens=T if args.ep_dispatch == "dedup" else None)
         block.forward(hidden, gate_w, gp, up, dp, k, True, check_capacity=True)
 
         def fn():
@@ -500,7 +500,8 @@ def run_block_suite(args):
                           "n_gpus": world, "scaling": "weak" if weak else "strong", "steps": args.steps, "ms": ms,
                           "tokens_per_s": T_total / ms * 1e3, "tokens_per_s_48_layers": T_total / ms * 1e3 / 48,
                           "tflops": flops / ms / 1e9, "kernel_wait_errors": err,
-                          "transport": "single GPU" if world == 1 else "peer memory (push + down-projection epilogue stores to the token's rank)"}),
+                          "transport": "single GPU" if world == 1 else "peer memory (tokens pushed once per destination rank + row indices, "
+                                       "down-projection epilogue stores to the token's rank)"}),
               flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -586,6 +587,9 @@ def main():
                     help="N > 1, peer transport: CTAs of the row push that overlaps a GEMM (0: four per SM)")
     ap.add_argument("--ep-overlap", default="on", choices=["on", "off"],
                     help="N > 1, peer transport: run the second row push beside the first GEMM (on) or before it (off)")
+    ap.add_argument("--ep-dispatch", default="dedup", choices=["dedup", "rows"],
+                    help="N > 1, peer transport: x travels once per (token, destination rank) and is expanded by the owner "
+                         "(dedup, default) or once per (token, expert) (rows)")
     ap.add_argument("--ep-chunks", type=int, default=1,
                     help="N > 1, peer transport: chunks of local experts whose exchange and GEMMs are pipelined")
     ap.add_argument("--gemm-path", default="auto", choices=["auto", "tc", "tc_single", "simt"],
@@ -651,13 +655,14 @@ def main():
     if world > 1:
         from qwen3_moe_fused.parallel_ep import ExpertParallelPlan
 
-    def route_and_sort(logits_d, ids_d):
+    def route(logits_d, ids_d):
+        """(T * k,) expert id of every expanded row, token-major."""
         if logits_d is not None:
-            _, sel = softmax_topk(logits_d, k, True, bf)
-            sel = sel.view(-1)
-        else:
-            sel = ids_d
-        return get_expert_counts_and_idx(sel, E)
+            return softmax_topk(logits_d, k, True, bf)[1].view(-1)
+        return ids_d
+
+    def route_and_sort(logits_d, ids_d):
+        return get_expert_counts_and_idx(route(logits_d, ids_d), E)
 
     # ---- resident inputs for the kernel-only measurement ----
     logits_d = logits_h.to(dev) if logits_h is not None else None
@@ -689,6 +694,19 @@ def main():
                 "y": PeerChannel(M, N, bf, dev), "dx": PeerChannel(M, K, bf, dev),
                 "x_all": ch_x, "dy_all": ch_dy, "token": torch.zeros(1, device=dev), "n": n_chunks}
         assert all(int(pl.recv_rows) <= region for pl in peer["plans"]), "receive buffer too small for this routing"
+        dedup = args.ep_dispatch == "dedup" and n_chunks == 1
+        if dedup:
+            # x travels as token rows, once per destination rank, plus a 4-byte index per expanded row;
+            # the owner expands its rows locally into the buffer the GEMMs read
+            from qwen3_moe_fused.parallel_ep import (expand_received, gather_counts_and_tokens, peer_push_index, peer_push_tokens,
+                                                     slot_bases, token_positions)
+
+            pos, n_tok = token_positions(route(logits_d, ids_d).view(T, k), E, world)
+            _, tokens_all = gather_counts_and_tokens(m_sizes, n_tok, world)
+            peer.update(pos=pos, base=slot_bases(tokens_all, rank), tok=PeerChannel(world * T, K, bf, dev),
+                        idx=PeerChannel(cap, 1, torch.int32, dev), sort_idx=sort_idx,
+                        tokens_out=int(tokens_all[rank].sum() - tokens_all[rank, rank]))
+        peer["dedup"] = dedup
         peer_fence(peer["token"])
     torch.cuda.synchronize()
 
@@ -698,7 +716,7 @@ def main():
     # three GEMMs, each preceded by the kernel that builds its per-expert tensor maps; per step at
     # N > 1 also two row pushes (peer) or four row permutations (nccl)
     nck = max(1, min(args.ep_chunks, E_local))
-    launches_per_step = 6 if world == 1 else (8 * nck if args.ep_transport == "peer" else 10)
+    launches_per_step = 6 if world == 1 else (8 * nck + (2 if peer["dedup"] else 0) if args.ep_transport == "peer" else 10)
 
     def step_resident(record: bool):
         if world == 1:
@@ -716,36 +734,55 @@ def main():
             marks[3].record()
             return marks if record else None, (y, dx, dw)
         if peer is not None:
-            # expert parallel over peer memory: rows are pushed to their experts' ranks by a copy
-            # kernel (the second push overlaps the forward GEMM), the forward and dX epilogues store
-            # their results straight into the source ranks' memory; a one-element all-reduce orders
-            # each phase across the ranks.
-            #   comm:    push dy | fence | push x | fence
-            #   compute:                 | dX              | forward | dW | fence
-            # (per chunk of local experts when --ep-chunks > 1; one chunk measured fastest)
+            # expert parallel over peer memory: rows are pushed to their experts' ranks by copy kernels,
+            # the forward and dX epilogues store their results straight into the source ranks' memory; a
+            # one-element all-reduce orders each phase across the ranks.
+            #   comm:    push dY | fence | x: tokens + indices | fence | expand
+            #   compute:                 | dX                          | forward | dW | fence
+            # dY goes first and is exposed; x (token rows once per destination rank: a third to a quarter of
+            # the bytes of one row per (token, expert)) travels beside the dX GEMM.  Measured alternatives at
+            # 2 GPUs: x first and the push of dY beside the forward GEMM is slower (1.65 against 1.51 ms: both
+            # send over NVLink and the GEMM's remote stores queue behind the push, whatever the push's CTA
+            # count); per chunk of local experts (--ep-chunks > 1) is slower too (fences and launches).
             marks = [ev() for _ in range(4)]
             main = torch.cuda.current_stream()
             nc = peer["n"]
             e_x = [torch.cuda.Event() for _ in range(nc)]
             e_dy = [torch.cuda.Event() for _ in range(nc)]
-            # dY (the smaller operand) goes first and dX runs first: the exposed first push is shorter
             push_stream = comm_stream if args.ep_overlap == "on" else main
             comm_stream.wait_stream(main)
+
+            def run_forward():
+                for i in range(nc):
+                    main.wait_event(e_x[i])
+                    peer_grouped_gemm(peer["plans"][i], peer["x"][i], peer["w"][i], peer["y"])
+
+            def run_dx():
+                for i in range(nc):
+                    main.wait_event(e_dy[i])
+                    peer_grouped_gemm(peer["plans"][i], peer["dy"][i], peer["w"][i], peer["dx"], transposed=True)
+
+            def push(rows, chans, events, ctas):
+                for i in range(nc):
+                    peer_push(peer["plans"][i], rows, chans[i], ctas)
+                    peer_fence(peer["token"])
+                    events[i].record()
+
             with torch.cuda.stream(push_stream):
-                for rows, chans, events, ctas in ((dy_d, peer["dy"], e_dy, 0), (x_d, peer["x"], e_x, args.push_ctas)):
-                    for i in range(nc):
-                        peer_push(peer["plans"][i], rows, chans[i], ctas)  # the second push runs beside a GEMM
-                        peer_fence(peer["token"])
-                        events[i].record()
-            for i in range(nc):
-                main.wait_event(e_dy[i])
-                if i == 0:
-                    marks[0].record()
-                peer_grouped_gemm(peer["plans"][i], peer["dy"][i], peer["w"][i], peer["dx"], transposed=True)
-            marks[1].record()  # marks 0-1: dX, 1-2: forward (including its wait for x), 2-3: dW
-            for i in range(nc):
-                main.wait_event(e_x[i])
-                peer_grouped_gemm(peer["plans"][i], peer["x"][i], peer["w"][i], peer["y"])
+                push(dy_d, peer["dy"], e_dy, 0)
+                if peer["dedup"]:
+                    peer_push_tokens(hidden_d, peer["pos"], peer["base"], peer["tok"], rank, max_ctas=args.push_ctas)
+                    peer_push_index(peer["plans"][0], peer["pos"], peer["base"], peer["sort_idx"], k, peer["idx"])
+                    peer_fence(peer["token"])
+                    expand_received(peer["tok"].local, peer["idx"].local.view(-1), peer["plans"][0].recv_rows, peer["x"][0].local)
+                    e_x[0].record()
+                else:
+                    push(x_d, peer["x"], e_x, args.push_ctas)     # beside the dX GEMM
+            main.wait_event(e_dy[0])
+            marks[0].record()   # marks 0-1: dX, 1-2: forward (including its wait for x), 2-3: dW
+            run_dx()
+            marks[1].record()
+            run_forward()
             marks[2].record()
             dw = [grouped_gemm_backward_dw(peer["x"][i].local, peer["dy"][i].local, peer["plans"][i].local_m_sizes, bf)
                   for i in range(nc)]
@@ -857,11 +894,21 @@ def main():
             dx = grouped_gemm_forward_transposed(dyd, w, ms)
             dw = grouped_gemm_backward_dw(xs, dyd, ms, bf)
         elif peer is not None:
-            pl = PeerPlan.build(ms, world, rank)
             cx, cdy = peer["x_all"], peer["dy_all"]
-            peer_push(pl, xs, cx)
+            if peer["dedup"]:
+                pos_i, n_tok_i = token_positions(route(lg, idd).view(T, k), E, world)
+                counts_i, tokens_i = gather_counts_and_tokens(ms, n_tok_i, world)
+                pl = PeerPlan.from_counts(counts_i, world, rank)
+                base_i = slot_bases(tokens_i, rank)
+                peer_push_tokens(hd, pos_i, base_i, peer["tok"], rank)
+                peer_push_index(pl, pos_i, base_i, si, k, peer["idx"])
+            else:
+                pl = PeerPlan.build(ms, world, rank)
+                peer_push(pl, xs, cx)
             peer_push(pl, dyd, cdy)
             peer_fence(peer["token"])
+            if peer["dedup"]:
+                expand_received(peer["tok"].local, peer["idx"].local.view(-1), pl.recv_rows, cx.local)
             peer_grouped_gemm(pl, cx, w, peer["y"])
             peer_grouped_gemm(pl, cdy, w, peer["dx"], transposed=True)
             dw = grouped_gemm_backward_dw(cx.local, cdy.local, pl.local_m_sizes, bf)
@@ -927,9 +974,16 @@ def main():
         own = int(m_sizes.view(world, E_local)[rank].sum())
         remote_bytes = (M - own) * K * 2
         if peer is not None:
+            if peer["dedup"]:
+                remote_bytes = peer["tokens_out"] * K * 2 + (M - own) * 4
+
             def exchange():
-                for i in range(peer["n"]):
-                    peer_push(peer["plans"][i], x_d, peer["x"][i])
+                if peer["dedup"]:
+                    peer_push_tokens(hidden_d, peer["pos"], peer["base"], peer["tok"], rank)
+                    peer_push_index(peer["plans"][0], peer["pos"], peer["base"], peer["sort_idx"], k, peer["idx"])
+                else:
+                    for i in range(peer["n"]):
+                        peer_push(peer["plans"][i], x_d, peer["x"][i])
                 peer_fence(peer["token"])
         else:
             def exchange():
@@ -1047,7 +1101,8 @@ def main():
             line["ep_check"] = ep_check
         if world > 1:
             line["exchange"] = {"what": "dispatch of x alone (rows to their experts' ranks), rank 0's remote bytes",
-                                "transport": args.ep_transport, "ms": xchg_ms, "remote_bytes": remote_bytes,
+                                "transport": args.ep_transport, "dispatch": (args.ep_dispatch if peer is not None and peer["dedup"] else "rows"),
+                                "ms": xchg_ms, "remote_bytes": remote_bytes,
                                 "gbs_out": remote_bytes / (xchg_ms * 1e-3) / 1e9, "nvlink_peak_gbs_per_direction": 900.0}
         if world == 1 and not args.no_extra and not args.only and args.workload == "gate_up" and not args.tokens and not args.experts:
             line["extra_workloads"] = [measure_single_gpu_workload("down", min(args.steps, 50), args.warmup, dev)]

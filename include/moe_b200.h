@@ -239,22 +239,30 @@ int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, const void*
                      int src_div, int max_ctas, int32_t* dropped, void* stream);
 
 /* Token-deduplicated dispatch: a token whose k experts live on r distinct ranks is sent r times,
- * not k times.  tokens (T rows of row_bytes) are copied to slot[t * world + d] of rank d's token
- * buffer (dst_ptrs[d], DEVICE array of `world` addresses; slot is a DEVICE int32 array, -1 = token
- * t has no expert on rank d).  Slots >= slot_limit would overrun the receiver: not written, counted
- * in `dropped` (may be NULL).  Destinations are visited starting with first_rank. */
-int moe_ep_push_tokens(const void* tokens, int64_t T, int64_t row_bytes, const int32_t* slot, int world,
-                       int first_rank, const uint64_t* dst_ptrs, int slot_limit, int max_ctas,
-                       int32_t* dropped, void* stream);
+ * not k times.  Step 1, bookkeeping (one launch): selected holds T * k expert ids (token-major,
+ * int32/int64); expert e lives on rank e / (E / world).  pos[t * world + d] (DEVICE int32) = number of
+ * earlier tokens of this rank that also have an expert on rank d, or -1 if token t has none there;
+ * n_tokens[d] = tokens with an expert on d (what the ranks exchange to lay out their token buffers). */
+int moe_ep_token_positions(const void* selected, int sel_dtype, int64_t T, int k, int E, int world,
+                           int32_t* pos, int32_t* n_tokens, void* stream);
 
-/* Companion of moe_ep_push_tokens: for every expanded row r (sorted by expert, m_sizes[e] rows per
- * expert, M in total; sort_idx[r] / k is its token) the slot of its token on the rank that owns its
- * expert (expert e lives on rank e / (E / world)) is stored as one int32 at dst_ptrs[e] + 4 i, i =
- * position of r among the rows of e: the same addressing as moe_ep_push_rows with 4-byte rows.
- * dst_limit / dropped as there.  The owner reads its rows as tokens[index[row]]. */
-int moe_ep_push_index(const int32_t* slot, int world, const int32_t* sort_idx, int k, int64_t M,
-                      const void* m_sizes, int m_sizes_dtype, int E, const uint64_t* dst_ptrs,
-                      const int32_t* dst_limit, int32_t* dropped, void* stream);
+/* Step 2: tokens (T rows of row_bytes) are copied to slot pos[t * world + d] + slot_base[d] of rank
+ * d's token buffer (dst_ptrs[d], DEVICE array of `world` addresses; slot_base: DEVICE int32 per rank,
+ * NULL = zeros: where this rank's tokens start on rank d) wherever pos is not negative.  Slots >=
+ * slot_limit would overrun the receiver: not written, counted in `dropped` (may be NULL).
+ * Destinations are visited starting with first_rank. */
+int moe_ep_push_tokens(const void* tokens, int64_t T, int64_t row_bytes, const int32_t* pos,
+                       const int32_t* slot_base, int world, int first_rank, const uint64_t* dst_ptrs,
+                       int slot_limit, int max_ctas, int32_t* dropped, void* stream);
+
+/* Step 3: for every expanded row r (sorted by expert, m_sizes[e] rows per expert, M in total;
+ * sort_idx[r] / k is its token) the slot of its token on the rank that owns its expert is stored as
+ * one int32 at dst_ptrs[e] + 4 i, i = position of r among the rows of e: the same addressing as
+ * moe_ep_push_rows with 4-byte rows.  dst_limit / dropped as there.  The owner reads its rows as
+ * tokens[index[row]]. */
+int moe_ep_push_index(const int32_t* pos, const int32_t* slot_base, int world, const int32_t* sort_idx,
+                      int k, int64_t M, const void* m_sizes, int m_sizes_dtype, int E,
+                      const uint64_t* dst_ptrs, const int32_t* dst_limit, int32_t* dropped, void* stream);
 
 /* Owner's side of the token-deduplicated dispatch: out[r] = tokens[index[r]] for r < min(*n_rows,
  * max_rows); n_rows is a DEVICE int64 (the received row count of moe_ep_plan), so the call needs no

@@ -230,19 +230,19 @@ def test_token_slots_are_dense_and_unique(world):
     """Token-deduplicated dispatch bookkeeping: on every destination the slots of all ranks' tokens are
     exactly 0 .. n-1, rank by rank, each rank's tokens in their own order; a token is sent to a rank iff
     one of its experts lives there."""
-    from qwen3_moe_fused.parallel_ep import token_destinations, token_slots
+    from qwen3_moe_fused.parallel_ep import slot_bases, token_positions
 
     E, T, k = 32, 200, 4
     e_all = E // world
     g = torch.Generator().manual_seed(world)
     sel = [torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]) for _ in range(world)]
-    masks, n_tok = zip(*[token_destinations(s, E, world) for s in sel])
+    poss, n_tok = zip(*[token_positions(s, E, world) for s in sel])
     tokens_all = torch.stack(n_tok)
     for s in range(world):
         want = torch.zeros(T, world, dtype=torch.bool)
         for d in range(world):
             want[:, d] = ((sel[s] // e_all) == d).any(dim=1)
-        assert torch.equal(masks[s], want)
+        assert torch.equal(poss[s] >= 0, want)
     for d in range(world):
-        got = torch.cat([token_slots(masks[s], tokens_all, s)[:, d][masks[s][:, d]] for s in range(world)])
+        got = torch.cat([(poss[s][:, d] + slot_bases(tokens_all, s)[d])[poss[s][:, d] >= 0] for s in range(world)])
         assert torch.equal(got.long(), torch.arange(int(tokens_all[:, d].sum())))

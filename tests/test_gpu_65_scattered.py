@@ -164,8 +164,8 @@ def test_token_deduplicated_dispatch(dev, world, E, T, k, W):
     destination rank, every expanded row sends the index of its token there, and the owner's expansion
     reproduces, bit for bit, the expert-major rows that the one-row-per-(token, expert) push delivers."""
     from oracle import moe_oracle as O
-    from qwen3_moe_fused.parallel_ep import (PeerPlan, expand_received, peer_push, peer_push_index, peer_push_tokens,
-                                             token_destinations, token_slots)
+    from qwen3_moe_fused.parallel_ep import (PeerPlan, expand_received, peer_push, peer_push_index, peer_push_tokens, slot_bases,
+                                             token_positions)
 
     rng = np.random.default_rng(world * 100 + T)
     e_all = E // world
@@ -173,8 +173,12 @@ def test_token_deduplicated_dispatch(dev, world, E, T, k, W):
     tokens = [torch.randn(T, W, device=dev).to(torch.bfloat16) for _ in range(world)]
     sorts = [O.get_expert_counts_and_idx_fast(sel[s].reshape(-1), E) for s in range(world)]
     counts_all = torch.from_numpy(np.stack([c for c, _, _ in sorts])).to(dev)
-    masks, n_tok = zip(*[token_destinations(torch.from_numpy(sel[s]).to(dev), E, world) for s in range(world)])
+    poss, n_tok = zip(*[token_positions(torch.from_numpy(sel[s]).to(dev), E, world) for s in range(world)])
     tokens_all = torch.stack(n_tok)
+    # the kernel's bookkeeping equals the tensor-op definition
+    for s in range(world):
+        ref_pos, ref_n = token_positions(torch.from_numpy(sel[s]), E, world)
+        assert torch.equal(poss[s].cpu(), ref_pos) and torch.equal(n_tok[s].cpu(), ref_n)
     # fewer stores than rows: that is the point
     assert int(tokens_all.sum()) < world * T * k
     cap = int(counts_all.view(world, world, e_all).sum(dim=(0, 2)).max()) + 8
@@ -184,10 +188,10 @@ def test_token_deduplicated_dispatch(dev, world, E, T, k, W):
     plans = [PeerPlan.from_counts(counts_all, world, s) for s in range(world)]
     for s in range(world):
         sort_idx = torch.from_numpy(sorts[s][1]).to(dev)
-        slot = token_slots(masks[s], tokens_all, s)
-        assert int((slot >= 0).sum()) == int(tokens_all[s].sum())
-        peer_push_tokens(tokens[s], slot, tok_ch, s)
-        peer_push_index(plans[s], slot, sort_idx, k, idx_ch)
+        base = slot_bases(tokens_all, s)
+        assert int((poss[s] >= 0).sum()) == int(tokens_all[s].sum())
+        peer_push_tokens(tokens[s], poss[s], base, tok_ch, s)
+        peer_push_index(plans[s], poss[s], base, sort_idx, k, idx_ch)
         peer_push(plans[s], tokens[s], row_ch, src_index=sort_idx, src_div=k)   # the reference dispatch
     for d in range(world):
         n = int(plans[d].recv_rows)

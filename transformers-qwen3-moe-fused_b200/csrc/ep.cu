@@ -10,6 +10,7 @@ namespace moe {
 
 constexpr int PUSH_THREADS = 256;
 constexpr int PUSH_MAX_E = 1024;
+constexpr int PLAN_MAX_WORLD_TOK = 16;  // ranks of one expert-parallel group (= PLAN_MAX_WORLD)
 
 // begins[e] = rows before expert e; computed by warp 0, E / 32 consecutive entries per lane.
 __device__ __forceinline__ void push_build_begins(const void* m_sizes, int ms64, int E, int* begins) {
@@ -96,12 +97,82 @@ ep_push_rows_kernel(const uint4* __restrict__ rows, int64_t M, int row_vecs, con
 // the rows locally (or gathers them in its GEMM's token load).
 // ---------------------------------------------------------------------------------------
 
+// Bookkeeping of the token-deduplicated dispatch, one CTA: for token t and rank d, pos[t * world + d] =
+// number of earlier tokens (of this rank) that also have an expert on rank d, or -1 when t has none there;
+// n_tokens[d] = tokens with an expert on d.  selected: T * k expert ids, token-major.
+constexpr int TOKPOS_THREADS = 1024;
+
+__global__ void __launch_bounds__(TOKPOS_THREADS)
+ep_token_positions_kernel(const void* __restrict__ selected, int sel64, int64_t T, int k, int e_all, int world,
+                          int32_t* __restrict__ pos, int32_t* __restrict__ n_tokens) {
+  // Rounds of 1024 consecutive tokens, one per thread (a warp reads its 32 tokens' ids as one contiguous
+  // run).  Per destination: ballot -> position inside the warp, warp totals scanned by warp d.
+  __shared__ int32_t warp_cnt[PLAN_MAX_WORLD_TOK][TOKPOS_THREADS / 32];
+  __shared__ int32_t round_total[PLAN_MAX_WORLD_TOK];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t lower = (1u << lane) - 1u;
+  int32_t running[PLAN_MAX_WORLD_TOK];
+#pragma unroll
+  for (int d = 0; d < PLAN_MAX_WORLD_TOK; ++d) running[d] = 0;
+  auto dest_mask = [&](int64_t t) {
+    uint32_t m = 0;
+    if (t < T) {
+      for (int j = 0; j < k; ++j) {
+        const int64_t e = sel64 ? __ldg(reinterpret_cast<const int64_t*>(selected) + t * k + j)
+                                : (int64_t)__ldg(reinterpret_cast<const int32_t*>(selected) + t * k + j);
+        const int64_t d = e / e_all;
+        if (d >= 0 && d < world) m |= 1u << d;
+      }
+    }
+    return m;
+  };
+  uint32_t m_next = dest_mask(tid);
+  for (int64_t base = 0; base < T; base += TOKPOS_THREADS) {
+    const int64_t t = base + tid;
+    const uint32_t m = m_next;
+    m_next = dest_mask(t + TOKPOS_THREADS);  // the next round's ids are in flight during this round's scan
+    int32_t in_warp[PLAN_MAX_WORLD_TOK];
+#pragma unroll
+    for (int d = 0; d < PLAN_MAX_WORLD_TOK; ++d) {
+      if (d < world) {
+        const uint32_t b = __ballot_sync(0xffffffffu, (m >> d) & 1u);
+        in_warp[d] = __popc(b & lower);
+        if (lane == 0) warp_cnt[d][warp] = __popc(b);
+      }
+    }
+    __syncthreads();
+    if (warp < world) {  // warp d scans the 32 warp totals of destination d
+      const int32_t w = warp_cnt[warp][lane];
+      int32_t incl = w;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      warp_cnt[warp][lane] = incl - w;
+      if (lane == 31) round_total[warp] = incl;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int d = 0; d < PLAN_MAX_WORLD_TOK; ++d) {
+      if (d < world) {
+        if (t < T) pos[t * world + d] = ((m >> d) & 1u) ? running[d] + warp_cnt[d][warp] + in_warp[d] : -1;
+        running[d] += round_total[d];
+      }
+    }
+    __syncthreads();  // warp_cnt / round_total are rewritten by the next round
+  }
+#pragma unroll
+  for (int d = 0; d < PLAN_MAX_WORLD_TOK; ++d)
+    if (d < world && tid == d) n_tokens[d] = running[d];
+}
+
 // One warp per token: the row is read once and stored to up to `world` destinations.
 template <int UNROLL>
 __global__ void __launch_bounds__(PUSH_THREADS)
-ep_push_tokens_kernel(const uint4* __restrict__ tokens, int64_t T, int row_vecs, const int32_t* __restrict__ slot,
-                      int world, int first_rank, const uint64_t* __restrict__ dst_ptrs, int slot_limit,
-                      int32_t* __restrict__ dropped) {
+ep_push_tokens_kernel(const uint4* __restrict__ tokens, int64_t T, int row_vecs, const int32_t* __restrict__ pos,
+                      const int32_t* __restrict__ slot_base, int world, int first_rank, const uint64_t* __restrict__ dst_ptrs,
+                      int slot_limit, int32_t* __restrict__ dropped) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps = PUSH_THREADS / 32;
   for (int64_t t = (int64_t)blockIdx.x * warps + warp; t < T; t += (int64_t)gridDim.x * warps) {
@@ -116,8 +187,9 @@ ep_push_tokens_kernel(const uint4* __restrict__ tokens, int64_t T, int row_vecs,
       // destinations are visited starting at `first_rank`, so that the ranks' stores fan out
       for (int j = 0; j < world; ++j) {
         const int d = (first_rank + j) % world;
-        const int sl = slot[t * world + d];
-        if (sl < 0) continue;
+        const int ps = pos[t * world + d];
+        if (ps < 0) continue;
+        const int sl = ps + (slot_base ? slot_base[d] : 0);
         if (sl >= slot_limit) {  // would overrun the receiver's token buffer: not written, but counted
           if (dropped != nullptr && lane == 0 && c0 == 0) atomicAdd(dropped, 1);
           continue;
@@ -137,9 +209,9 @@ ep_push_tokens_kernel(const uint4* __restrict__ tokens, int64_t T, int row_vecs,
 // goes to position i of expert e's index run on that owner (dst_ptrs[e] + 4 i); rows with
 // i >= dst_limit[e] are not written (the row push counts them).
 __global__ void __launch_bounds__(PUSH_THREADS)
-ep_push_index_kernel(const int32_t* __restrict__ slot, int world, int e_all, const int32_t* __restrict__ sort_idx, int k,
-                     int64_t M, const void* __restrict__ m_sizes, int ms64, int E, const uint64_t* __restrict__ dst_ptrs,
-                     const int32_t* __restrict__ dst_limit, int32_t* __restrict__ dropped) {
+ep_push_index_kernel(const int32_t* __restrict__ pos, const int32_t* __restrict__ slot_base, int world, int e_all,
+                     const int32_t* __restrict__ sort_idx, int k, int64_t M, const void* __restrict__ m_sizes, int ms64, int E,
+                     const uint64_t* __restrict__ dst_ptrs, const int32_t* __restrict__ dst_limit, int32_t* __restrict__ dropped) {
   __shared__ int begins[PUSH_MAX_E + 1];
   push_build_begins(m_sizes, ms64, E, begins);
   const int64_t total = min(M, (int64_t)begins[E]);
@@ -160,7 +232,8 @@ ep_push_index_kernel(const int32_t* __restrict__ slot, int world, int e_all, con
       }
     }
     const int64_t t = sort_idx[r] / k;
-    reinterpret_cast<int32_t*>(dst_ptrs[e])[local] = slot[t * world + e / e_all];
+    const int d = e / e_all;
+    reinterpret_cast<int32_t*>(dst_ptrs[e])[local] = pos[t * world + d] + (slot_base ? slot_base[d] : 0);
   }
 }
 
@@ -298,9 +371,19 @@ MOE_API int moe_ep_push_rows(const void* rows, int64_t M, int64_t row_bytes, con
   return launch_status();
 }
 
-MOE_API int moe_ep_push_tokens(const void* tokens, int64_t T, int64_t row_bytes, const int32_t* slot, int world,
-                               int first_rank, const uint64_t* dst_ptrs, int slot_limit, int max_ctas, int32_t* dropped,
-                               void* stream_) {
+MOE_API int moe_ep_token_positions(const void* selected, int sel_dtype, int64_t T, int k, int E, int world, int32_t* pos,
+                                   int32_t* n_tokens, void* stream_) {
+  if (!is_int_dtype(sel_dtype)) return MOE_ERR_DTYPE;
+  if (T < 0 || T > 0x7fffffffLL || k <= 0 || world <= 0 || world > PLAN_MAX_WORLD_TOK || E <= 0 || (E % world) != 0) return MOE_ERR_SHAPE;
+  if (!n_tokens || (T > 0 && (!selected || !pos))) return MOE_ERR_NULL;
+  ep_token_positions_kernel<<<1, TOKPOS_THREADS, 0, (cudaStream_t)stream_>>>(selected, sel_dtype == MOE_I64, T, k, E / world, world, pos,
+                                                                              n_tokens);
+  return launch_status();
+}
+
+MOE_API int moe_ep_push_tokens(const void* tokens, int64_t T, int64_t row_bytes, const int32_t* slot, const int32_t* slot_base,
+                               int world, int first_rank, const uint64_t* dst_ptrs, int slot_limit, int max_ctas,
+                               int32_t* dropped, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (T < 0 || row_bytes < 0 || world <= 0 || world > PLAN_MAX_WORLD || T > 0x7fffffffLL || slot_limit < 0) return MOE_ERR_SHAPE;
   if (first_rank < 0 || first_rank >= world) return MOE_ERR_SHAPE;
@@ -312,13 +395,13 @@ MOE_API int moe_ep_push_tokens(const void* tokens, int64_t T, int64_t row_bytes,
   const int64_t cap = max_ctas > 0 ? max_ctas : (int64_t)sm_count() * 4;
   if (grid > cap) grid = cap;
   ep_push_tokens_kernel<8><<<(int)grid, PUSH_THREADS, 0, stream>>>(reinterpret_cast<const uint4*>(tokens), T, (int)(row_bytes / 16),
-                                                                  slot, world, first_rank, dst_ptrs, slot_limit, dropped);
+                                                                  slot, slot_base, world, first_rank, dst_ptrs, slot_limit, dropped);
   return launch_status();
 }
 
-MOE_API int moe_ep_push_index(const int32_t* slot, int world, const int32_t* sort_idx, int k, int64_t M, const void* m_sizes,
-                              int m_sizes_dtype, int E, const uint64_t* dst_ptrs, const int32_t* dst_limit, int32_t* dropped,
-                              void* stream_) {
+MOE_API int moe_ep_push_index(const int32_t* slot, const int32_t* slot_base, int world, const int32_t* sort_idx, int k, int64_t M,
+                              const void* m_sizes, int m_sizes_dtype, int E, const uint64_t* dst_ptrs, const int32_t* dst_limit,
+                              int32_t* dropped, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (!is_int_dtype(m_sizes_dtype)) return MOE_ERR_DTYPE;
   if (M < 0 || M > 0x7fffffffLL || world <= 0 || world > PLAN_MAX_WORLD || E <= 0 || E > PUSH_MAX_E || (E % world) != 0 || k <= 0)
@@ -328,8 +411,8 @@ MOE_API int moe_ep_push_index(const int32_t* slot, int world, const int32_t* sor
   int64_t grid = (M + PUSH_THREADS - 1) / PUSH_THREADS;
   const int64_t cap = (int64_t)sm_count() * 4;
   if (grid > cap) grid = cap;
-  ep_push_index_kernel<<<(int)grid, PUSH_THREADS, 0, stream>>>(slot, world, E / world, sort_idx, k, M, m_sizes, m_sizes_dtype == MOE_I64,
-                                                             E, dst_ptrs, dst_limit, dropped);
+  ep_push_index_kernel<<<(int)grid, PUSH_THREADS, 0, stream>>>(slot, slot_base, world, E / world, sort_idx, k, M, m_sizes,
+                                                             m_sizes_dtype == MOE_I64, E, dst_ptrs, dst_limit, dropped);
   return launch_status();
 }
 

@@ -51,8 +51,9 @@ SIGNATURES = {
     "moe_combine": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _P]),
     "moe_ep_plan": (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "moe_ep_push_rows": (_I, [_P, _L, _L, _P, _I, _I, _P, _P, _I, _P, _I, _I, _P, _P]),
-    "moe_ep_push_tokens": (_I, [_P, _L, _L, _P, _I, _I, _P, _I, _I, _P, _P]),
-    "moe_ep_push_index": (_I, [_P, _I, _P, _I, _L, _P, _I, _I, _P, _P, _P, _P]),
+    "moe_ep_token_positions": (_I, [_P, _I, _L, _I, _I, _I, _P, _P, _P]),
+    "moe_ep_push_tokens": (_I, [_P, _L, _L, _P, _P, _I, _I, _P, _I, _I, _P, _P]),
+    "moe_ep_push_index": (_I, [_P, _P, _I, _P, _I, _L, _P, _I, _I, _P, _P, _P, _P]),
     "moe_ep_expand_rows": (_I, [_P, _L, _L, _P, _P, _L, _P, _P]),
     "moe_grouped_gemm_fwd_scattered": (_I, [_P, _P, _P, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_grouped_gemm_dx_scattered": (_I, [_P, _P, _P, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),

@@ -365,14 +365,26 @@ def peer_grouped_gemm(plan: PeerPlan, rows_in, weight: torch.Tensor, rows_out, t
 # fewer than k ranks (on average 1.99 / 3.6 / 5.25 of 2 / 4 / 8 ranks for k = 8 of 128 experts):
 # the token travels once per destination RANK, and each of its rows sends a 4-byte index.
 # ------------------------------------------------------------------------------------------
-def token_destinations(selected: torch.Tensor, E: int, world: int):
-    """selected (T, k) expert ids.  Returns (mask (T, world) bool: token t has an expert on rank d;
-    n_tokens (world,) int32: tokens this rank sends to each rank)."""
-    T = selected.shape[0]
-    e_all = E // world
-    mask = torch.zeros((T, world), dtype=torch.bool, device=selected.device)
-    mask.scatter_(1, torch.div(selected, e_all, rounding_mode="floor"), True)
-    return mask, mask.sum(dim=0).to(torch.int32)
+def token_positions(selected: torch.Tensor, E: int, world: int):
+    """selected (T, k) expert ids.  Returns (pos (T, world) int32: number of earlier tokens of this rank
+    that also have an expert on rank d, -1 where token t has none there; n_tokens (world,) int32: tokens
+    this rank sends to each rank).  One kernel on the GPU."""
+    T, k = selected.shape
+    if selected.is_cuda:
+        from . import _lib
+
+        selected = _lib.as_index_tensor(selected).contiguous()
+        pos = torch.empty((T, world), dtype=torch.int32, device=selected.device)
+        n_tokens = torch.empty(world, dtype=torch.int32, device=selected.device)
+        with torch.cuda.device(selected.device):
+            _lib.check(_lib.load().moe_ep_token_positions(
+                _lib.ptr(selected), _lib.int_code(selected.dtype), T, k, E, world, _lib.ptr(pos), _lib.ptr(n_tokens),
+                _lib.stream_ptr(selected.device)), "moe_ep_token_positions")
+        return pos, n_tokens
+    mask = torch.zeros((T, world), dtype=torch.bool)
+    mask.scatter_(1, torch.div(selected, E // world, rounding_mode="floor"), True)
+    pos = mask.to(torch.int32).cumsum(dim=0, dtype=torch.int32) - 1
+    return torch.where(mask, pos, torch.full_like(pos, -1)).contiguous(), mask.sum(dim=0).to(torch.int32)
 
 
 def gather_counts_and_tokens(m_sizes: torch.Tensor, n_tokens: torch.Tensor, world: int, group=None):
@@ -386,31 +398,31 @@ def gather_counts_and_tokens(m_sizes: torch.Tensor, n_tokens: torch.Tensor, worl
     return out[:, :E].contiguous(), out[:, E:].contiguous()
 
 
-def token_slots(mask: torch.Tensor, tokens_all: torch.Tensor, rank: int) -> torch.Tensor:
-    """(T, world) int32: slot of this rank's token t in rank d's token buffer (-1 where mask is
-    false).  Rank d's buffer holds the tokens of rank 0, then rank 1, ... ; a rank's tokens keep
-    their order."""
-    base = tokens_all[:rank].sum(dim=0, dtype=torch.int64)              # (world,): tokens of lower ranks on each destination
-    pos = mask.to(torch.int32).cumsum(dim=0, dtype=torch.int64) - 1     # (T, world)
-    return torch.where(mask, pos + base, torch.full_like(pos, -1)).to(torch.int32).contiguous()
+def slot_bases(tokens_all: torch.Tensor, rank: int) -> torch.Tensor:
+    """(world,) int32: where this rank's tokens start in each rank's token buffer.  Rank d's buffer holds
+    the tokens of rank 0, then rank 1, ...; a rank's tokens keep their order, so the slot of token t on
+    rank d is slot_bases[d] + pos[t, d]."""
+    return tokens_all[:rank].sum(dim=0, dtype=torch.int32).contiguous()
 
 
-def peer_push_tokens(tokens: torch.Tensor, slot: torch.Tensor, channel, rank: int, dropped: Optional[torch.Tensor] = None,
-                     max_ctas: int = 0) -> None:
-    """Every token row goes once to each rank that owns one of its experts (slot: see token_slots)."""
+def peer_push_tokens(tokens: torch.Tensor, pos: torch.Tensor, slot_base: torch.Tensor, channel, rank: int,
+                     dropped: Optional[torch.Tensor] = None, max_ctas: int = 0) -> None:
+    """Every token row goes once to each rank that owns one of its experts (pos / slot_base: see
+    token_positions and slot_bases)."""
     from . import _lib
 
     assert tokens.is_cuda and tokens.is_contiguous() and tokens.dim() == 2
-    world = slot.shape[1]
-    assert slot.dtype == torch.int32 and slot.is_contiguous() and slot.shape[0] == tokens.shape[0]
+    world = pos.shape[1]
+    assert pos.dtype == torch.int32 and pos.is_contiguous() and pos.shape[0] == tokens.shape[0]
+    assert slot_base.dtype == torch.int32 and slot_base.numel() == world
     row_bytes = tokens.shape[1] * tokens.element_size()
     assert row_bytes == channel.row_bytes
     _lib.check(_lib.load().moe_ep_push_tokens(
-        _lib.ptr(tokens), tokens.shape[0], row_bytes, _lib.ptr(slot), world, (rank + 1) % world, _lib.ptr(channel.ptrs),
-        channel.capacity_rows, max_ctas, _lib.ptr(dropped), _lib.stream_ptr(tokens.device)), "moe_ep_push_tokens")
+        _lib.ptr(tokens), tokens.shape[0], row_bytes, _lib.ptr(pos), _lib.ptr(slot_base), world, (rank + 1) % world,
+        _lib.ptr(channel.ptrs), channel.capacity_rows, max_ctas, _lib.ptr(dropped), _lib.stream_ptr(tokens.device)), "moe_ep_push_tokens")
 
 
-def peer_push_index(plan: PeerPlan, slot: torch.Tensor, sort_idx: torch.Tensor, k: int, channel,
+def peer_push_index(plan: PeerPlan, pos: torch.Tensor, slot_base: torch.Tensor, sort_idx: torch.Tensor, k: int, channel,
                     dropped: Optional[torch.Tensor] = None) -> None:
     """The 4-byte companion of peer_push_tokens: for every expanded row (sorted by expert) the slot of its
     token on the expert's owner, stored at the row's expert-major position in the owners' `channel`
@@ -424,8 +436,9 @@ def peer_push_index(plan: PeerPlan, slot: torch.Tensor, sort_idx: torch.Tensor, 
         plan.cache[key] = (dst, push_limits(plan, channel.capacity_rows), channel)
     dst, limit, _ = plan.cache[key]
     _lib.check(_lib.load().moe_ep_push_index(
-        _lib.ptr(slot), plan.world, _lib.ptr(sort_idx), k, sort_idx.numel(), _lib.ptr(plan.m_sizes), _lib.int_code(plan.m_sizes.dtype),
-        plan.m_sizes.numel(), _lib.ptr(dst), _lib.ptr(limit), _lib.ptr(dropped), _lib.stream_ptr(slot.device)), "moe_ep_push_index")
+        _lib.ptr(pos), _lib.ptr(slot_base), plan.world, _lib.ptr(sort_idx), k, sort_idx.numel(), _lib.ptr(plan.m_sizes),
+        _lib.int_code(plan.m_sizes.dtype), plan.m_sizes.numel(), _lib.ptr(dst), _lib.ptr(limit), _lib.ptr(dropped),
+        _lib.stream_ptr(pos.device)), "moe_ep_push_index")
 
 
 def expand_received(tokens: torch.Tensor, index: torch.Tensor, n_rows: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -525,7 +538,7 @@ class PeerMoeBlock:
         m_sizes, sort_idx, inv_sort_idx = get_expert_counts_and_idx(selected.view(T * k), E)
         if self.dedup:
             assert T * self.world <= self.ch_tok.capacity_rows
-            mask, n_tokens = token_destinations(selected, E, self.world)
+            pos, n_tokens = token_positions(selected, E, self.world)
             counts_all, tokens_all = gather_counts_and_tokens(m_sizes, n_tokens, self.world, self.group)
             plan = PeerPlan.from_counts(counts_all, self.world, self.rank)
         else:
@@ -536,9 +549,9 @@ class PeerMoeBlock:
             # result rows that never arrive (their input was dropped) must not be whatever an earlier call left there
             self.ch_y.local[:T * k].fill_(float("nan"))
         if self.dedup:
-            slot = token_slots(mask, tokens_all, self.rank)
-            peer_push_tokens(x, slot, self.ch_tok, self.rank)
-            peer_push_index(plan, slot, sort_idx, k, self.ch_idx, dropped=self.dropped)
+            base = slot_bases(tokens_all, self.rank)
+            peer_push_tokens(x, pos, base, self.ch_tok, self.rank)
+            peer_push_index(plan, pos, base, sort_idx, k, self.ch_idx, dropped=self.dropped)
         else:
             peer_push(plan, x, self.ch_x, src_index=sort_idx, src_div=k, dropped=self.dropped)  # rows are expanded while they travel
         if self.can_overflow:
