@@ -88,10 +88,10 @@ def make_routing(cfg, seed: int):
 
 
 class ClockSampler:
-    """Samples SM clock, power and throttle reasons while a timed region runs: NVML every 10 ms from a
+    """Samples SM clock, power and throttle reasons while a timed region runs: NVML every 25 ms from a
     thread of this process (read-only queries), or `nvidia-smi -lms 100` where NVML cannot be loaded."""
 
-    PERIOD_S = 0.010
+    PERIOD_S = 0.025
 
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -163,7 +163,7 @@ class ClockSampler:
             sm = [c for c, _, _ in self.samples]
             return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_min_mhz": min(sm) if sm else None,
                     "sm_max_mhz": self.max_mhz, "power_w_max": max((p for _, p, _ in self.samples), default=None),
-                    "reasons": reasons, "samples": len(sm), "source": "nvml, 10 ms period"}
+                    "reasons": reasons, "samples": len(sm), "source": "nvml, 25 ms period"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -594,7 +594,13 @@ def main():
                     help="N > 1, peer transport: chunks of local experts whose exchange and GEMMs are pipelined")
     ap.add_argument("--gemm-path", default="auto", choices=["auto", "tc", "tc_single", "simt"],
                     help="kernel family for the grouped GEMMs (default: CTA-pair tcgen05 where eligible)")
+    ap.add_argument("--watchdog-s", type=int, default=600,
+                    help="dump every thread's stack and exit if the run has not finished after this many seconds (0: off)")
     args = ap.parse_args()
+    if args.watchdog_s > 0:
+        import faulthandler
+
+        faulthandler.dump_traceback_later(args.watchdog_s, exit=True)
     cfg = dict(WORKLOADS[args.workload])
     if args.tokens:
         cfg["tokens"] = args.tokens
@@ -831,19 +837,25 @@ def main():
     n_warm = args.warmup if (args.no_e2e and args.only) else max(args.warmup, 3)
     for _ in range(n_warm):
         step_resident(False)
-    barrier()
+    # the sampler starts before the barrier: its set-up takes milliseconds on rank 0 alone, which the other
+    # ranks would otherwise spend inside their timed region waiting for rank 0's first fence
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    barrier()
     t_start, t_end = ev(), ev()
     all_marks = []
     t_start.record()
+    host_t0 = time.perf_counter()
     for _ in range(args.steps):
         marks, _ = step_resident(True)
         all_marks.append(marks)
+    host_issue_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps  # host time to enqueue a step
     t_end.record()
     barrier()
     resident_ms = t_start.elapsed_time(t_end) / args.steps
+    # device time between the last GEMM of a step and the first GEMM of the next (exchange, fences, idle)
+    gaps = [all_marks[i][3].elapsed_time(all_marks[i + 1][0]) for i in range(len(all_marks) - 1)]
     clocks = sampler.stop() if rank == 0 else None  # samples of the resident loop only
     first, second = ("dx", "fwd") if peer is not None else ("fwd", "dx")  # the peer schedule runs dX first
     for marks in all_marks:
@@ -943,10 +955,10 @@ def main():
         upload(0)
         for i in range(3):
             step_e2e(i, i == 2)
-        barrier()
         if rank == 0:
             e2e_sampler = ClockSampler(local_rank)
             e2e_sampler.start()
+        barrier()
         e0, e1 = ev(), ev()
         e0.record()
         upload(0)  # the first step's upload is inside the timed region too
@@ -1097,6 +1109,9 @@ def main():
         for name, ms in burst_ms.items():
             line["kernels"][name].update(isolated_ms=ms, isolated_tflops=flops_one / (ms * 1e-3) / 1e12,
                                          isolated_frac_of_burst_peak=flops_one / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"])
+        line["step_issue"] = {"host_ms_per_step": host_issue_ms,
+                              "between_steps_ms": ({"p50": float(np.median(gaps)), "max": float(np.max(gaps))} if gaps else None),
+                              "note": "host time to enqueue one step; device time from a step's last GEMM to the next step's first"}
         if ep_check is not None:
             line["ep_check"] = ep_check
         if world > 1:

@@ -310,6 +310,12 @@ int moe_grouped_gemm_dx_scattered(const void* x, const void* w, const void* grou
  * No counterpart in the reference. */
 int moe_debug_read_error(int* flag_out, int clear);
 
+/* Diagnostic counter: how many times, since the library was loaded, a role of a tensor-core kernel
+ * found the barrier of the tile ring complete before the tile id of its round was visible in shared
+ * memory and had to wait for it (harmless, but worth knowing).  Synchronises the device.
+ * No counterpart in the reference. */
+int moe_debug_read_late_values(int* out);
+
 /* Text describing the most recent host-side set-up failure on the calling thread (for
  * instance the driver's answer to a tensor-map encode), "" if there was none.
  * No counterpart in the reference. */

@@ -28,6 +28,7 @@ int tc_gate_up_silu(const void* x, const void* w_gate, const void* w_up, const v
                     int64_t M, int I, int K, int E, int dtype, void* ws, size_t ws_bytes, cudaStream_t stream);
 int tc_read_error(int* flag_out, bool clear);
 size_t tc_workspace_bytes(int E);
+int tc_read_late_values(int* out);
 const char* tc_last_detail();
 
 static std::atomic<int> g_path{MOE_PATH_AUTO};
@@ -219,6 +220,11 @@ MOE_API int moe_grouped_gemm_dx_scattered(const void* x, const void* w, const vo
 MOE_API int moe_debug_read_error(int* flag_out, int clear) {
   if (!flag_out) return MOE_ERR_NULL;
   return tc_read_error(flag_out, clear != 0);
+}
+
+MOE_API int moe_debug_read_late_values(int* out) {
+  if (!out) return MOE_ERR_NULL;
+  return tc_read_late_values(out);
 }
 
 MOE_API const char* moe_debug_last_detail(void) { return tc_last_detail(); }

@@ -17,6 +17,7 @@ namespace tc {
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 __device__ int g_tc_error = 0;  // 0 = none; otherwise (code << 16) | blockIdx.x of first reporter
+__device__ int g_tc_late_values = 0;  // diagnostic counter of the tile ring (see TileFeed::take)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -183,6 +184,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 __device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
 __device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
@@ -249,6 +251,17 @@ __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.b
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Barrier over `nthreads` threads that also tells every one of them whether any passed a true `pred`:
+// the epilogue warps use it to leave their loop together (a warp that left on its own would leave the
+// others waiting at their next named barrier for ever).
+__device__ __forceinline__ bool named_barrier_any(int id, int nthreads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %3, 0;\n\tbar.red.or.pred q, %1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r) : "r"(id), "r"(nthreads), "r"((uint32_t)pred) : "memory");
+  return r != 0;
 }
 
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {  // one warp in each CTA

@@ -1056,4 +1056,10 @@ int tc_read_error(int* flag_out, bool clear) {
   return MOE_OK;
 }
 
+// Diagnostic counter of the tile ring: how often a reader found the ring's barrier complete before the
+// value of its round was visible (it then waited for the value).
+int tc_read_late_values(int* out) {
+  return cuda_status(cudaMemcpyFromSymbol(out, tc::g_tc_late_values, sizeof(int)));
+}
+
 }  // namespace moe

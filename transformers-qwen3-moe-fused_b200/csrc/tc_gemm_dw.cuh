@@ -278,7 +278,7 @@ dw_kernel(const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
     bool ok = true;
     while (ok) {
       const int item = feed.take_warp(lane);
-      if (item < 0) break;
+      if (named_barrier_any(2, 128, item < 0)) break;  // the four warps leave together
       const int e = sorted[item / per_expert];
       const int j = (int)(item % per_expert);
       const int n0 = (j % n_tiles) * ROWS + (int)rank * 128;
@@ -287,7 +287,7 @@ dw_kernel(const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
       const uint32_t acc = acc_it & 1;
       const uint32_t acc_ph = (acc_it >> 1) & 1;
       if (rows > 0) {
-        if (!mbar_wait_cluster(&ctl->tmem_full[acc], acc_ph, abort_flag, W_TMEM_FULL)) { ok = false; break; }
+        if (named_barrier_any(2, 128, !mbar_wait_cluster(&ctl->tmem_full[acc], acc_ph, abort_flag, W_TMEM_FULL))) { ok = false; break; }
         tc_fence_after_sync();
       }
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);

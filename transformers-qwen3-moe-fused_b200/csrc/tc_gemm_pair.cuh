@@ -77,7 +77,7 @@ enum { REG_E0 = 0, REG_RA = 1, REG_RB = 2, REG_E1 = 3 };
 constexpr int PAIR_STAGING_BYTES = 32 * 128;  // 32 tokens x 64 weight rows x 16 bit
 
 enum PairWaitCode { PW_EMPTY = 11, PW_FULL = 12, PW_TMEM_EMPTY = 13, PW_TMEM_FULL = 14, PW_PEER = 15,
-                    PW_SCHED_FULL = 17, PW_SCHED_EMPTY = 18 };
+                    PW_SCHED_FULL = 17, PW_SCHED_EMPTY = 18, PW_SCHED_VALUE = 19 };
 
 template <typename T>
 __device__ __forceinline__ void store_scalar(void* out, int64_t idx, float v) {
@@ -202,16 +202,27 @@ struct TileFeed {
   __device__ __forceinline__ TileFeed(SchedRing* r, volatile int* a)
       : ring(r), home_empty0(NCTA == 2 ? map_to_cta(smem_u32(&r->empty[0]), HOME) : smem_u32(&r->empty[0])), abort_flag(a) {}
 
+  // A slot holds (tile + 1) with the parity of its round (n / SCHED_DEPTH) in bit 31, so that a reader
+  // can tell the id of its round from the one the slot held a round earlier.
+  static __device__ __forceinline__ uint32_t encode(int tile, uint32_t round_parity) {
+    return ((uint32_t)(tile + 1) & 0x7fffffffu) | (round_parity << 31);
+  }
   static __device__ __forceinline__ void init(SchedRing* r) {  // one thread per CTA, before the barriers are used
-    for (int q = 0; q < SCHED_DEPTH; ++q) { mbar_init(&r->full[q], 1); mbar_init(&r->empty[q], READERS); }
+    for (int q = 0; q < SCHED_DEPTH; ++q) {
+      mbar_init(&r->full[q], 1);
+      mbar_init(&r->empty[q], READERS);
+      r->tile[q] = (int)0x80000000u;  // parity 1: not a value of round 0
+    }
   }
   // drawing thread: make `tile` (or -1: no more tiles) visible to every reader
   __device__ __forceinline__ bool publish(int tile) {
     const uint32_t q = n % SCHED_DEPTH, ph = (n / SCHED_DEPTH) & 1;
     if (!mbar_wait_cluster(&ring->empty[q], ph ^ 1, abort_flag, PW_SCHED_EMPTY)) return false;
-    ring->tile[q] = tile;
+    const uint32_t v = encode(tile, ph);
+    *(volatile uint32_t*)&ring->tile[q] = v;
     if constexpr (NCTA == 2) {
-      st_shared_cluster_u32(map_to_cta(smem_u32(&ring->tile[q]), HOME ^ 1), (uint32_t)tile);
+      st_shared_cluster_u32(map_to_cta(smem_u32(&ring->tile[q]), HOME ^ 1), v);
+      fence_acq_rel_cluster();  // the value is in both CTAs' shared memory before either barrier hears of it
       mbar_arrive_release_cluster(map_to_cta(smem_u32(&ring->full[q]), 0));
       mbar_arrive_release_cluster(map_to_cta(smem_u32(&ring->full[q]), 1));
     } else {
@@ -233,11 +244,26 @@ struct TileFeed {
   __device__ __forceinline__ int take() {
     const uint32_t q = n % SCHED_DEPTH, ph = (n / SCHED_DEPTH) & 1;
     if (!mbar_wait_cluster(&ring->full[q], ph, abort_flag, PW_SCHED_FULL)) return -1;
-    const int tile = *(volatile int*)&ring->tile[q];
+    // the slot must hold this round's value (checked, not assumed: all roles of the pair have to agree
+    // on the tile, or their barrier counts and byte counts stop matching)
+    uint32_t v = *(volatile uint32_t*)&ring->tile[q];
+    if ((v >> 31) != ph) {
+      const unsigned long long t0 = global_ns();
+      do {
+        v = *(volatile uint32_t*)&ring->tile[q];
+        if (global_ns() - t0 > WAIT_LIMIT_NS) {
+          atomicCAS(&g_tc_error, 0, (PW_SCHED_VALUE << 16) | (int)(blockIdx.x & 0xffff));
+          *abort_flag = 1;
+          return -1;
+        }
+      } while ((v >> 31) != ph);
+      atomicAdd(&g_tc_late_values, 1);  // diagnostic: the barrier completed before the value was visible
+    }
+    fence_acq_rel_cluster();  // the read is over before the slot is handed back
     if constexpr (NCTA == 2) mbar_arrive_cluster(home_empty0 + q * 8);
     else mbar_arrive(&ring->empty[q]);
     ++n;
-    return tile;
+    return (int)(v & 0x7fffffffu) - 1;
   }
   // a whole warp: lane 0 takes the id and signs the slot off for the warp
   __device__ __forceinline__ int take_warp(int lane) {
@@ -490,7 +516,7 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     int last_e = -1;
     while (true) {
       const int tile = feed.take_warp(lane);
-      if (tile < 0) break;
+      if (named_barrier_any(2, 128, tile < 0)) break;  // the four warps leave together
       const PairTile t = decode(tile);
       const uint32_t par = seq & 1;
       const uint32_t full_ph = (seq >> 1) & 1;
@@ -498,7 +524,7 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       const bool n_ok = n < p.N;
       const CUtensorMap* my = staged ? p.group_maps + (size_t)GM_OUT * p.E + t.e : nullptr;
       if (staged && epi_tid == 0 && t.e != last_e) { tensormap_acquire(my); last_e = t.e; }
-      if (!mbar_wait_cluster(&ctl->tmem_full[par], full_ph, abort_flag, PW_TMEM_FULL)) break;
+      if (named_barrier_any(2, 128, !mbar_wait_cluster(&ctl->tmem_full[par], full_ph, abort_flag, PW_TMEM_FULL))) break;
       tc_fence_after_sync();
       const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
 

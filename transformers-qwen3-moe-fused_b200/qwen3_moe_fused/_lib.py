@@ -58,6 +58,7 @@ SIGNATURES = {
     "moe_grouped_gemm_fwd_scattered": (_I, [_P, _P, _P, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_grouped_gemm_dx_scattered": (_I, [_P, _P, _P, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_debug_read_error": (_I, [_P, _I]),
+    "moe_debug_read_late_values": (_I, [_P]),
     "moe_debug_last_detail": (c_char_p, []),
 }
 
@@ -135,6 +136,12 @@ def is_int_tensor(x: torch.Tensor) -> bool:
 
 def set_gemm_path(path: int) -> int:
     return load().moe_set_gemm_path(path)
+
+
+def read_late_values() -> int:
+    v = ctypes.c_int(0)
+    check(load().moe_debug_read_late_values(ctypes.addressof(v)), "moe_debug_read_late_values")
+    return v.value
 
 
 def read_error_flag(clear: bool = True) -> int:
