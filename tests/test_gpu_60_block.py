@@ -131,3 +131,42 @@ def test_fast_lora_forward_backward(cuda, dtype, quant):
                             (Au.grad, Aur.grad, "dAu"), (Bu.grad, Bur.grad, "dBu"), (Aw.grad, Awr.grad, "dAw"),
                             (Bw.grad, Bwr.grad, "dBw")):
         assert rel(got, want) < tol, name
+
+
+def test_block_patch_installs_the_fused_forward(cuda):
+    """`patch_Qwen3MoeFusedSparseMoeBlock_forward` on a class with the reference block's attributes
+    (modular_qwen3_moe_fused.py:62-77 of the reference): same output and gradients as the block's own
+    sequence of calls, and LoRA-wrapped projections are refused."""
+    from torch import nn
+
+    from qwen3_moe_fused.moe_block import MoeFusedLinear, moe_block_forward, patch_Qwen3MoeFusedSparseMoeBlock_forward
+
+    class Block(nn.Module):
+        def __init__(self, H, I, E, k):
+            super().__init__()
+            self.num_experts, self.num_selected, self.norm_topk_prob = E, k, True
+            self.gate = nn.Linear(H, E, bias=False)
+            self.gate_proj, self.up_proj, self.down_proj = MoeFusedLinear(H, I, E), MoeFusedLinear(H, I, E), MoeFusedLinear(I, H, E)
+
+        def forward(self, hidden_states):
+            raise AssertionError("the patch replaces this")
+
+    torch.manual_seed(4)
+    H, I, E, k, T = 256, 192, 8, 2, 300
+    blk = Block(H, I, E, k).to(cuda).to(torch.bfloat16)
+    patch_Qwen3MoeFusedSparseMoeBlock_forward(Block)
+    x = torch.randn(1, T, H, device=cuda).to(torch.bfloat16).requires_grad_()
+    out, logits = blk(x)
+    out.float().square().sum().backward()
+    x2 = x.detach().clone().requires_grad_()
+    ref, ref_logits = moe_block_forward(x2, blk.gate.weight.detach(), blk.gate_proj.weight.detach(), blk.up_proj.weight.detach(),
+                                        blk.down_proj.weight.detach(), k, True)
+    ref.float().square().sum().backward()
+    assert torch.equal(out, ref) and torch.equal(logits, ref_logits) and torch.equal(x.grad, x2.grad)
+    assert blk.down_proj.weight.grad is not None and blk.gate.weight.grad is not None
+    with torch.no_grad():  # inference: gate, up and SiLU-mul in one kernel, same bits
+        out_ng, _ = blk(x)
+    assert torch.equal(out_ng, out)
+    blk.up_proj.base_layer = blk.up_proj  # what a LoRA wrapper looks like
+    with pytest.raises(NotImplementedError):
+        blk(x)

@@ -91,6 +91,17 @@ CHILD = textwrap.dedent(
     lin(torch.zeros(3, 8), torch.tensor([1, 1, 1, 0]))
     assert len(calls) == 1 and calls[0][1] is lin.weight
     modular.moe_fused_linear = real
+    # the block patch of this package installs on the reference's block class
+    from qwen3_moe_fused import moe_block
+    moe_block.patch_Qwen3MoeFusedSparseMoeBlock_forward()
+    assert modular.Qwen3MoeFusedSparseMoeBlock.forward is moe_block.fused_sparse_moe_block_forward
+    from transformers import Qwen3MoeConfig
+    cfg = Qwen3MoeConfig(hidden_size=16, moe_intermediate_size=8, num_experts=4, num_experts_per_tok=2, norm_topk_prob=True)
+    blk = modular.Qwen3MoeFusedSparseMoeBlock(cfg)
+    seen = []
+    moe_block.moe_block_forward = lambda *a: seen.append(a) or (torch.zeros(1, 3, 16), torch.zeros(3, 4))
+    out, logits = blk(torch.zeros(1, 3, 16))
+    assert seen and seen[0][1] is blk.gate.weight and seen[0][2] is blk.gate_proj.weight and seen[0][5] == 2
     print("overlay ok")
     """
 )

@@ -11,6 +11,7 @@
 // buffered in TMEM so the epilogue of tile i overlaps the main loop of tile i+1.
 // No tile ever crosses an expert boundary on the store side: an M tile starts at a group's
 // first row and rows past the group's end are computed but not stored.
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -605,9 +606,24 @@ static constexpr int smem_bytes_for(int E, int tables) {
   return ((BN == 256) ? 4 : 6) * (A_STAGE_BYTES + (BN < 64 ? 64 : BN) * BK * 2) + (int)sizeof(Control) + tables * (E + 1) * 4 + 1024;
 }
 
+// Per-kernel, per-device memo of launch set-up that does not change between calls: a call of a thin
+// (LoRA-sized) GEMM would otherwise spend more host time on attribute and occupancy queries than the
+// kernel runs.  Each template instantiation of the two helpers below has its own table.
+constexpr int MEMO_DEVICES = 64;
+static int current_device() {
+  int dev = 0;
+  return (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < MEMO_DEVICES) ? dev : -1;
+}
+
+// Raises the kernel's dynamic shared-memory limit to at least `bytes` (once per device and size).
 template <typename K>
 static int set_smem(K kernel, int bytes) {
-  return cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  static std::atomic<int> granted[MEMO_DEVICES];
+  const int dev = current_device();
+  if (dev >= 0 && granted[dev].load(std::memory_order_acquire) >= bytes) return MOE_OK;
+  const int st = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  if (st == MOE_OK && dev >= 0) granted[dev].store(bytes, std::memory_order_release);
+  return st;
 }
 
 }  // namespace tc
@@ -641,6 +657,13 @@ static void bind_context_once() {
 // Number of CTA pairs that can be resident at once (persistent grid = 2 x this).
 template <typename Kern>
 static int resident_pairs(Kern kernel, int smem_bytes, int threads = 192) {
+  // memo: (shared-memory bytes << 8 | result) of the last query on each device
+  static std::atomic<long long> memo[tc::MEMO_DEVICES];
+  const int dev = tc::current_device();
+  if (dev >= 0) {
+    const long long m = memo[dev].load(std::memory_order_acquire);
+    if (m != 0 && (m >> 8) == (long long)smem_bytes) return (int)(m & 0xff);
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * sm_count());
   cfg.blockDim = dim3(threads);
@@ -656,7 +679,9 @@ static int resident_pairs(Kern kernel, int smem_bytes, int threads = 192) {
     n = sm_count() / 2;
   }
   const int cap = sm_count() / 2;
-  return n < cap ? n : cap;
+  n = n < cap ? n : cap;
+  if (dev >= 0 && n < 256) memo[dev].store(((long long)smem_bytes << 8) | n, std::memory_order_release);
+  return n;
 }
 
 template <typename... KArgs, typename... Args>

@@ -130,6 +130,24 @@ def stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+_WORKSPACES: dict = {}
+
+
+def workspace(device: torch.device, nbytes: int) -> tuple[int | None, int]:
+    """(128-byte aligned device address, nbytes) of scratch memory for a launch on the current stream of
+    `device`.  One buffer per (device, stream) is kept and grown on demand instead of allocating per
+    call: launches on one stream run in order, so the next launch may overwrite the scratch of the
+    previous one; launches on different streams get different buffers."""
+    if nbytes <= 0:
+        return None, 0
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_ptr(device))
+    buf = _WORKSPACES.get(key)
+    if buf is None or buf.numel() < nbytes + 128:
+        buf = torch.empty(max(nbytes + 128, 1 << 16), device=device, dtype=torch.uint8)
+        _WORKSPACES[key] = buf
+    return (buf.data_ptr() + 127) & ~127, nbytes
+
+
 def is_int_tensor(x: torch.Tensor) -> bool:
     return x.dtype in {torch.uint8, torch.int8, torch.int16, torch.int32, torch.int64}
 

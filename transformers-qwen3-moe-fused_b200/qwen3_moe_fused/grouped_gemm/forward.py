@@ -18,11 +18,10 @@ def _launch(name: str, which: int, a, b, m_sizes, out, M: int, N: int, K: int, E
     m_sizes = _lib.as_index_tensor(m_sizes)
     fn = getattr(lib, name)
     # scratch for the per-expert tensor maps the tensor-core kernels derive from m_sizes
-    ws_bytes = lib.moe_grouped_gemm_workspace_bytes(which, M, N, K, E)
-    ws = torch.empty(ws_bytes, device=a.device, dtype=torch.uint8) if ws_bytes else None
+    ws_ptr, ws_bytes = _lib.workspace(a.device, lib.moe_grouped_gemm_workspace_bytes(which, M, N, K, E))
     status = fn(
         _lib.ptr(a), _lib.ptr(b), _lib.ptr(m_sizes), _lib.int_code(m_sizes.dtype), _lib.ptr(out),
-        M, N, K, E, _lib.float_code(a.dtype), _lib.float_code(out.dtype), _lib.ptr(ws), ws_bytes,
+        M, N, K, E, _lib.float_code(a.dtype), _lib.float_code(out.dtype), ws_ptr, ws_bytes,
         _lib.stream_ptr(a.device),
     )
     _lib.check(status, name)

@@ -104,13 +104,12 @@ def grouped_gemm_forward_4bit(
     y = torch.empty((M, N), device=x.device, dtype=dtype)
     lib = _lib.load()
     m_sizes = _lib.as_index_tensor(m_sizes)
-    ws_bytes = lib.moe_grouped_gemm_workspace_bytes(0, M, N, K, E)
-    ws = torch.empty(ws_bytes, device=x.device, dtype=torch.uint8) if ws_bytes else None
+    ws_ptr, ws_bytes = _lib.workspace(x.device, lib.moe_grouped_gemm_workspace_bytes(0, M, N, K, E))
     with torch.cuda.device(x.device):
         status = lib.moe_grouped_gemm_fwd_nf4(
             _lib.ptr(x), _lib.ptr(w_quant), _lib.ptr(w_code), _lib.ptr(w_absmax), blocksize,
             _lib.ptr(m_sizes), _lib.int_code(m_sizes.dtype), _lib.ptr(y), M, N, K, E,
-            _lib.float_code(x.dtype), _lib.float_code(dtype), _lib.ptr(ws), ws_bytes, _lib.stream_ptr(x.device),
+            _lib.float_code(x.dtype), _lib.float_code(dtype), ws_ptr, ws_bytes, _lib.stream_ptr(x.device),
         )
     _lib.check(status, "moe_grouped_gemm_fwd_nf4")
     return y
@@ -145,13 +144,12 @@ def grouped_gemm_forward_transposed_4bit(
     y = torch.empty((M, N), device=x.device, dtype=dtype)
     lib = _lib.load()
     m_sizes = _lib.as_index_tensor(m_sizes)
-    ws_bytes = lib.moe_grouped_gemm_workspace_bytes(1, M, N, K, E)
-    ws = torch.empty(ws_bytes, device=x.device, dtype=torch.uint8) if ws_bytes else None
+    ws_ptr, ws_bytes = _lib.workspace(x.device, lib.moe_grouped_gemm_workspace_bytes(1, M, N, K, E))
     with torch.cuda.device(x.device):
         status = lib.moe_grouped_gemm_dx_nf4(
             _lib.ptr(x), _lib.ptr(w_quant), _lib.ptr(w_code), _lib.ptr(w_absmax), blocksize,
             _lib.ptr(m_sizes), _lib.int_code(m_sizes.dtype), _lib.ptr(y), M, N, K, E,
-            _lib.float_code(x.dtype), _lib.float_code(dtype), _lib.ptr(ws), ws_bytes, _lib.stream_ptr(x.device),
+            _lib.float_code(x.dtype), _lib.float_code(dtype), ws_ptr, ws_bytes, _lib.stream_ptr(x.device),
         )
     if status == _lib.ERR_UNSUPPORTED:
         from ..quantize.nf4 import dequantize_4bit

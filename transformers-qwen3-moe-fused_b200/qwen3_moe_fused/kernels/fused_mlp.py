@@ -24,9 +24,7 @@ def gate_up_silu_forward(x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torc
     lib = _lib.load()
     if x.dtype in (torch.bfloat16, torch.float16) and M > 0:
         h = torch.empty((M, I), device=x.device, dtype=x.dtype)
-        ws_bytes = lib.moe_grouped_gemm_workspace_bytes(0, M, I, K, E)
-        ws = torch.empty(ws_bytes + 128, device=x.device, dtype=torch.uint8)
-        ws_ptr = (ws.data_ptr() + 127) & ~127
+        ws_ptr, ws_bytes = _lib.workspace(x.device, lib.moe_grouped_gemm_workspace_bytes(0, M, I, K, E))
         with torch.cuda.device(x.device):
             status = lib.moe_gate_up_silu_fwd(
                 _lib.ptr(x), _lib.ptr(gate_proj), _lib.ptr(up_proj), _lib.ptr(m_sizes), _lib.int_code(m_sizes.dtype),

@@ -78,3 +78,36 @@ def moe_block_forward(hidden_states: torch.Tensor, gate_weight: torch.Tensor, ga
     y = moe_fused_linear(h, down_proj, m_sizes)
     out = combine(y, sort_idx, inv_sort_idx, routing_weights)
     return out.view(B, S, H), router_logits
+
+
+def fused_sparse_moe_block_forward(self, hidden_states: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """`forward` for the reference's `Qwen3MoeFusedSparseMoeBlock`
+    (qwen3_moe_fused/modular_qwen3_moe_fused.py:79-118): same inputs, outputs and gradients, computed by
+    `moe_block_forward` (router epilogue, expand + gather and un-permute + weighted sum as one kernel
+    each; under `torch.no_grad()` gate, up and SiLU-mul as one tensor-core kernel).  `self` needs the
+    attributes of that class: `gate` (a bias-free Linear), `gate_proj` / `up_proj` / `down_proj` (plain
+    `MoeFusedLinear` modules), `num_selected`, `norm_topk_prob`."""
+    for name in ("gate_proj", "up_proj", "down_proj"):
+        if not _is_plain_fused_linear(getattr(self, name)):
+            raise NotImplementedError(f"{name} is a {type(getattr(self, name)).__name__}: this forward takes plain MoeFusedLinear "
+                                      "projections (LoRA or 4-bit projections go through fast_lora)")
+    return moe_block_forward(hidden_states, self.gate.weight, self.gate_proj.weight, self.up_proj.weight,
+                             self.down_proj.weight, self.num_selected, self.norm_topk_prob)
+
+
+def _is_plain_fused_linear(module) -> bool:
+    """True for a module that is exactly a weight-only fused linear: this package's `MoeFusedLinear` or the
+    class of that name in the reference's modular file (not a subclass that changes `forward`)."""
+    cls = type(module)
+    return cls.__name__ == "MoeFusedLinear" and isinstance(getattr(module, "weight", None), torch.Tensor) and \
+        not hasattr(module, "base_layer") and not hasattr(module, "quant_state")
+
+
+def patch_Qwen3MoeFusedSparseMoeBlock_forward(block_class=None) -> None:
+    """Installs `fused_sparse_moe_block_forward` on the sparse MoE block class, the way the reference's
+    own patch function does for its fused-LoRA forward (qwen3_moe_fused/fast_lora.py:84-85).  Without an
+    argument the class is `Qwen3MoeFusedSparseMoeBlock` of the reference's modular file, which is
+    importable through this package when `QWEN3_MOE_FUSED_REFERENCE` points at a checkout."""
+    if block_class is None:
+        from .modular_qwen3_moe_fused import Qwen3MoeFusedSparseMoeBlock as block_class  # file of the reference checkout
+    block_class.forward = fused_sparse_moe_block_forward

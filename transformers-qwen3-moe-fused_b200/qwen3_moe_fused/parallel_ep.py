@@ -308,9 +308,7 @@ def scattered_grouped_gemm(x: torch.Tensor, weight: torch.Tensor, group_sizes: t
     if weight_index is not None:
         assert weight_index.dtype == torch.int32 and weight_index.is_contiguous() and weight_index.numel() == G
     lib = _lib.load()
-    ws_bytes = lib.moe_grouped_gemm_workspace_bytes(0, M, N, K, G)
-    ws = torch.empty(ws_bytes + 128, dtype=torch.uint8, device=x.device)
-    ws_ptr = (ws.data_ptr() + 127) & ~127
+    ws_ptr, ws_bytes = _lib.workspace(x.device, lib.moe_grouped_gemm_workspace_bytes(0, M, N, K, G))
     name = "moe_grouped_gemm_dx_scattered" if transposed else "moe_grouped_gemm_fwd_scattered"
     dt = _lib.float_code(x.dtype)
     _lib.check(getattr(lib, name)(
