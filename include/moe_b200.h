@@ -134,6 +134,23 @@ int moe_gate_up_silu_fwd(const void* x, const void* w_gate, const void* w_up, co
                          int m_sizes_dtype, void* h, int64_t M, int I, int K, int E, int dtype,
                          void* ws, size_t ws_bytes, void* stream);
 
+/* moe_gate_up_silu_fwd and moe_grouped_gemm_fwd with the token rows gathered inside the kernel's
+ * token load: sorted row r (r < M, grouped by m_sizes as usual) is row row_index[r] / index_div of x,
+ * which has x_rows rows (row_index: DEVICE int32 array of M entries).  Passing the sort's gather index
+ * and k = index_div feeds the expert GEMMs straight from the (T, hidden) token tensor, without
+ * materialising the expanded, sorted copy (qwen3_moe_fused/modular_qwen3_moe_fused.py:95-103 builds that
+ * copy with expand + reshape + index).  The result is bit-identical to gathering first.  Rows are fetched
+ * with TMA tile::gather4 loads.  Tensor-core CTA-pair kernels only: bf16/fp16, N (I) >= 192 for the plain
+ * forward, workspace required; MOE_ERR_UNSUPPORTED / MOE_ERR_WORKSPACE otherwise. */
+int moe_gate_up_silu_fwd_gather(const void* x, int64_t x_rows, const int32_t* row_index, int index_div,
+                                const void* w_gate, const void* w_up, const void* m_sizes,
+                                int m_sizes_dtype, void* h, int64_t M, int I, int K, int E, int dtype,
+                                void* ws, size_t ws_bytes, void* stream);
+int moe_grouped_gemm_fwd_gather(const void* x, int64_t x_rows, const int32_t* row_index, int index_div,
+                                const void* w, const void* m_sizes, int m_sizes_dtype, void* y,
+                                int64_t M, int N, int K, int E, int dtype_in, int dtype_out,
+                                void* ws, size_t ws_bytes, void* stream);
+
 /* Forward with an NF4 weight decoded inside the kernel:
  *   w[e,n,k] = code[nibble(e,n,k)] * absmax[(e*N*K + n*K + k) / blocksize], rounded to
  *   dtype_in, then as moe_grouped_gemm_fwd.  packed: E*N*K/2 bytes, element 2j in the

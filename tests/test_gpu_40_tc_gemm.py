@@ -209,3 +209,45 @@ def test_gate_up_silu_fused_equals_three_kernels(cuda, dtype, M, K, I, E, empty)
         _lib.set_gemm_path(prev)
     assert _lib.read_error_flag() == 0
     assert torch.equal(h, ref)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("T,k,K,I,E,empty", [
+    (1000, 4, 256, 384, 8, 0.2),
+    (4096, 8, 2048, 768, 64, 0.0),   # about 512 rows per expert: tiles with tails
+    (300, 2, 72, 192, 5, 0.0),       # K % 64 != 0
+    (64, 8, 128, 256, 16, 0.5),      # groups of a few rows
+])
+def test_token_rows_gathered_inside_the_kernel(cuda, dtype, T, k, K, I, E, empty):
+    """Forward and fused gate/up forward fed from the (T, K) token tensor through the sort's gather index
+    (TMA gather4 in the token load): bit-identical to gathering the rows first."""
+    from qwen3_moe_fused import _lib
+    from qwen3_moe_fused.grouped_gemm.forward import grouped_gemm_forward, grouped_gemm_forward_gather
+    from qwen3_moe_fused.kernels.fused_mlp import gate_up_silu_forward
+    from qwen3_moe_fused.kernels.indexing import get_expert_counts_and_idx
+    from qwen3_moe_fused.kernels.routing import _gather_rows
+
+    rng = np.random.default_rng(T + K + I)
+    p = rng.random(E) + 0.05
+    p[rng.random(E) < empty] = 0.0
+    p[0] += 0.01
+    sel = torch.from_numpy(rng.choice(E, size=T * k, p=p / p.sum())).to(cuda)
+    m_sizes, sort_idx, _ = get_expert_counts_and_idx(sel, E)
+    tokens = to_dev(rounded(rng.standard_normal((T, K)), dtype), dtype, cuda)
+    wg = to_dev(rounded(rng.standard_normal((E, I, K)) / np.sqrt(K) * 2, dtype), dtype, cuda)
+    wu = to_dev(rounded(rng.standard_normal((E, I, K)) / np.sqrt(K), dtype), dtype, cuda)
+    xs = _gather_rows(tokens, sort_idx, k)
+    prev = _lib.set_gemm_path(_lib.PATH_AUTO)
+    try:
+        h_ref = gate_up_silu_forward(xs, wg, wu, m_sizes)
+        h = gate_up_silu_forward(tokens, wg, wu, m_sizes, row_index=sort_idx, index_div=k)
+        y_ref = grouped_gemm_forward(xs, wg, m_sizes)
+        y = grouped_gemm_forward_gather(tokens, sort_idx, k, wg, m_sizes)
+        # index_div = 1: an index of rows rather than of (token, slot) pairs
+        y1 = grouped_gemm_forward_gather(tokens, (sort_idx // k).to(torch.int32).contiguous(), 1, wg, m_sizes)
+        torch.cuda.synchronize()
+    finally:
+        _lib.set_gemm_path(prev)
+    assert _lib.read_error_flag() == 0
+    assert torch.equal(h, h_ref)
+    assert torch.equal(y, y_ref) and torch.equal(y1, y_ref)

@@ -25,7 +25,11 @@ int tc_grouped_gemm_scattered(int which, const void* a, const void* b, const voi
                               int64_t M, int N, int K, int G, int dtype_in, int dtype_out, void* ws, size_t ws_bytes,
                               cudaStream_t stream);
 int tc_gate_up_silu(const void* x, const void* w_gate, const void* w_up, const void* m_sizes, int ms64, void* h,
-                    int64_t M, int I, int K, int E, int dtype, void* ws, size_t ws_bytes, cudaStream_t stream);
+                    int64_t M, int I, int K, int E, int dtype, void* ws, size_t ws_bytes, cudaStream_t stream,
+                    const int* row_index, int index_div, int64_t x_rows);
+int tc_grouped_gemm_gather(const void* x, int64_t x_rows, const int* row_index, int index_div, const void* w,
+                           const void* m_sizes, int ms64, void* y, int64_t M, int N, int K, int E, int dtype_in,
+                           int dtype_out, void* ws, size_t ws_bytes, cudaStream_t stream);
 int tc_read_error(int* flag_out, bool clear);
 size_t tc_workspace_bytes(int E);
 int tc_read_late_values(int* out);
@@ -181,7 +185,38 @@ MOE_API int moe_gate_up_silu_fwd(const void* x, const void* w_gate, const void* 
   if (K == 0 || dtype == MOE_F32 || !tc_eligible(0, x, w_gate, h, M, I, K, E, dtype, dtype) ||
       ((uintptr_t)w_up & 15) || ((uintptr_t)h & 15))
     return MOE_ERR_UNSUPPORTED;
-  return tc_gate_up_silu(x, w_gate, w_up, m_sizes, msd == MOE_I64, h, M, I, K, E, dtype, ws, ws_bytes, (cudaStream_t)stream);
+  return tc_gate_up_silu(x, w_gate, w_up, m_sizes, msd == MOE_I64, h, M, I, K, E, dtype, ws, ws_bytes, (cudaStream_t)stream,
+                         nullptr, 1, 0);
+}
+
+MOE_API int moe_gate_up_silu_fwd_gather(const void* x, int64_t x_rows, const int32_t* row_index, int index_div,
+                                        const void* w_gate, const void* w_up, const void* m_sizes, int msd, void* h,
+                                        int64_t M, int I, int K, int E, int dtype, void* ws, size_t ws_bytes, void* stream) {
+  int st = check_common(x, w_gate, m_sizes, msd, h, M, I, K, E, dtype, dtype);
+  if (st != MOE_OK) return st;
+  if (x_rows < 0 || index_div <= 0) return MOE_ERR_SHAPE;
+  if (M > 0 && I > 0 && K > 0 && (!w_up || !row_index)) return MOE_ERR_NULL;
+  if (M == 0 || I == 0) return MOE_OK;
+  if (!device_is_sm100()) return MOE_ERR_DEVICE;
+  if (K == 0 || x_rows == 0 || dtype == MOE_F32 || !tc_eligible(0, x, w_gate, h, M, I, K, E, dtype, dtype) ||
+      ((uintptr_t)w_up & 15) || ((uintptr_t)h & 15))
+    return MOE_ERR_UNSUPPORTED;
+  return tc_gate_up_silu(x, w_gate, w_up, m_sizes, msd == MOE_I64, h, M, I, K, E, dtype, ws, ws_bytes, (cudaStream_t)stream,
+                         row_index, index_div, x_rows);
+}
+
+MOE_API int moe_grouped_gemm_fwd_gather(const void* x, int64_t x_rows, const int32_t* row_index, int index_div, const void* w,
+                                        const void* m_sizes, int msd, void* y, int64_t M, int N, int K, int E, int dtype_in,
+                                        int dtype_out, void* ws, size_t ws_bytes, void* stream) {
+  int st = check_common(x, w, m_sizes, msd, y, M, N, K, E, dtype_in, dtype_out);
+  if (st != MOE_OK) return st;
+  if (x_rows < 0 || index_div <= 0) return MOE_ERR_SHAPE;
+  if (M > 0 && N > 0 && K > 0 && !row_index) return MOE_ERR_NULL;
+  if (M == 0 || N == 0) return MOE_OK;
+  if (!device_is_sm100()) return MOE_ERR_DEVICE;
+  if (K == 0 || x_rows == 0 || !tc_eligible(0, x, w, y, M, N, K, E, dtype_in, dtype_out)) return MOE_ERR_UNSUPPORTED;
+  return tc_grouped_gemm_gather(x, x_rows, row_index, index_div, w, m_sizes, msd == MOE_I64, y, M, N, K, E, dtype_in,
+                                dtype_out, ws, ws_bytes, (cudaStream_t)stream);
 }
 
 static int run_scattered(int which, const void* x, const void* w, const void* group_sizes, int msd,

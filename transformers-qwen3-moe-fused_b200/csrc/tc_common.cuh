@@ -232,6 +232,17 @@ __device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorM
       ::"r"(smem_u32(smem_dst)), "l"((uint64_t)map), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// Four rows of a 2-D tensor, given by their row indices, into four consecutive 128-byte rows of shared
+// memory (the tensor map's box is {64 elements, 1 row}); completion as for the loads above.  Rows whose
+// index lies outside the tensor are filled with zeros.  Not multicast.
+__device__ __forceinline__ void tma_gather4_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x,
+                                                 int r0, int r1, int r2, int r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.cta_group::2"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"((uint64_t)map), "r"(bar_cluster_addr), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+      : "memory");
+}
 // TMA store of a shared-memory tile (bulk async-group completion)
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int x, int y, int z) {
   asm volatile(

@@ -11,8 +11,8 @@
 // buffered in TMEM so the epilogue of tile i overlaps the main loop of tile i+1.
 // No tile ever crosses an expert boundary on the store side: an M tile starts at a group's
 // first row and rows past the group's end are computed but not stored.
-#include <atomic>
 #include <cstdio>
+#include <mutex>
 #include <cstdlib>
 #include <cstring>
 #include <type_traits>
@@ -45,6 +45,9 @@ struct GemmParams {
   int* tile_counter = nullptr;  // work items are drawn from this counter (zeroed by build_group_maps_kernel); null: round-robin
   int stages = 0;               // CTA-pair forward / dX: depth of the operand ring
   int small_maps = 0;           // CTA-pair forward / dX: per-expert maps with the small token box exist (slot GM_IN_SMALL)
+  const int* row_index = nullptr;  // gathered forms: sorted row r reads row row_index[r] / index_div of the token tensor
+  int index_div = 1;
+  int64_t x_rows = 0;           // gathered forms: rows of the token tensor
 };
 
 struct Control {
@@ -608,21 +611,40 @@ static constexpr int smem_bytes_for(int E, int tables) {
 
 // Per-kernel, per-device memo of launch set-up that does not change between calls: a call of a thin
 // (LoRA-sized) GEMM would otherwise spend more host time on attribute and occupancy queries than the
-// kernel runs.  Each template instantiation of the two helpers below has its own table.
-constexpr int MEMO_DEVICES = 64;
-static int current_device() {
+// kernel runs.  Entries are keyed by the kernel's address (template instantiations share their
+// function-pointer TYPE, so the key cannot be the type).
+struct LaunchMemo {
+  const void* kernel;
+  int device;
+  int smem_granted;     // largest dynamic shared-memory limit set so far
+  int pairs_smem;       // shared-memory size of the memoised occupancy answer (0: none)
+  int pairs;
+};
+constexpr int MEMO_SLOTS = 96;
+static LaunchMemo g_memo[MEMO_SLOTS];
+static int g_memo_used = 0;
+static std::mutex g_memo_lock;
+
+// Entry of (kernel, current device), created on first use; nullptr when the table is full (callers then
+// simply repeat the query).  Call with g_memo_lock held.
+static LaunchMemo* memo_entry(const void* kernel) {
   int dev = 0;
-  return (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < MEMO_DEVICES) ? dev : -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  for (int i = 0; i < g_memo_used; ++i)
+    if (g_memo[i].kernel == kernel && g_memo[i].device == dev) return &g_memo[i];
+  if (g_memo_used == MEMO_SLOTS) return nullptr;
+  g_memo[g_memo_used] = LaunchMemo{kernel, dev, 0, 0, 0};
+  return &g_memo[g_memo_used++];
 }
 
-// Raises the kernel's dynamic shared-memory limit to at least `bytes` (once per device and size).
+// Raises the kernel's dynamic shared-memory limit to at least `bytes` (once per kernel, device and size).
 template <typename K>
 static int set_smem(K kernel, int bytes) {
-  static std::atomic<int> granted[MEMO_DEVICES];
-  const int dev = current_device();
-  if (dev >= 0 && granted[dev].load(std::memory_order_acquire) >= bytes) return MOE_OK;
+  std::lock_guard<std::mutex> guard(g_memo_lock);
+  LaunchMemo* m = memo_entry(reinterpret_cast<const void*>(kernel));
+  if (m != nullptr && m->smem_granted >= bytes) return MOE_OK;
   const int st = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  if (st == MOE_OK && dev >= 0) granted[dev].store(bytes, std::memory_order_release);
+  if (st == MOE_OK && m != nullptr) m->smem_granted = bytes;
   return st;
 }
 
@@ -657,12 +679,10 @@ static void bind_context_once() {
 // Number of CTA pairs that can be resident at once (persistent grid = 2 x this).
 template <typename Kern>
 static int resident_pairs(Kern kernel, int smem_bytes, int threads = 192) {
-  // memo: (shared-memory bytes << 8 | result) of the last query on each device
-  static std::atomic<long long> memo[tc::MEMO_DEVICES];
-  const int dev = tc::current_device();
-  if (dev >= 0) {
-    const long long m = memo[dev].load(std::memory_order_acquire);
-    if (m != 0 && (m >> 8) == (long long)smem_bytes) return (int)(m & 0xff);
+  {
+    std::lock_guard<std::mutex> guard(tc::g_memo_lock);
+    tc::LaunchMemo* m = tc::memo_entry(reinterpret_cast<const void*>(kernel));
+    if (m != nullptr && m->pairs_smem == smem_bytes && m->pairs > 0) return m->pairs;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * sm_count());
@@ -680,7 +700,11 @@ static int resident_pairs(Kern kernel, int smem_bytes, int threads = 192) {
   }
   const int cap = sm_count() / 2;
   n = n < cap ? n : cap;
-  if (dev >= 0 && n < 256) memo[dev].store(((long long)smem_bytes << 8) | n, std::memory_order_release);
+  {
+    std::lock_guard<std::mutex> guard(tc::g_memo_lock);
+    tc::LaunchMemo* m = tc::memo_entry(reinterpret_cast<const void*>(kernel));
+    if (m != nullptr) { m->pairs_smem = smem_bytes; m->pairs = n; }
+  }
   return n;
 }
 
@@ -713,13 +737,16 @@ static int pair_stages(int E) {
 // Launches build_group_maps_kernel for the forward / dX / gate-up kernels: per-expert copies of the
 // token maps (128-row and small box) and, for 16-bit outputs, of the output map.
 static int build_pair_maps(tc::GemmParams& p, const CUtensorMap& mx, const void* a, void* out, int dtype_in, int dtype_out,
-                           void* ws, cudaStream_t stream, const uint64_t* out_ptrs) {
+                           void* ws, cudaStream_t stream, const uint64_t* out_ptrs, bool gather = false) {
   using namespace tc;
   GroupMapTemplates tm;
   int st;
-  tm.mask = (1 << GM_IN) | (1 << GM_IN_SMALL);
-  tm.t[GM_IN] = mx;
-  if ((st = make_map(&tm.t[GM_IN_SMALL], dtype_in, a, (uint64_t)p.K, (uint64_t)p.M, 0, PAIR_SMALL_BOX)) != MOE_OK) return st;
+  tm.mask = 0;
+  if (!gather) {  // (gathered token rows are addressed by index: no per-expert token maps)
+    tm.mask = (1 << GM_IN) | (1 << GM_IN_SMALL);
+    tm.t[GM_IN] = mx;
+    if ((st = make_map(&tm.t[GM_IN_SMALL], dtype_in, a, (uint64_t)p.K, (uint64_t)p.M, 0, PAIR_SMALL_BOX)) != MOE_OK) return st;
+  }
   if (dtype_out != MOE_F32) {
     tm.mask |= 1 << GM_OUT;
     if ((st = make_map(&tm.t[GM_OUT], dtype_out, out, (uint64_t)p.N, (uint64_t)p.M, 0, 32)) != MOE_OK) return st;
@@ -730,7 +757,7 @@ static int build_pair_maps(tc::GemmParams& p, const CUtensorMap& mx, const void*
   if ((st = launch_status()) != MOE_OK) return st;
   p.group_maps = reinterpret_cast<const CUtensorMap*>(ws);
   p.tile_counter = ws_counter(ws, p.E);
-  p.small_maps = 1;
+  p.small_maps = gather ? 0 : 1;
   return MOE_OK;
 }
 
@@ -740,11 +767,15 @@ static int build_pair_maps(tc::GemmParams& p, const CUtensorMap& mx, const void*
 static int pair_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes, int ms64, void* out,
                              int64_t M, int N, int K, int E, int dtype_in, int dtype_out, void* ws, size_t ws_bytes,
                              cudaStream_t stream, const int* weight_index = nullptr, int n_weights = 0,
-                             const uint64_t* out_ptrs = nullptr) {
+                             const uint64_t* out_ptrs = nullptr, const int* row_index = nullptr, int index_div = 1,
+                             int64_t x_rows = 0) {
   using namespace tc;
   if (which != 0 && which != 1) return MOE_ERR_UNSUPPORTED;
+  const bool gather = row_index != nullptr;
+  if (gather && (which != 0 || index_div <= 0 || x_rows <= 0 || x_rows > 0x7fffffffLL)) return MOE_ERR_UNSUPPORTED;
   if (n_weights <= 0) n_weights = E;
   GemmParams p;
+  p.row_index = row_index; p.index_div = index_div; p.x_rows = x_rows;
   p.weight_index = weight_index;
   p.a = a; p.b = b;
   p.m_sizes = m_sizes; p.out = out; p.M = M; p.N = N; p.K = K; p.E = E; p.ms64 = ms64; p.dtype_out = dtype_out;
@@ -758,19 +789,28 @@ static int pair_grouped_gemm(int which, const void* a, const void* b, const void
   if (which == 0) st = make_map(&mw, dtype_in, b, (uint64_t)K, (uint64_t)N, (uint64_t)n_weights, 128);
   else st = make_map(&mw, dtype_in, b, (uint64_t)N, (uint64_t)K, (uint64_t)n_weights, BK);
   if (st != MOE_OK) return st;
-  if ((st = make_map(&mx, dtype_in, a, (uint64_t)K, (uint64_t)M, 0, 128)) != MOE_OK) return st;
+  // token map: 128-row boxes over the M sorted rows, or one-row boxes (for gather4) over the x_rows token rows
+  if (gather) st = make_map(&mx, dtype_in, a, (uint64_t)K, (uint64_t)x_rows, 0, 1);
+  else st = make_map(&mx, dtype_in, a, (uint64_t)K, (uint64_t)M, 0, 128);
+  if (st != MOE_OK) return st;
   p.idesc = make_idesc(fmt, which == 1, 0, 256, 0);  // N field is filled per tile
   // Per-expert copies of the token and output maps (row extent = the group's last row): partial
   // tiles then load no rows of the next expert, and 16-bit outputs can leave through TMA stores.
   if (ws_usable(ws, ws_bytes, E) && (((uintptr_t)out & 15) == 0 || dtype_out == MOE_F32)) {
-    if ((st = build_pair_maps(p, mx, a, out, dtype_in, dtype_out, ws, stream, out_ptrs)) != MOE_OK) return st;
+    if ((st = build_pair_maps(p, mx, a, out, dtype_in, dtype_out, ws, stream, out_ptrs, gather)) != MOE_OK) return st;
   }
+  if (gather && p.group_maps == nullptr) return MOE_ERR_WORKSPACE;
   // scattered outputs exist only as per-group output maps
   if (out_ptrs != nullptr && (p.group_maps == nullptr || dtype_out == MOE_F32)) return MOE_ERR_UNSUPPORTED;
   p.stages = pair_stages(E);
   if (p.stages == 0) return MOE_ERR_UNSUPPORTED;
   const int bytes = pair_smem_bytes(p.stages, E);
-  if (which == 0) {
+  if (gather) {
+    auto kern = pair_fwd_kernel<false, false, true>;
+    if ((st = set_smem(kern, bytes)) != MOE_OK) return st;
+    const int grid = 2 * resident_pairs(kern, bytes);
+    kern<<<grid, PAIR_THREADS, bytes, stream>>>(mw, mx, p, mw);
+  } else if (which == 0) {
     if ((st = set_smem(pair_fwd_kernel<false>, bytes)) != MOE_OK) return st;
     const int grid = 2 * resident_pairs(pair_fwd_kernel<false>, bytes);
     pair_fwd_kernel<false><<<grid, PAIR_THREADS, bytes, stream>>>(mw, mx, p, mw);
@@ -928,7 +968,8 @@ int tc_grouped_gemm(int which, const void* a, const void* b, const void* m_sizes
 
 // h = silu(x w_gate^T) * (x w_up^T) per expert in one launch (pair_fwd_kernel<false, true>).
 int tc_gate_up_silu(const void* x, const void* w_gate, const void* w_up, const void* m_sizes, int ms64, void* h,
-                    int64_t M, int I, int K, int E, int dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
+                    int64_t M, int I, int K, int E, int dtype, void* ws, size_t ws_bytes, cudaStream_t stream,
+                    const int* row_index, int index_div, int64_t x_rows) {
   using namespace tc;
   bind_context_once();
   if (!ws_usable(ws, ws_bytes, E)) return MOE_ERR_WORKSPACE;
@@ -941,16 +982,37 @@ int tc_gate_up_silu(const void* x, const void* w_gate, const void* w_up, const v
   int st;
   if ((st = make_map(&mg, dtype, w_gate, (uint64_t)K, (uint64_t)I, (uint64_t)E, 16)) != MOE_OK) return st;
   if ((st = make_map(&mu, dtype, w_up, (uint64_t)K, (uint64_t)I, (uint64_t)E, 16)) != MOE_OK) return st;
-  if ((st = make_map(&mx, dtype, x, (uint64_t)K, (uint64_t)M, 0, 128)) != MOE_OK) return st;
-  if ((st = build_pair_maps(p, mx, x, h, dtype, dtype, ws, stream, nullptr)) != MOE_OK) return st;
+  const bool gather = row_index != nullptr;
+  if (gather && (index_div <= 0 || x_rows <= 0 || x_rows > 0x7fffffffLL)) return MOE_ERR_SHAPE;
+  p.row_index = row_index; p.index_div = index_div; p.x_rows = x_rows;
+  if (gather) st = make_map(&mx, dtype, x, (uint64_t)K, (uint64_t)x_rows, 0, 1);
+  else st = make_map(&mx, dtype, x, (uint64_t)K, (uint64_t)M, 0, 128);
+  if (st != MOE_OK) return st;
+  if ((st = build_pair_maps(p, mx, x, h, dtype, dtype, ws, stream, nullptr, gather)) != MOE_OK) return st;
   p.stages = pair_stages(E);
   if (p.stages == 0) return MOE_ERR_UNSUPPORTED;
   const int bytes = pair_smem_bytes(p.stages, E);
+  if (gather) {
+    auto kern = pair_fwd_kernel<false, true, true>;
+    if ((st = set_smem(kern, bytes)) != MOE_OK) return st;
+    kern<<<2 * resident_pairs(kern, bytes), PAIR_THREADS, bytes, stream>>>(mg, mx, p, mu);
+    return launch_status();
+  }
   auto kern = pair_fwd_kernel<false, true>;
   if ((st = set_smem(kern, bytes)) != MOE_OK) return st;
   const int grid = 2 * resident_pairs(kern, bytes);
   kern<<<grid, PAIR_THREADS, bytes, stream>>>(mg, mx, p, mu);
   return launch_status();
+}
+
+// Forward whose sorted row r is row row_index[r] / index_div of x (x_rows rows): CTA-pair kernel only.
+int tc_grouped_gemm_gather(const void* x, int64_t x_rows, const int* row_index, int index_div, const void* w,
+                           const void* m_sizes, int ms64, void* y, int64_t M, int N, int K, int E, int dtype_in,
+                           int dtype_out, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  bind_context_once();
+  if (N < 192) return MOE_ERR_UNSUPPORTED;
+  return pair_grouped_gemm(0, x, w, m_sizes, ms64, y, M, N, K, E, dtype_in, dtype_out, ws, ws_bytes, stream, nullptr, 0,
+                           nullptr, row_index, index_div, x_rows);
 }
 
 // Scattered forward (which = 0) / dX (which = 1) on the CTA-pair kernels: see pair_grouped_gemm.

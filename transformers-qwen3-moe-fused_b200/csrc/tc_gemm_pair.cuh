@@ -294,11 +294,12 @@ __device__ __forceinline__ uint32_t pair_regions(uint32_t parity, int n_main, in
 // [gate f..f+15][up f..f+15]... so that a warp's quarter of TMEM holds gate and up of the same 16
 // features; the epilogue writes h = silu(gate) * up (p.N = I columns) and neither projection.
 // ---------------------------------------------------------------------------------------
-template <bool W_MN, bool GATE_UP = false>
+template <bool W_MN, bool GATE_UP = false, bool GATHER = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                 const GemmParams p, const __grid_constant__ CUtensorMap tmap_w2) {
   static_assert(!(W_MN && GATE_UP), "the fused gate/up form reads K-major weights");
+  static_assert(!(W_MN && GATHER), "rows are gathered in the forward forms only");
   constexpr int TILE_N = GATE_UP ? 128 : 256;  // output columns (features) per pair
   constexpr int STAGE_BYTES = PAIR_STAGE_BYTES;
   constexpr uint32_t TMEM_COLS = 512;
@@ -318,7 +319,7 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   const bool leader = rank == 0;
   // tails and small boxes need the per-expert small-box maps
   const bool small_maps = p.group_maps != nullptr && p.small_maps;
-  const int tail = small_maps ? PAIR_TAIL : 0;
+  const int tail = (small_maps || GATHER) ? PAIR_TAIL : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
@@ -376,7 +377,64 @@ pair_fwd_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   };
   auto tail_boxes = [&](int n_tail) { return ((n_tail >> 1) + PAIR_SMALL_BOX - 1) / PAIR_SMALL_BOX; };
 
-  if (warp == 0) {
+  if (warp == 0 && GATHER) {
+    // ---------------- TMA producer, token rows gathered through an index (both CTAs) ----------------
+    // The tile's token rows are x[row_index[r] / index_div] for its sorted rows r: every lane owns four of
+    // this CTA's (up to 128) main rows and fetches them per k-block with one tile::gather4 load (four rows
+    // of 128 bytes, swizzled like a four-row box); lanes 0.. also own the tail rows.  Rows past the expert's
+    // end get the row index x_rows, which lies outside the tensor: TMA fills them with zeros.
+    TileFeed<2> feed(&ctl->sched, abort_flag);
+    const uint32_t full_leader0 = map_to_cta(smem_u32(&ctl->full[0]), 0);
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    while (ok) {
+      const int tile = feed.take_warp(lane);
+      if (tile < 0) break;
+      const PairTile t = decode(tile);
+      const int we = p.weight_index ? __ldg(p.weight_index + t.e) : t.e;
+      const int w_row = t.n0 + (int)rank * 128;
+      const int rows_main = t.n_main >> 1, rows_tail = t.n_tail >> 1;  // this CTA's rows: multiples of 8
+      const int tok = t.t0 + (int)rank * rows_main;
+      const int tok_tail = t.t0 + PAIR_TOKENS + (int)rank * rows_tail;
+      auto source_row = [&](int r) { return r < t.t_end ? __ldg(p.row_index + r) / p.index_div : (int)p.x_rows; };
+      int mr[4], tr[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        mr[j] = source_row(tok + 4 * lane + j);
+        tr[j] = source_row(tok_tail + 4 * lane + j);
+      }
+      const bool has_main = 4 * lane < rows_main, has_tail = 4 * lane < rows_tail;
+      const uint32_t b_bytes = (uint32_t)(rows_main + rows_tail) * (BK * 2);
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        uint8_t* sa = smem + s * STAGE_BYTES;
+        uint8_t* sb = sa + PAIR_HALF_BYTES;
+        const uint32_t bar = full_leader0 + s * 8;
+        int go = 1;
+        if (lane == 0) {
+          go = mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, PW_EMPTY) ? 1 : 0;
+          if (go) {
+            if (leader) mbar_expect_tx(&ctl->full[s], 2 * (PAIR_HALF_BYTES + b_bytes));  // both CTAs' bytes
+            if constexpr (GATE_UP) {
+              const int feat = t.n0 + (int)rank * 64;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                tma_load_3d_pair(sa + (2 * q) * 2048, &tmap_w, bar, kb * BK, feat + 16 * q, we);
+                tma_load_3d_pair(sa + (2 * q + 1) * 2048, &tmap_w2, bar, kb * BK, feat + 16 * q, we);
+              }
+            } else {
+              tma_load_3d_pair(sa, &tmap_w, bar, kb * BK, w_row, we);
+            }
+          }
+        }
+        go = __shfl_sync(0xffffffffu, go, 0);  // the stage is free (and its byte count announced) for every lane
+        if (!go) { ok = false; break; }
+        if (has_main) tma_gather4_pair(sb + lane * (4 * BK * 2), &tmap_x, bar, kb * BK, mr[0], mr[1], mr[2], mr[3]);
+        if (has_tail) tma_gather4_pair(sb + PAIR_HALF_BYTES + lane * (4 * BK * 2), &tmap_x, bar, kb * BK, tr[0], tr[1], tr[2], tr[3]);
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
     if (elect_one()) {
       TileFeed<2> feed(&ctl->sched, abort_flag);

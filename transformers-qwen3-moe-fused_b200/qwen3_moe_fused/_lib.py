@@ -38,6 +38,8 @@ SIGNATURES = {
     "moe_grouped_gemm_dx": (_I, [_P, _P, _P, _I, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_grouped_gemm_dw": (_I, [_P, _P, _P, _I, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_gate_up_silu_fwd": (_I, [_P, _P, _P, _P, _I, _P, _L, _I, _I, _I, _I, _P, _Z, _P]),
+    "moe_gate_up_silu_fwd_gather": (_I, [_P, _L, _P, _I, _P, _P, _P, _I, _P, _L, _I, _I, _I, _I, _P, _Z, _P]),
+    "moe_grouped_gemm_fwd_gather": (_I, [_P, _L, _P, _I, _P, _P, _I, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_grouped_gemm_fwd_nf4": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_grouped_gemm_dx_nf4": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "moe_nf4_dequant": (_I, [_P, _P, _P, _I, _P, _L, _I, _P]),
