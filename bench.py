@@ -306,6 +306,9 @@ def run_kernel_suite(args):
         if flops is not None:
             line.update(flops=flops, tflops=flops / ms / 1e9)
         line.update(extra)
+        flag = _lib.read_error_flag()
+        if flag:
+            line["kernel_wait_error"] = {"code": flag >> 16, "cta": flag & 0xffff}
         print(json.dumps(line), flush=True)
 
     # ---- SiLU-mul at the down-projection input size ----

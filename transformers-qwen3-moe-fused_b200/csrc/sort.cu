@@ -1,4 +1,5 @@
-// Stable sort of rows by expert id: histogram -> scan -> stable scatter.
+// Stable sort of rows by expert id: histogram -> scan -> stable scatter, as one cooperative launch
+// (sort_fused_kernel) when all chunks fit on the GPU at once, otherwise as the three kernels below.
 //
 // Work is split into chunks of SORT_CHUNK consecutive rows, one CTA per chunk.
 //   sort_hist    : per-chunk histogram                       -> ws.hist[chunk][e]
@@ -9,6 +10,8 @@
 //                  warp with __match_any_sync so equal ids keep their original order.
 // Essential traffic is M*(sizeof(id) + 8) bytes; the E*M compare matrix of the reference
 // formulation (qwen3_moe_fused/kernels/indexing.py:52-56) is never materialised.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace moe {
@@ -151,6 +154,112 @@ sort_scatter_kernel(const void* __restrict__ s, int is64, int64_t M, int E,
   }
 }
 
+// The whole sort in ONE cooperative launch (all chunks' CTAs resident at once, one grid-wide barrier):
+//   A  per-warp histograms of the chunk in shared memory; the chunk's totals go to hist[chunk][e]
+//   -- grid barrier --
+//   B  every CTA sums the totals of all chunks per expert (E * chunks words from L2), scans the experts,
+//      adds the rows of earlier chunks, and turns its per-warp histograms into running positions
+//   C  stable scatter, as in sort_scatter_kernel
+// The ids are read twice from L2 (A and C); nothing else is shared between launches, so the three-kernel
+// path's two launch gaps disappear.  Used when every chunk's CTA fits on the GPU at once.
+__global__ void __launch_bounds__(SORT_THREADS)
+sort_fused_kernel(const void* __restrict__ s, int is64, int64_t M, int E, int nchunks, int32_t* __restrict__ hist,
+                  int32_t* __restrict__ counts, int32_t* __restrict__ inv_idx, int32_t* __restrict__ idx) {
+  extern __shared__ int32_t sh[];            // [SORT_WARPS][E] histograms, then running positions
+  int32_t* base_of = sh + (size_t)SORT_WARPS * E;  // [E] first position of this chunk's rows of expert e
+  __shared__ int32_t warp_excl[SORT_WARPS];
+  __shared__ int32_t pass_total;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int32_t* mine = sh + (size_t)warp * E;
+  for (int i = threadIdx.x; i < SORT_WARPS * E; i += SORT_THREADS) sh[i] = 0;
+  __syncthreads();
+  const int64_t wbase = (int64_t)blockIdx.x * SORT_CHUNK + (int64_t)warp * SORT_ROWS_PER_WARP;
+  for (int it = 0; it < SORT_ROWS_PER_WARP / 32; ++it) {
+    const int64_t b = wbase + it * 32 + lane;
+    const int64_t e = (b < M) ? load_index(s, is64, b) : -1;
+    const bool ok = e >= 0 && e < E;
+    const unsigned key = ok ? (unsigned)e : (unsigned)(E + lane);
+    const unsigned peers = __match_any_sync(0xffffffffu, key);
+    if (ok && lane == (__ffs(peers) - 1)) mine[e] += __popc(peers);
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
+    int32_t t = 0;
+#pragma unroll
+    for (int w = 0; w < SORT_WARPS; ++w) t += sh[(size_t)w * E + e];
+    hist[(int64_t)blockIdx.x * E + e] = t;
+  }
+  __threadfence();
+  cooperative_groups::this_grid().sync();
+
+  // B: expert totals, exclusive scan over the experts, rows of earlier chunks
+  int32_t carry = 0;  // same value in every thread
+  for (int e0 = 0; e0 < E; e0 += SORT_THREADS) {
+    const int e = e0 + (int)threadIdx.x;
+    int32_t total = 0, before = 0;
+    if (e < E) {
+      for (int c = 0; c < nchunks; ++c) {
+        const int32_t t = __ldcg(hist + (int64_t)c * E + e);
+        if (c < (int)blockIdx.x) before += t;
+        total += t;
+      }
+      if (blockIdx.x == 0) counts[e] = total;
+    }
+    int32_t incl = total;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int32_t v = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += v;
+    }
+    if (lane == 31) warp_excl[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      const int32_t w = lane < SORT_WARPS ? warp_excl[lane] : 0;
+      int32_t wi = w;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int32_t v = __shfl_up_sync(0xffffffffu, wi, d);
+        if (lane >= d) wi += v;
+      }
+      if (lane < SORT_WARPS) warp_excl[lane] = wi - w;
+      if (lane == 31) pass_total = wi;
+    }
+    __syncthreads();
+    if (e < E) base_of[e] = carry + warp_excl[warp] + (incl - total) + before;
+    carry += pass_total;
+    __syncthreads();
+  }
+  if (idx == nullptr) return;
+  for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
+    int32_t run = base_of[e];
+#pragma unroll
+    for (int w = 0; w < SORT_WARPS; ++w) {
+      const int32_t t = sh[(size_t)w * E + e];
+      sh[(size_t)w * E + e] = run;
+      run += t;
+    }
+  }
+  __syncthreads();
+  // C: positions in original order
+  for (int it = 0; it < SORT_ROWS_PER_WARP / 32; ++it) {
+    const int64_t b = wbase + it * 32 + lane;
+    const int64_t e = (b < M) ? load_index(s, is64, b) : -1;
+    const bool ok = e >= 0 && e < E;
+    const unsigned key = ok ? (unsigned)e : (unsigned)(E + lane);
+    const unsigned peers = __match_any_sync(0xffffffffu, key);
+    int32_t pos = 0;
+    if (ok) pos = mine[e] + __popc(peers & ((1u << lane) - 1u));
+    __syncwarp();
+    if (ok && lane == (__ffs(peers) - 1)) mine[e] += __popc(peers);
+    __syncwarp();
+    if (ok) {
+      idx[b] = pos;
+      inv_idx[pos] = (int32_t)b;
+    }
+  }
+}
+
 // Single CTA: counts of ids below / at-or-below each expert (any input order).
 __global__ void __launch_bounds__(1024)
 begins_ends_kernel(const void* __restrict__ s, int is64, int64_t M, int E, int32_t* __restrict__ out) {
@@ -224,10 +333,41 @@ static int sort_check(const void* s, int s_dtype, int64_t M, int E, const int32_
 // The three launches of the sort, with `scratch` holding moe_sort_workspace_bytes(M, E) bytes.
 // Every word of the scratch that the scan and scatter kernels read is written first by the
 // histogram and scan kernels of the same call, so its previous contents do not matter.
+// Chunks whose CTAs of sort_fused_kernel can all be resident at once on the current device (0: the
+// device cannot launch cooperatively); the answer depends on E through the shared-memory size.
+static int sort_fused_capacity(int E, size_t smem) {
+  static int coop[64] = {0};  // 0 unknown, 1 yes, 2 no
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (coop[dev] == 0) {
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrCooperativeLaunch, dev);
+    coop[dev] = v ? 1 : 2;
+  }
+  if (coop[dev] != 1) return 0;
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sort_fused_kernel, SORT_THREADS, smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  (void)E;
+  return per_sm * sm_count();
+}
+
 static int sort_launch(const void* s, int is64, int64_t M, int E, int32_t* counts, int32_t* inv_idx, int32_t* idx,
                        void* scratch, cudaStream_t stream) {
   const int nchunks = (int)sort_chunks(M);
   int32_t* hist = (int32_t*)scratch;
+  // one cooperative launch when every chunk's CTA fits on the GPU at once (up to a few million rows)
+  const size_t fused_smem = (size_t)(SORT_WARPS + 1) * E * sizeof(int32_t);
+  if (nchunks > 0 && fused_smem <= 48 * 1024 && nchunks <= sort_fused_capacity(E, fused_smem)) {
+    int nch = nchunks;
+    void* args[] = {(void*)&s, (void*)&is64, (void*)&M, (void*)&E, (void*)&nch, (void*)&hist, (void*)&counts, (void*)&inv_idx, (void*)&idx};
+    const cudaError_t e = cudaLaunchCooperativeKernel((const void*)sort_fused_kernel, dim3(nchunks), dim3(SORT_THREADS), args,
+                                                      fused_smem, stream);
+    if (e == cudaSuccess) return MOE_OK;
+    (void)cudaGetLastError();  // (e.g. the device is shared with another resident kernel's reservation): three launches
+  }
   int32_t* offsets = hist + (size_t)nchunks * E;
   if (nchunks > 0) {
     sort_hist_kernel<<<nchunks, SORT_THREADS, E * sizeof(int32_t), stream>>>(s, is64, M, E, hist);

@@ -259,7 +259,8 @@ struct TileFeed {
       } while ((v >> 31) != ph);
       atomicAdd(&g_tc_late_values, 1);  // diagnostic: the barrier completed before the value was visible
     }
-    fence_acq_rel_cluster();  // the read is over before the slot is handed back
+    // (the parity test above depends on the loaded value, so the load has completed before the slot is
+    // handed back below)
     if constexpr (NCTA == 2) mbar_arrive_cluster(home_empty0 + q * 8);
     else mbar_arrive(&ring->empty[q]);
     ++n;
