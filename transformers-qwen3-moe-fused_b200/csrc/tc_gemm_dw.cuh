@@ -240,26 +240,39 @@ dw_kernel(const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
         if (!mbar_wait_cluster(&ctl->tmem_empty[acc], acc_ph ^ 1, abort_flag, W_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int mb = 0; mb < m_blocks; ++mb, ++it) {
+        // One reduction block of 64 rows: `steps` MMAs of 16 rows.  The full blocks use the unrolled,
+        // branch-free form (a test between the MMAs of one block slows the issuing thread markedly);
+        // only the expert's last block runs the counted loop.
+        auto issue_block = [&](int mb, auto full_block, int steps) -> bool {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait_cluster(&ctl->full[s], ph, abort_flag, W_FULL)) { ok = false; break; }
+          if (!mbar_wait_cluster(&ctl->full[s], ph, abort_flag, W_FULL)) return false;
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
           const uint32_t sb = sa + 2 * CHUNK_BYTES;
           const uint64_t da = make_smem_desc(sa, CHUNK_BYTES, 1024);
           const uint64_t db = make_smem_desc(sb, CHUNK_BYTES, 1024);
-          const int steps = mb == m_blocks - 1 ? last_steps : BK / UMMA_K;
+          if constexpr (decltype(full_block)::value) {
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t adv = (uint64_t)((k * UMMA_K * 128) >> 4);
-            if (k < steps) {
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t adv = (uint64_t)((k * UMMA_K * 128) >> 4);
+              if constexpr (PAIR) umma_f16_pair(d_tmem, da + adv, db + adv, p.idesc, (mb | k) != 0);
+              else umma_f16(d_tmem, da + adv, db + adv, p.idesc, (mb | k) != 0);
+            }
+          } else {
+#pragma unroll 1
+            for (int k = 0; k < steps; ++k) {
+              const uint64_t adv = (uint64_t)((k * UMMA_K * 128) >> 4);
               if constexpr (PAIR) umma_f16_pair(d_tmem, da + adv, db + adv, p.idesc, (mb | k) != 0);
               else umma_f16(d_tmem, da + adv, db + adv, p.idesc, (mb | k) != 0);
             }
           }
           if constexpr (PAIR) umma_commit_pair(&ctl->empty[s], 3); else umma_commit(&ctl->empty[s]);
-        }
+          ++it;
+          return true;
+        };
+        for (int mb = 0; mb + 1 < m_blocks && ok; ++mb) ok = issue_block(mb, std::true_type{}, BK / UMMA_K);
+        if (ok) ok = issue_block(m_blocks - 1, std::false_type{}, last_steps);
         if (ok) { if constexpr (PAIR) umma_commit_pair(&ctl->tmem_full[acc], 3); else umma_commit(&ctl->tmem_full[acc]); }
         ++acc_it;
       }

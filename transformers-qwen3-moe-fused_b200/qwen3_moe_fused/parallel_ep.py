@@ -473,8 +473,8 @@ class PeerMoeBlock:
     max_rows rows.  By default the receive buffers have that size, so no routing can overflow them.
     With a smaller `capacity_factor` a skewed routing can: rows that do not fit are never written
     (nothing is stored out of bounds), the push kernels count them on the sending rank, and the
-    outputs of the tokens they belong to are WRONG for that call (their result rows are set to NaN,
-    so the output rows are NaN rather than plausible numbers).  The counts of all ranks are summed
+    outputs of the tokens they belong to are WRONG for that call (their result rows hold whatever an
+    earlier call left there, or NaN with `poison_results=True`).  The counts of all ranks are summed
     inside the call's first fence and copied to the host without stalling the stream; a non-zero
     sum raises `ReceiveOverflow` on EVERY rank at the start of the NEXT call on this object (so no
     rank is left waiting in a collective), or when `check()` is called; `check_capacity=True` tests
@@ -482,14 +482,18 @@ class PeerMoeBlock:
     """
 
     def __init__(self, world: int, rank: int, device, hidden: int, max_rows: int, dtype: torch.dtype,
-                 capacity_factor: Optional[float] = None, group=None, max_tokens: Optional[int] = None):
+                 capacity_factor: Optional[float] = None, group=None, max_tokens: Optional[int] = None,
+                 poison_results: bool = False):
         """max_rows: tokens * top_k per rank; max_tokens: tokens per rank (enables the token-deduplicated
         dispatch); a rank can receive up to capacity_factor * max_rows rows (None: world * max_rows, which
-        every routing fits into)."""
+        every routing fits into).  poison_results: with a capacity that can overflow, fill the result buffer
+        with NaN before every call, so that the outputs of tokens whose rows were dropped are NaN instead of
+        numbers of an earlier call (costs one pass over max_rows * hidden; the overflow is reported either way)."""
         self.world, self.rank, self.group = world, rank, group
         factor = float(world) if capacity_factor is None else float(capacity_factor)
         cap = (int(max_rows * factor) + 7) // 8 * 8
         self.can_overflow = cap < world * max_rows
+        self.poison_results = poison_results and self.can_overflow
         self.dedup = max_tokens is not None
         if self.dedup:
             self.ch_tok = PeerChannel(world * max_tokens, hidden, dtype, device, group)  # every rank's tokens fit
@@ -514,7 +518,7 @@ class PeerMoeBlock:
         n = int(self.dropped_host[0])
         if n:
             raise ReceiveOverflow(f"{n} rows did not fit into their owners' receive buffers (capacity {self.capacity_rows} rows "
-                                  f"per rank); the outputs of the affected tokens were NaN. Build PeerMoeBlock with a larger capacity_factor.")
+                                  f"per rank); the outputs of the affected tokens were wrong. Build PeerMoeBlock with a larger capacity_factor.")
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, gate_weight: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor,
@@ -543,7 +547,7 @@ class PeerMoeBlock:
             plan = PeerPlan.build(m_sizes, self.world, self.rank, self.group)
         if check_capacity:  # one host read
             assert int(plan.recv_rows) <= self.capacity_rows, "receive buffer too small for this routing"
-        if self.can_overflow:
+        if self.poison_results:
             # result rows that never arrive (their input was dropped) must not be whatever an earlier call left there
             self.ch_y.local[:T * k].fill_(float("nan"))
         if self.dedup:
