@@ -641,7 +641,7 @@ def main():
     from qwen3_moe_fused.grouped_gemm.forward import grouped_gemm_forward
     from qwen3_moe_fused.grouped_gemm.forward_transposed import grouped_gemm_forward_transposed
     from qwen3_moe_fused.kernels.indexing import get_expert_counts_and_idx
-    from qwen3_moe_fused.kernels.routing import _gather_rows, softmax_topk
+    from qwen3_moe_fused.kernels.routing import _expand_rows, softmax_topk
 
     _lib.load()
     _lib.set_gemm_path({"auto": _lib.PATH_AUTO, "tc": _lib.PATH_TC, "tc_single": _lib.PATH_TC_SINGLE, "simt": _lib.PATH_SIMT}[args.gemm_path])
@@ -679,7 +679,7 @@ def main():
     hidden_d = hidden_h.to(dev)
     dy_d = dy_h.to(dev)
     m_sizes, sort_idx, inv_sort_idx = route_and_sort(logits_d, ids_d)
-    x_d = _gather_rows(hidden_d, sort_idx, k)
+    x_d = _expand_rows(hidden_d, inv_sort_idx, k)  # rows in expert order, every token row read once
     plan = None
     peer = None
     if world > 1 and args.ep_transport == "nccl":
@@ -902,8 +902,8 @@ def main():
         if not last:
             upload((i + 1) % 2)
         hd, dyd, lg, idd = sl["hd"], sl["dyd"], sl["lg"], sl["idd"]
-        ms, si, _ = route_and_sort(lg, idd)
-        xs = _gather_rows(hd, si, k)
+        ms, si, inv = route_and_sort(lg, idd)
+        xs = _expand_rows(hd, inv, k)
         if world == 1:
             y = grouped_gemm_forward(xs, w, ms)
             dx = grouped_gemm_forward_transposed(dyd, w, ms)

@@ -53,7 +53,11 @@ int moe_b200_version(void);
 const char* moe_status_string(int status);
 
 /* Set / get the kernel family used by the grouped GEMM entry points (process wide,
- * MOE_PATH_*; default AUTO).  Returns the previous value. */
+ * MOE_PATH_*; default AUTO).  Returns the previous value.
+ * For tests and measurements only (they compare the kernel families on the same inputs):
+ * the setting is one word shared by every thread and stream of the process and is read when
+ * a call is issued, so production code leaves it at AUTO, where the selection depends on
+ * dtype, extents and alignment of the call alone. */
 int moe_set_gemm_path(int path);
 int moe_get_gemm_path(void);
 

@@ -138,7 +138,7 @@ class Combine(torch.autograd.Function):
         dy = dw = None
         if ctx.needs_input_grad[0]:
             # dy[j] = weights.flat[sort_idx[j]] * dout[sort_idx[j] // k]
-            dy = _gather_rows(dout, sort_idx, k) * weights.reshape(-1)[sort_idx.long()].unsqueeze(1)
+            dy = _expand_rows(dout, inv_sort_idx, k) * weights.reshape(-1)[sort_idx.long()].unsqueeze(1)
         if ctx.needs_input_grad[3]:
             # dweights[t, j] = <dout[t], y[inv_sort_idx[t*k+j]]>
             dw = torch.einsum("tkh,th->tk", y[inv_sort_idx.long()].view(T, k, -1).float(), dout.float()).to(weights.dtype)

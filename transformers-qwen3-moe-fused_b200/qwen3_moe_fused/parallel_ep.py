@@ -305,6 +305,9 @@ def scattered_grouped_gemm(x: torch.Tensor, weight: torch.Tensor, group_sizes: t
     G = group_sizes.numel()
     group_sizes = _lib.as_index_tensor(group_sizes).contiguous()
     assert out_ptrs.dtype == torch.int64 and out_ptrs.is_contiguous() and out_ptrs.numel() == G
+    # out_ptrs are buffer bases plus whole rows: with a row pitch of a multiple of 16 bytes every entry is
+    # 16-byte aligned (what the output tensor maps need) without reading the device tensor here
+    assert (N * x.element_size()) % 16 == 0 and out_template.data_ptr() % 16 == 0
     if weight_index is not None:
         assert weight_index.dtype == torch.int32 and weight_index.is_contiguous() and weight_index.numel() == G
     lib = _lib.load()
