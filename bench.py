@@ -88,10 +88,11 @@ def make_routing(cfg, seed: int):
 
 
 class ClockSampler:
-    """Samples SM clock, power and throttle reasons while a timed region runs: NVML every 25 ms from a
-    thread of this process (read-only queries), or `nvidia-smi -lms 100` where NVML cannot be loaded."""
+    """Samples SM clock, power and throttle reasons while a timed region runs: NVML every 10 ms from a
+    thread of this process (read-only queries; a default run's timed region lasts 20-odd ms), or
+    `nvidia-smi -lms 100` where NVML cannot be loaded."""
 
-    PERIOD_S = 0.025
+    PERIOD_S = 0.010
 
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -163,7 +164,7 @@ class ClockSampler:
             sm = [c for c, _, _ in self.samples]
             return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_min_mhz": min(sm) if sm else None,
                     "sm_max_mhz": self.max_mhz, "power_w_max": max((p for _, p, _ in self.samples), default=None),
-                    "reasons": reasons, "samples": len(sm), "source": "nvml, 25 ms period"}
+                    "reasons": reasons, "samples": len(sm), "source": f"nvml, {int(self.PERIOD_S * 1000)} ms period"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -238,7 +239,7 @@ def config_dict(args, cfg):
                         f"{cfg['tokens'] * cfg['k']} rows/GPU, in={cfg['K']}, out={cfg['N']}, experts={cfg['E']}",
             "routing": cfg["routing"], "l2": "inputs larger than L2 (weights alone exceed 400 MB); no flush needed",
             "parallelism": "single GPU" if args.gpus == 1 else (
-                f"expert parallel ep{args.gpus}, rows pushed over peer memory (x once per token and destination rank), GEMM epilogues store to the source rank"
+                f"expert parallel ep{args.gpus}, rows pushed over peer memory ({'x once per token and destination rank' if args.ep_dispatch == 'dedup' and args.ep_chunks == 1 else 'one row per token and expert'}), GEMM epilogues store to the source rank"
                 if args.ep_transport == "peer" else f"expert parallel ep{args.gpus} (NCCL all-to-all dispatch/combine)")}
 
 
