@@ -103,7 +103,12 @@ int moe_batch_begins_ends(const void* s_sorted, int s_dtype, int64_t M, int E,
  * Grouped GEMMs.  Rows of x / y are sorted by expert; expert e owns m_sizes[e]
  * consecutive rows (m_sizes_dtype MOE_I32 or MOE_I64, sum = M, zeros allowed).
  * Accumulation is fp32; the result is rounded once to dtype_out.
- * ws/ws_bytes: moe_grouped_gemm_workspace_bytes(); may be NULL/0 when that is 0.
+ * ws/ws_bytes: device scratch of moe_grouped_gemm_workspace_bytes() bytes, 128-byte aligned,
+ *   owned by the caller.  A small launch ahead of each GEMM writes per-expert tensor maps and a
+ *   work-item counter into it, so one workspace serves one GEMM at a time: calls issued on one
+ *   stream may share it, calls on different streams need one each.  Forward and dX also accept
+ *   NULL/0 and then run a slower form (no per-expert maps, fixed tile order); dW on the
+ *   tensor-core path and the fused / gathered / scattered forms return MOE_ERR_WORKSPACE.
  * ------------------------------------------------------------------------------- */
 size_t moe_grouped_gemm_workspace_bytes(int which /*0 fwd, 1 dx, 2 dw*/, int64_t M, int N, int K, int E);
 
