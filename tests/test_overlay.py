@@ -82,6 +82,20 @@ CHILD = textwrap.dedent(
     from_package(qlayer.moe_fused_linear)
     assert issubclass(qlayer.MoeFusedLinear4bit, modular.MoeFusedLinear)
 
+    # the import lines of the reference's kernel tests and benchmarks (test_moe_fused_linear.py:9-11,
+    # test_moe_fused_linear_bwd.py:8-14, benchmark_moe_fused_linear*.py:10-13) resolve to this package
+    from qwen3_moe_fused.functional import (_moe_fused_linear_naive_bwd_input, _moe_fused_linear_naive_bwd_weight,
+                                            _moe_fused_linear_naive_fwd, moe_fused_linear)
+    from qwen3_moe_fused.grouped_gemm.backward_dw import grouped_gemm_backward_dw
+    from qwen3_moe_fused.grouped_gemm.forward import grouped_gemm_forward
+    from qwen3_moe_fused.grouped_gemm.forward_4bit import grouped_gemm_forward_4bit
+    from qwen3_moe_fused.grouped_gemm.forward_transposed import grouped_gemm_forward_transposed
+    from qwen3_moe_fused.kernels.indexing import get_expert_counts
+    for fn in (_moe_fused_linear_naive_fwd, _moe_fused_linear_naive_bwd_input, _moe_fused_linear_naive_bwd_weight,
+               moe_fused_linear, grouped_gemm_forward, grouped_gemm_forward_transposed, grouped_gemm_backward_dw,
+               grouped_gemm_forward_4bit, get_expert_counts):
+        from_package(fn)
+
     # the reference's module classes build on the CPU and call this package's function
     lin = modular.MoeFusedLinear(8, 16, 4)
     assert tuple(lin.weight.shape) == (4, 16, 8)
