@@ -904,7 +904,8 @@ def main():
             upload((i + 1) % 2)
         hd, dyd, lg, idd = sl["hd"], sl["dyd"], sl["lg"], sl["idd"]
         ms, si, inv = route_and_sort(lg, idd)
-        xs = _expand_rows(hd, inv, k)
+        # expert-major rows of x; the deduplicated dispatch sends tokens and expands them on the owner instead
+        xs = None if (peer is not None and peer["dedup"]) else _expand_rows(hd, inv, k)
         if world == 1:
             y = grouped_gemm_forward(xs, w, ms)
             dx = grouped_gemm_forward_transposed(dyd, w, ms)
