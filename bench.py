@@ -18,11 +18,17 @@ its own 8192 tokens and rows travel to the rank that owns their expert and resul
 back (weak scaling: per-GPU rows are fixed).  Default transport: rows are stored into the
 owner's memory over NVLink by a copy kernel, and the forward / dX epilogues store their
 results straight into the source rank's memory (`--ep-transport peer`); `--ep-transport
-nccl` moves both directions by NCCL all-to-all instead.  After the timed loop one step's
-results are checked against the single-GPU kernels (`ep_check` in the line).
+nccl` moves both directions by NCCL all-to-all instead.  By default a token of x crosses once
+per destination rank and is expanded into its expert rows on the owner (`--ep-dispatch dedup`;
+`rows` sends one row per token and expert).  After the timed loop one step's results are
+checked against the single-GPU kernels (`ep_check` in the line).
 
 At N = 1 the line also carries `extra_workloads`: the same measurement on the down_proj
 shape with Zipf(1.2) routing (skewed, ragged and empty groups).
+
+`--suite kernels` times the surrounding kernels (SiLU-mul, router, sort, gather / expand, combine,
+NF4 decode and NF4-fused forward, fused-LoRA MLP, fused gate/up, block forward, the library
+grouped GEMM as a yardstick), one JSON line each; `--suite block` the MoE block forward on N GPUs.
 """
 from __future__ import annotations
 
