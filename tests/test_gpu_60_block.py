@@ -123,7 +123,10 @@ def test_fast_lora_forward_backward(cuda, dtype, quant):
     yr = _fast_lora_reference(xr, G.float().cpu(), Agr, Bgr, Sg, U.float().cpu(), Aur, Bur, Su, W.float().cpu(), Awr, Bwr, Sw,
                               m_sizes.cpu())
     yr.backward(dy.float().cpu())
-    tol = 2e-4 if dtype == "f32" else 3e-2  # bf16: several chained roundings (e, g, h, A x) as in the reference
+    # bf16 against the fp32 definition: storing e, g, h, A x and the gradients' intermediates in bf16 moves every
+    # result by 0.5-1 % of its largest element, in the reference's order of operations as much as in this one
+    # (tests/test_fast_lora_rounding.py measures both on the CPU), so 1e-2 has no margin; 2e-2 is the bar
+    tol = 2e-4 if dtype == "f32" else 2e-2
     def rel(a, b):
         return float((a.float().cpu() - b).abs().max() / b.abs().max().clamp_min(1e-30))
     assert rel(y, yr.detach()) < tol, "y"
