@@ -6,10 +6,13 @@ benchmark, and by nothing else.  No product code path may call into it.
 
 Parity status: the sort / permutation functions, the three grouped-GEMM definitions, the
 plain SiLU-mul and the block composition are pinned against outputs of the reference's
-own Python code (fixtures under tests/golden/, produced by tests/golden/make_golden.py).
+own Python code (fixtures under tests/golden/, produced by tests/golden/make_golden.py);
+SiLU-mul's rounding points, the three grouped GEMMs and the 4-bit decode inside the forward
+are pinned against the reference's Triton kernels executed under Triton's CPU interpreter
+(tests/golden/make_golden_triton.py, float16 / float32).
 The NF4 code table and quantiser come from bitsandbytes, which is neither part of the
-reference tree nor installed: "parity unpinned" for those two (the decode arithmetic and
-the packed layout are pinned by the reference source, see `nf4_dequantize`).
+reference tree nor installed: "parity unpinned" for those two (the table is rebuilt from its
+published construction and checked against the published constants).
 
 Every function cites the reference lines it follows (paths inside the reference project).
 Floating-point inputs are taken as float32 arrays holding values already rounded to the
