@@ -6,8 +6,9 @@ Triton's interpreter (TRITON_INTERPRET=1) runs a `@triton.jit` function program 
 the reference's own kernel sources produce these vectors: SiLU-mul forward / backward / in-place backward
 (kernels/silu_mul.py), the grouped GEMM forward, transposed forward (dX) and weight gradient
 (grouped_gemm/forward.py, forward_transposed.py, backward_dw.py) and the forward with the 4-bit weight decoded
-inside the kernel (grouped_gemm/forward_4bit.py).  The kernels are launched directly (`kernel.fn[grid](...)`,
-the function under the autotuner) with the argument lists of the reference's wrappers
+inside the kernel (grouped_gemm/forward_4bit.py), and the whole fused-LoRA expert MLP with its hand-written
+backward (kernels/fast_lora.py, the reference's autograd function running on those kernels).  The kernels are
+launched directly (`kernel.fn[grid](...)`, the function under the autotuner) with the argument lists of the reference's wrappers
 (forward.py:138-159, forward_transposed.py:128-149, backward_dw.py:111-133, forward_4bit.py:183-207,
 silu_mul.py:121-161), because the wrappers insist on CUDA tensors.  The interpreter has no bfloat16 (numpy
 has none), so the fixtures are float16 and float32; the kernels' rounding points do not depend on which
@@ -82,12 +83,7 @@ def silu_cases(out):
 
 
 def gemm_cases(out):
-    from qwen3_moe_fused.grouped_gemm import backward_dw as DW
-    from qwen3_moe_fused.grouped_gemm import forward as FW
-    from qwen3_moe_fused.grouped_gemm import forward_transposed as FT
-
-    blocks = dict(BLOCK_SIZE_M=32, BLOCK_SIZE_N=32, BLOCK_SIZE_K=32)
-    sms = 4
+    forward, forward_transposed, backward_dw, _, _ = _interpreted_wrappers()
     for name, dt, M, N, K, E, empty in (("f16", torch.float16, 150, 48, 40, 6, (2,)),
                                         ("f32", torch.float32, 97, 24, 36, 5, (0, 4))):
         rng = np.random.default_rng(M)
@@ -97,21 +93,88 @@ def gemm_cases(out):
         x = torch.randn(M, K, generator=g).to(dt)
         w = (torch.randn(E, N, K, generator=g) * K ** -0.5).to(dt)
         dy = torch.randn(M, N, generator=g).to(dt)
-        y = torch.zeros((M, N), dtype=dt)
-        FW._grouped_gemm_forward_kernel.fn[(sms,)](x, w, m_sizes, y, M, N, K, E, sms, x.stride(0), x.stride(1), w.stride(0),
-                                                   w.stride(1), w.stride(2), y.stride(0), y.stride(1), **blocks)
-        # dX: rows dy (M, N) times w (E, N, K) read transposed -> (M, K); in the kernel's names x = dy, "K" = N, "N" = K
-        dx = torch.zeros((M, K), dtype=dt)
-        FT._grouped_gemm_forward_transposed_kernel.fn[(sms,)](dy, w, m_sizes, dx, M, K, N, E, sms, dy.stride(0), dy.stride(1),
-                                                              w.stride(0), w.stride(1), w.stride(2), dx.stride(0),
-                                                              dx.stride(1), **blocks)
-        dw = torch.zeros((E, N, K), dtype=dt)
-        DW._grouped_gemm_backward_dw_kernel.fn[(sms,)](x, dy, m_sizes, dw, M, N, K, E, sms, x.stride(0), x.stride(1), dy.stride(0),
-                                                       dy.stride(1), dw.stride(0), dw.stride(1), dw.stride(2), **blocks)
+        y = forward(x, w, m_sizes)
+        dx = forward_transposed(dy, w, m_sizes)  # rows dy (M, N) times w (E, N, K) read transposed -> (M, K)
+        dw = backward_dw(x, dy, m_sizes, dt)
         f32 = lambda t: t.float().numpy()
         np.savez_compressed(out / f"triton_grouped_gemm_{name}.npz", x=f32(x), w=f32(w), dy=f32(dy), m_sizes=sizes,
                             y=f32(y), dx=f32(dx), dw=f32(dw))
         print("gemm", name, "ok")
+
+
+def _interpreted_wrappers(sms=4, block=32):
+    """The reference's five wrappers (same arguments, same results) for CPU tensors: each launches the reference's
+    kernel under the interpreter exactly as the wrapper in the reference does."""
+    import triton
+    from qwen3_moe_fused.grouped_gemm import backward_dw as DW
+    from qwen3_moe_fused.grouped_gemm import forward as FW
+    from qwen3_moe_fused.grouped_gemm import forward_transposed as FT
+    from qwen3_moe_fused.kernels import silu_mul as S
+
+    blocks = dict(BLOCK_SIZE_M=block, BLOCK_SIZE_N=block, BLOCK_SIZE_K=block)
+
+    def forward(x, w, m_sizes, dtype=None):
+        (M, K), (E, N, _) = x.shape, w.shape
+        y = torch.zeros((M, N), dtype=dtype or x.dtype)
+        FW._grouped_gemm_forward_kernel.fn[(sms,)](x, w, m_sizes, y, M, N, K, E, sms, x.stride(0), x.stride(1), w.stride(0),
+                                                   w.stride(1), w.stride(2), y.stride(0), y.stride(1), **blocks)
+        return y
+
+    def forward_transposed(x, w, m_sizes, dtype=None):
+        (M, K), (E, _, N) = x.shape, w.shape
+        y = torch.zeros((M, N), dtype=dtype or x.dtype)
+        FT._grouped_gemm_forward_transposed_kernel.fn[(sms,)](x, w, m_sizes, y, M, N, K, E, sms, x.stride(0), x.stride(1),
+                                                              w.stride(0), w.stride(1), w.stride(2), y.stride(0), y.stride(1),
+                                                              **blocks)
+        return y
+
+    def backward_dw(x, y, m_sizes, dtype):
+        (M, K), N, E = x.shape, y.shape[1], m_sizes.numel()
+        w = torch.zeros((E, N, K), dtype=dtype)
+        DW._grouped_gemm_backward_dw_kernel.fn[(sms,)](x, y, m_sizes, w, M, N, K, E, sms, x.stride(0), x.stride(1), y.stride(0),
+                                                       y.stride(1), w.stride(0), w.stride(1), w.stride(2), **blocks)
+        return w
+
+    def silu_forward(e, g):
+        h = torch.empty_like(e)
+        S._silu_mul_forward_kernel.fn[(triton.cdiv(e.numel(), 128),)](e, g, h, e.numel(), BLOCK_SIZE=128)
+        return h
+
+    def silu_backward_inplace(dh, e, g):
+        S._silu_mul_backward_inplace_kernel.fn[(triton.cdiv(e.numel(), 128),)](dh, e, g, e.numel(), BLOCK_SIZE=128)
+
+    return forward, forward_transposed, backward_dw, silu_forward, silu_backward_inplace
+
+
+def fast_lora_case(out):
+    """The reference's `FastLora` autograd function (kernels/fast_lora.py:66-175), unchanged, with the five kernel
+    wrappers it imports rebound to the interpreter-backed ones: forward and all seven gradients in float16."""
+    import qwen3_moe_fused.kernels.fast_lora as FL
+
+    (FL.grouped_gemm_forward, FL.grouped_gemm_forward_transposed, FL.grouped_gemm_backward_dw, FL.silu_mul_forward,
+     FL.silu_mul_backward_inplace) = _interpreted_wrappers()
+    B, H, I, E, R = 120, 32, 48, 4, 8
+    rng = np.random.default_rng(11)
+    g = torch.Generator().manual_seed(11)
+    dt = torch.float16
+    sizes = _ragged_sizes(rng, B, E, (2,))
+    m_sizes = torch.from_numpy(sizes).to(torch.int32)
+    mk = lambda *s, scale=1.0: (torch.randn(*s, generator=g) * scale).to(dt)
+    x = mk(B, H).requires_grad_()
+    G, U, W = mk(E, I, H, scale=H ** -0.5), mk(E, I, H, scale=H ** -0.5), mk(E, H, I, scale=I ** -0.5)
+    loras = [mk(E, R, H, scale=H ** -0.5), mk(E, I, R, scale=0.1), mk(E, R, H, scale=H ** -0.5), mk(E, I, R, scale=0.1),
+             mk(E, R, I, scale=I ** -0.5), mk(E, H, R, scale=0.1)]
+    Ag, Bg, Au, Bu, Aw, Bw = (t.requires_grad_() for t in loras)
+    Sg, Su, Sw = 0.5, 2.0, 1.0
+    dy = mk(B, H)
+    y = FL.fast_lora(x, G, None, Ag, Bg, Sg, U, None, Au, Bu, Su, W, None, Aw, Bw, Sw, m_sizes)
+    y.backward(dy)
+    f32 = lambda t: t.detach().float().numpy()
+    np.savez_compressed(out / "triton_fast_lora_f16.npz", x=f32(x), G=f32(G), U=f32(U), W=f32(W), Ag=f32(Ag), Bg=f32(Bg),
+                        Au=f32(Au), Bu=f32(Bu), Aw=f32(Aw), Bw=f32(Bw), scalings=np.array([Sg, Su, Sw]), dy=f32(dy),
+                        m_sizes=sizes, y=f32(y), dx=f32(x.grad), dAg=f32(Ag.grad), dBg=f32(Bg.grad), dAu=f32(Au.grad),
+                        dBu=f32(Bu.grad), dAw=f32(Aw.grad), dBw=f32(Bw.grad))
+    print("fast_lora ok")
 
 
 def nf4_case(out):
@@ -145,6 +208,7 @@ def main():
     silu_cases(HERE)
     gemm_cases(HERE)
     nf4_case(HERE)
+    fast_lora_case(HERE)
 
 
 if __name__ == "__main__":
