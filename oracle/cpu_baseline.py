@@ -47,6 +47,26 @@ def vectorised_fwd(x: torch.Tensor, w: torch.Tensor, m_sizes: torch.Tensor) -> t
     return out
 
 
+def vectorised_bwd_input(dy: torch.Tensor, w: torch.Tensor, m_sizes: torch.Tensor) -> torch.Tensor:
+    out = torch.empty(dy.shape[0], w.shape[2], dtype=dy.dtype)
+    row = 0
+    for e, n in enumerate(m_sizes.tolist()):
+        if n:
+            out[row:row + n] = dy[row:row + n] @ w[e]
+            row += n
+    return out
+
+
+def vectorised_bwd_weight(dy: torch.Tensor, x: torch.Tensor, w_like: torch.Tensor, m_sizes: torch.Tensor) -> torch.Tensor:
+    out = torch.zeros_like(w_like)
+    row = 0
+    for e, n in enumerate(m_sizes.tolist()):
+        if n:
+            out[e] = dy[row:row + n].T @ x[row:row + n]
+            row += n
+    return out
+
+
 def time_call(fn, *args, repeats: int = 1) -> float:
     """Best wall time in seconds over `repeats` calls."""
     best = float("inf")

@@ -89,3 +89,19 @@ def test_reference_arm_prints_the_contract_line():
     env["RANK"] = "1"
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=str(ROOT))
     assert res.returncode == 0 and not [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+
+
+def test_vectorised_cpu_figure_computes_the_same_results_as_the_row_loops():
+    from oracle import cpu_baseline as C
+
+    g = torch.Generator().manual_seed(1)
+    E, N, K, M = 5, 7, 9, 40
+    w = torch.randn(E, N, K, generator=g)
+    x, dy = torch.randn(M, K, generator=g), torch.randn(M, N, generator=g)
+    experts = torch.sort(torch.randint(0, E - 1, (M,), generator=g)).values   # the last expert stays empty
+    m_sizes = torch.bincount(experts, minlength=E)
+    assert torch.allclose(C.vectorised_fwd(x, w, m_sizes), C.rowloop_fwd(x, w, experts), atol=1e-5)
+    assert torch.allclose(C.vectorised_bwd_input(dy, w, m_sizes), C.rowloop_bwd_input(dy, w, experts), atol=1e-5)
+    assert torch.allclose(C.vectorised_bwd_weight(dy, x, w, m_sizes), C.rowloop_bwd_weight(dy, x, w, experts), atol=1e-5)
+    small = dict(tokens=64, K=32, N=16, E=4, k=2, routing="softmax")
+    assert bench.cpu_vectorised_arm(small, 64) > 0
